@@ -1,0 +1,76 @@
+"""ctypes binding of the C ABI in include/deepgemm_b200.h.
+
+There is no fallback: if the shared library is missing or a call fails, a RuntimeError is
+raised (the reference raises RuntimeError from its DG_HOST_ASSERT, csrc/utils/exception.hpp:13-37).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from .build import LIB_PATH
+
+DG_E4M3, DG_E2M1_PACKED, DG_BF16, DG_F32 = 0, 1, 2, 3
+GEMM_NORMAL, GEMM_M_CONTIGUOUS, GEMM_M_MASKED, GEMM_M_PSUM, GEMM_K_GROUPED, GEMM_K_GROUPED_PSUM = range(6)
+
+EXPORTS = (
+    "dg_gemm_bs", "dg_sf_pack_ue8m0", "dg_sf_pack_ue8m0_k_grouped", "dg_set_num_sms", "dg_get_num_sms",
+    "dg_set_tc_util", "dg_get_tc_util", "dg_set_mk_alignment_for_contiguous_layout",
+    "dg_get_mk_alignment_for_contiguous_layout", "dg_get_theoretical_mk_alignment_for_contiguous_layout",
+    "dg_set_wait_timeout_ms", "dg_check_status", "dg_last_error", "dg_version",
+)
+
+
+class Operand(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("sf", C.c_void_p), ("ld", C.c_int64), ("sf_ld", C.c_int64),
+                ("dtype", C.c_int32), ("mn_major", C.c_int32), ("gran_k", C.c_int32), ("reserved", C.c_int32)]
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [("gemm_type", C.c_int32), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+                ("num_groups", C.c_int32), ("alignment", C.c_int32),
+                ("a", Operand), ("b", Operand),
+                ("d", C.c_void_p), ("ldd", C.c_int64), ("d_dtype", C.c_int32), ("accumulate", C.c_int32),
+                ("alpha", C.c_float), ("expected_m", C.c_int32),
+                ("grouped_layout", C.c_void_p), ("stream", C.c_void_p),
+                ("force_cta_group", C.c_int32), ("force_block_n", C.c_int32), ("force_swap", C.c_int32),
+                ("reserved", C.c_int32)]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m deepgemm_b200.build` "
+                "(there is no fallback path)")
+        l = C.CDLL(LIB_PATH)
+        l.dg_last_error.restype = C.c_char_p
+        l.dg_version.restype = C.c_char_p
+        l.dg_gemm_bs.argtypes = [C.POINTER(GemmArgs)]
+        l.dg_sf_pack_ue8m0.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                       C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_int32,
+                                       C.c_void_p]
+        l.dg_sf_pack_ue8m0_k_grouped.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                                 C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                                 C.c_void_p]
+        l.dg_check_status.argtypes = [C.POINTER(C.c_uint32)]
+        for name in ("dg_set_num_sms", "dg_set_tc_util", "dg_set_mk_alignment_for_contiguous_layout",
+                     "dg_get_theoretical_mk_alignment_for_contiguous_layout", "dg_set_wait_timeout_ms"):
+            getattr(l, name).argtypes = [C.c_int32]
+        _lib = l
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise RuntimeError(lib().dg_last_error().decode())
+
+
+def check_status():
+    """Synchronise and raise if a kernel abandoned a bounded wait (see dg_check_status)."""
+    info = (C.c_uint32 * 8)()
+    check(lib().dg_check_status(info))

@@ -1,0 +1,632 @@
+// Block-scaled FP8 / FP8xFP4 GEMM for sm_100a: one persistent, warp-specialised kernel.
+//
+//   D[m, n] = alpha * sum_k (A[m, k] * 2^ea[m, k / gran_a]) * (B[n, k] * 2^eb[n, k / gran_b])  (+ C)
+//
+// Replaces the reference's sm100_fp8_fp4_gemm_1d1d_impl
+// (deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_gemm_1d1d.cuh:24-46) for all of its
+// M-/K-grouped schedules.  The design is written in terms of the two UMMA operands:
+//
+//   R ("row" operand, UMMA A): 128 rows per CTA; rows become TMEM lanes.
+//   C ("col" operand, UMMA B): BN rows per tile (split in halves across a CTA pair);
+//                              rows become TMEM columns.
+//
+// kSwap = false: R = GEMM A (tokens), C = GEMM B (weights): the accumulator is a D tile.
+// kSwap = true : R = GEMM B (weights), C = GEMM A (tokens): the accumulator is D^T, which
+//                lets a CTA pair share one (possibly short) token block of any expert.
+//
+// Warp roles (256 threads):  0 TMA producer | 1 UMMA issuer (+TMEM owner) | 2 scale-factor
+// transposer | 3 idle | 4..7 epilogue (warp % 4 == TMEM lane quadrant).
+//
+// Every wait is bounded: on expiry the waiting thread records where it gave up in the
+// status block, raises the CTA's (and its pair's) abort flag, all roles leave their
+// loops, outstanding copies are given time to land, TMEM is freed and the kernel returns.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace dg {
+
+enum GemmType : uint32_t {
+    kGemmNormal = 0,
+    kGemmMContiguous = 1,   // grouped_layout: int32[M], expert id per row (-1 = padding)
+    kGemmMMasked = 2,       // grouped_layout: int32[G], valid rows per group
+    kGemmMPsum = 3,         // grouped_layout: int32[G], cumulative unaligned row ends
+    kGemmKGrouped = 4,      // grouped_layout: int32[G], padded K per group
+    kGemmKGroupedPsum = 5,  // grouped_layout: int32[G], cumulative unaligned K ends
+};
+
+enum StatusCode : uint32_t {
+    kStatusOk = 0,
+    kStatusTimeout = 1,
+};
+enum WaitSite : uint32_t {
+    kSiteProducerEmpty = 1,
+    kSiteTransposerSfFull = 2,
+    kSiteMmaTmemEmpty = 3,
+    kSiteMmaFull = 4,
+    kSiteEpilogueTmemFull = 5,
+};
+
+// One UMMA operand as the kernel sees it (all values computed on the host).
+struct OperandParams {
+    uint32_t mn_major;    // 0: K is the contiguous axis in global memory
+    uint32_t num_boxes;   // TMA boxes per stage per CTA
+    uint32_t box_bytes;   // shared-memory bytes per box
+    uint32_t box_mn;      // rows (MN extent) covered by one box
+    uint32_t tx_bytes;    // bytes one stage's boxes add to the barrier's transaction count
+    uint32_t desc_lbo;    // UMMA descriptor: leading-dimension byte offset
+    uint32_t desc_sbo;    // UMMA descriptor: stride-dimension byte offset
+    uint32_t desc_kstep;  // descriptor start-address advance per UMMA_K (32 elements), bytes
+    uint32_t gran_k;      // 32 or 128 K elements per scale
+    uint32_t fmt;         // kFmtE4M3 / kFmtE2M1
+};
+
+struct GemmParams {
+    CUtensorMap tm_r, tm_c, tm_sfr, tm_sfc, tm_d;
+    OperandParams r, c;
+    uint32_t gemm_type;
+    uint32_t m, n, k;           // logical GEMM shape (per group where grouped)
+    uint32_t num_groups;
+    uint32_t alignment;         // M / K alignment of psum layouts
+    const int32_t* grouped_layout;
+    uint32_t num_m_blocks, num_n_blocks;   // of the (un-grouped) m x n tile grid
+    uint32_t raster;            // tiles along the rasterised axis per super-row
+    uint32_t num_units;         // CTAs (kCtas == 1) or CTA pairs (kCtas == 2) in the grid
+    uint32_t sf_groups_r, sf_groups_c;     // packed-K words per group in the SF tensors (0: not grouped)
+    uint32_t rows_per_group_r, rows_per_group_c;  // row stride between groups of a K-major operand (0: none)
+    uint32_t k_rows_per_group_r, k_rows_per_group_c;  // K-row stride between groups of an MN-major operand
+    float alpha;
+    uint32_t accumulate;        // D += result (TMA reduce-add) instead of D = result
+    uint32_t d_grouped;         // D has a group axis (masked / K-grouped): third store coordinate = group
+    uint32_t timeout_ms;
+    uint32_t* status;           // 16 words: [0] code, [1] site, [2] block, [3] tile iter, [4] k block, [5] stage
+};
+
+struct TileCoord {
+    uint32_t m_blk, n_blk, group;
+    uint32_t k_start, k_len, sfk_base;
+};
+
+// Persistent tile walk shared by all roles: each role thread owns one instance and asks
+// for tile indices unit, unit + num_units, ...
+struct TileWalker {
+    const GemmParams& p;
+    const uint32_t bm, bn;   // GEMM-level tile extents of one unit
+    uint32_t group = 0;
+    uint32_t m_blk_cum = 0;       // m-blocks of the groups before `group`
+    uint32_t group_m_blocks = 0;  // m-blocks of `group`
+    uint32_t row_start = 0;       // psum: first row of `group`
+    uint32_t prev_end = 0;        // psum: unaligned end of the previous group
+    uint32_t k_start = 0, k_len = 0, sfk_base = 0;
+    bool primed = false;
+
+    __device__ TileWalker(const GemmParams& p_, uint32_t bm_, uint32_t bn_) : p(p_), bm(bm_), bn(bn_) {}
+
+    __device__ uint32_t layout(uint32_t i) const { return static_cast<uint32_t>(__ldg(p.grouped_layout + i)); }
+
+    __device__ void swizzle(uint32_t idx, uint32_t num_m, uint32_t num_n, uint32_t& m_blk, uint32_t& n_blk) const {
+        // Super-rows of `raster` m-blocks; inside one, n varies slowest so that concurrently
+        // running units share a small set of R and C rows in L2.
+        const uint32_t per_super = p.raster * num_n;
+        const uint32_t super = idx / per_super;
+        const uint32_t first = super * p.raster;
+        const uint32_t in_super = idx - super * per_super;
+        const uint32_t rows = min(p.raster, num_m - first);
+        m_blk = first + in_super % rows;
+        n_blk = in_super / rows;
+    }
+
+    __device__ void load_group_m() {
+        if (p.gemm_type == kGemmMMasked) {
+            group_m_blocks = (layout(group) + bm - 1) / bm;
+        } else {  // psum
+            const uint32_t end = layout(group);
+            row_start = (prev_end + p.alignment - 1) / p.alignment * p.alignment;
+            group_m_blocks = end > row_start ? (end - row_start + bm - 1) / bm : 0;
+            prev_end = end;
+        }
+    }
+    __device__ void load_group_k() {
+        if (p.gemm_type == kGemmKGroupedPsum) {
+            const uint32_t end = layout(group);
+            k_start = (prev_end + p.alignment - 1) / p.alignment * p.alignment;
+            k_len = end - k_start;
+            prev_end = end;
+        } else {
+            k_len = layout(group);
+        }
+    }
+
+    __device__ bool next(uint32_t t, TileCoord& tc) {
+        tc.k_start = 0, tc.k_len = p.k, tc.sfk_base = 0, tc.group = 0;
+        const uint32_t num_n = p.num_n_blocks;
+        if (p.gemm_type == kGemmNormal || p.gemm_type == kGemmMContiguous) {
+            if (t >= p.num_m_blocks * num_n) return false;
+            swizzle(t, p.num_m_blocks, num_n, tc.m_blk, tc.n_blk);
+            if (p.gemm_type == kGemmMContiguous) {
+                const int32_t g = static_cast<int32_t>(layout(tc.m_blk * bm));
+                tc.group = g < 0 ? 0u : static_cast<uint32_t>(g);
+            }
+            return true;
+        }
+        if (p.gemm_type == kGemmMMasked || p.gemm_type == kGemmMPsum) {
+            if (!primed) {
+                primed = true;
+                load_group_m();
+            }
+            while (t >= (m_blk_cum + group_m_blocks) * num_n) {
+                if (++group >= p.num_groups) return false;
+                m_blk_cum += group_m_blocks;
+                load_group_m();
+            }
+            swizzle(t - m_blk_cum * num_n, group_m_blocks, num_n, tc.m_blk, tc.n_blk);
+            if (p.gemm_type == kGemmMPsum) tc.m_blk += row_start / bm;
+            tc.group = group;
+            return true;
+        }
+        // K-grouped: every group owns a full m x n tile grid and its own K range.
+        const uint32_t per_group = p.num_m_blocks * num_n;
+        if (!primed) {
+            primed = true;
+            load_group_k();
+        }
+        while (t >= (group + 1) * per_group) {
+            if (++group >= p.num_groups) return false;
+            const uint32_t aligned = (k_len + p.alignment - 1) / p.alignment * p.alignment;
+            sfk_base += (aligned + p.r.gran_k * 4 - 1) / (p.r.gran_k * 4);
+            if (p.gemm_type == kGemmKGrouped) k_start += k_len;
+            load_group_k();
+        }
+        if (group >= p.num_groups) return false;
+        swizzle(t - group * per_group, p.num_m_blocks, num_n, tc.m_blk, tc.n_blk);
+        tc.group = group, tc.k_start = k_start, tc.k_len = k_len, tc.sfk_base = sfk_base;
+        return true;
+    }
+};
+
+template <int kCtas_, int BN_, bool kSwap_, bool kCdF32_>
+struct GemmConfig {
+    static constexpr int kCtas = kCtas_;
+    static constexpr int BN = BN_;
+    static constexpr bool kSwap = kSwap_;
+    static constexpr bool kCdF32 = kCdF32_;
+    static_assert(!(kSwap && kCdF32), "the transposed epilogue writes BF16 only");
+    static_assert(BN % 16 == 0 && BN >= 32 && BN <= 256, "UMMA N");
+
+    static constexpr uint32_t kThreads = 256;
+    static constexpr uint32_t BLOCK_K = 128;
+    static constexpr uint32_t R_ROWS = 128;
+    static constexpr uint32_t C_ROWS_PER_CTA = BN / kCtas;
+    static constexpr uint32_t R_STAGE = R_ROWS * BLOCK_K;
+    static constexpr uint32_t C_STAGE = C_ROWS_PER_CTA * BLOCK_K;
+    static constexpr uint32_t SFC_ROWS = (BN + 127) / 128 * 128;
+    static constexpr uint32_t SFR_STAGE = 128 * 4;
+    static constexpr uint32_t SFC_STAGE = SFC_ROWS * 4;
+    static constexpr uint32_t STAGE_BYTES = R_STAGE + C_STAGE + SFR_STAGE + SFC_STAGE;
+
+    // Epilogue staging: each epilogue warp owns one slab per buffer and stores it by itself.
+    //   D tile:   32 rows x 128 B (64 BF16 or 32 FP32 columns), 128 B swizzle
+    //   D^T tile: 32 tokens x 32 BF16 (64 B rows), no swizzle
+    static constexpr uint32_t CHUNK_COLS = kSwap ? 32 : (kCdF32 ? 32 : 64);
+    static constexpr uint32_t SLAB_BYTES = kSwap ? 32 * 64 : 32 * 128;
+    static constexpr uint32_t kStoreBufs = (kCtas == 1 && BN == 256) ? 1 : 2;
+    static constexpr uint32_t CD_BYTES = kStoreBufs * 4 * SLAB_BYTES;
+
+    static constexpr uint32_t kSmemLimit = 232448;
+    static constexpr uint32_t kBarrierBytes = 1024;
+    static constexpr uint32_t kStagesRaw = (kSmemLimit - 1024 - CD_BYTES - kBarrierBytes) / STAGE_BYTES;
+    static constexpr uint32_t kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
+    static_assert(kStages >= 3, "pipeline too shallow");
+    static constexpr uint32_t kSmemBytes = 1024 + kStages * STAGE_BYTES + CD_BYTES + kBarrierBytes;
+
+    // TMEM columns: accumulator stages, then the scale factors of R (4) and C (BN / 32, >= 4).
+    static constexpr uint32_t SFC_COLS = SFC_ROWS / 32;
+    static constexpr uint32_t kAccStages = (2 * BN + 4 + SFC_COLS <= 512) ? 2 : 1;
+    static constexpr uint32_t kSfrCol = kAccStages * BN;
+    static constexpr uint32_t kSfcCol = kSfrCol + 4;
+    static constexpr uint32_t kUsedCols = kSfcCol + SFC_COLS;
+    static constexpr uint32_t kTmemCols = kUsedCols <= 32 ? 32 : kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128
+                                          : kUsedCols <= 256 ? 256 : 512;
+    static_assert(kUsedCols <= 512, "TMEM overflow");
+
+    // GEMM-level extents of the tile one unit (CTA or CTA pair) produces.
+    static constexpr uint32_t UNIT_M = kSwap ? BN : 128 * kCtas;
+    static constexpr uint32_t UNIT_N = kSwap ? 128 * kCtas : BN;
+};
+
+struct alignas(8) GemmBarriers {
+    uint64_t full[10];
+    uint64_t empty[10];
+    uint64_t sf_full[10];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort;
+};
+static_assert(sizeof(GemmBarriers) <= 1024, "barrier block");
+
+__device__ __noinline__ void report_timeout(const GemmParams& p, uint32_t site, uint32_t iter, uint32_t kb,
+                                            uint32_t stage) {
+    if (atomicCAS(p.status, kStatusOk, kStatusTimeout) == kStatusOk) {
+        p.status[1] = site;
+        p.status[2] = blockIdx.x;
+        p.status[3] = iter;
+        p.status[4] = kb;
+        p.status[5] = stage;
+        __threadfence_system();
+    }
+}
+
+// Bounded mbarrier wait.  Returns false if the CTA is aborting or the budget ran out.
+template <bool kClusterScope>
+DG_DEVICE bool wait_barrier(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t peer_abort_addr,
+                            const GemmParams& p, uint32_t site, uint32_t iter, uint32_t kb, uint32_t stage) {
+    auto poll = [&]() { return kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
+    if (poll()) return true;
+    const uint64_t t0 = global_timer_ns();
+    const uint64_t budget = static_cast<uint64_t>(p.timeout_ms) * 1000000ull;
+    uint32_t spins = 0;
+    while (true) {
+        if (poll()) return true;
+        if ((++spins & 15u) == 0) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > budget) {
+                report_timeout(p, site, iter, kb, stage);
+                *abort_flag = 1;
+                if (peer_abort_addr) st_cluster_u32(peer_abort_addr, 1);
+                return false;
+            }
+        }
+    }
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__ GemmParams p) {
+    constexpr int kCtas = Cfg::kCtas;
+    constexpr uint32_t BN = Cfg::BN;
+    constexpr uint32_t kStages = Cfg::kStages;
+    constexpr uint32_t kAccStages = Cfg::kAccStages;
+    constexpr bool kPair = kCtas == 2;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    // Carve-up: R stages | C stages | CD slabs (all 1024 B aligned: they are swizzled) | SFR | SFC | barriers
+    const uint32_t smem_r = smem_base;
+    const uint32_t smem_c = smem_r + kStages * Cfg::R_STAGE;
+    const uint32_t smem_cd = smem_c + kStages * Cfg::C_STAGE;
+    const uint32_t smem_sfr = smem_cd + Cfg::CD_BYTES;
+    const uint32_t smem_sfc = smem_sfr + kStages * Cfg::SFR_STAGE;
+    GemmBarriers* bars =
+        reinterpret_cast<GemmBarriers*>(smem_gen + (smem_sfc + kStages * Cfg::SFC_STAGE - smem_base));
+    uint32_t* sf_words_r = reinterpret_cast<uint32_t*>(smem_gen + (smem_sfr - smem_base));
+    uint32_t* sf_words_c = reinterpret_cast<uint32_t*>(smem_gen + (smem_sfc - smem_base));
+
+    const uint32_t warp = threadIdx.x / 32;
+    const uint32_t lane = threadIdx.x % 32;
+    const uint32_t cta_rank = kPair ? cluster_ctarank() : 0;
+    const bool is_leader = cta_rank == 0;
+    const uint32_t unit = kPair ? blockIdx.x / 2 : blockIdx.x;
+    volatile uint32_t* abort_flag = &bars->abort;
+    const uint32_t peer_abort = kPair ? map_to_cta(smem_u32(&bars->abort), cta_rank ^ 1) : 0;
+
+    // ---------------------------------------------------------------- set-up
+    if (warp == 0 && lane == 0) {
+        prefetch_tmap(&p.tm_r);
+        prefetch_tmap(&p.tm_c);
+        prefetch_tmap(&p.tm_sfr);
+        prefetch_tmap(&p.tm_sfc);
+        prefetch_tmap(&p.tm_d);
+        for (uint32_t i = 0; i < kStages; ++i) {
+            mbar_init(&bars->full[i], kCtas * 2);   // per CTA: producer + transposer
+            mbar_init(&bars->empty[i], 1);          // UMMA commit
+            mbar_init(&bars->sf_full[i], 1);        // producer (SF copies land here)
+        }
+        for (uint32_t i = 0; i < 2; ++i) {
+            mbar_init(&bars->tmem_full[i], 1);            // UMMA commit
+            mbar_init(&bars->tmem_empty[i], kCtas * 4);   // one lane per epilogue warp
+        }
+        bars->abort = 0;
+        fence_mbar_init();
+    }
+    if (kPair) cluster_sync();   // both CTAs exist before the paired TMEM allocation
+    if (warp == 1) {
+        tmem_alloc<kCtas>(&bars->tmem_base, Cfg::kTmemCols);
+        tmem_relinquish<kCtas>();
+    }
+    tc_fence_before();
+    if (kPair) cluster_sync(); else __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+    // Barrier addresses in the leader CTA (own CTA when not paired)
+    auto leader_addr = [&](uint64_t* bar) -> uint32_t {
+        return kPair ? map_to_cta(smem_u32(bar), 0) : smem_u32(bar);
+    };
+
+    const uint32_t first_k_block_words_r = p.r.gran_k == 128 ? 4 : 1;   // k-blocks covered by one SF word
+    const uint32_t first_k_block_words_c = p.c.gran_k == 128 ? 4 : 1;
+
+    // Role loops share: tile iteration, stage / phase bookkeeping.
+    uint32_t stage = 0, phase = 0;
+    auto advance = [&]() {
+        stage = stage + 1 == kStages ? 0 : stage + 1;
+        phase ^= (stage == 0);
+    };
+
+    if (warp == 0) {
+        // ============================================================ TMA producer
+        if (lane == 0) {
+            TileWalker walker(p, Cfg::UNIT_M, Cfg::UNIT_N);
+            TileCoord tc;
+            bool ok = true;
+            for (uint32_t iter = 0; ok && walker.next(iter * p.num_units + unit, tc); ++iter) {
+                // Operand coordinates of this tile (GEMM A / B, then mapped to R / C)
+                const uint32_t a_blk_rows = Cfg::kSwap ? BN : 128 * kCtas;
+                const uint32_t b_blk_rows = Cfg::kSwap ? 128 * kCtas : BN;
+                uint32_t a_mn = tc.m_blk * a_blk_rows, b_mn = tc.n_blk * b_blk_rows;
+                uint32_t a_k = tc.k_start, b_k = tc.k_start;
+                uint32_t sfa_k = tc.sfk_base, sfb_k = tc.sfk_base;
+                const OperandParams& pa = Cfg::kSwap ? p.c : p.r;
+                const OperandParams& pb = Cfg::kSwap ? p.r : p.c;
+                const uint32_t rpg_a = Cfg::kSwap ? p.rows_per_group_c : p.rows_per_group_r;
+                const uint32_t rpg_b = Cfg::kSwap ? p.rows_per_group_r : p.rows_per_group_c;
+                const uint32_t kpg_a = Cfg::kSwap ? p.k_rows_per_group_c : p.k_rows_per_group_r;
+                const uint32_t kpg_b = Cfg::kSwap ? p.k_rows_per_group_r : p.k_rows_per_group_c;
+                const uint32_t sfg_a = Cfg::kSwap ? p.sf_groups_c : p.sf_groups_r;
+                const uint32_t sfg_b = Cfg::kSwap ? p.sf_groups_r : p.sf_groups_c;
+                a_mn += tc.group * rpg_a, a_k += tc.group * kpg_a, sfa_k += tc.group * sfg_a;
+                b_mn += tc.group * rpg_b, b_k += tc.group * kpg_b, sfb_k += tc.group * sfg_b;
+                // SF rows are addressed inside the group (the group offset is on the packed-K axis)
+                const uint32_t sfa_mn = tc.m_blk * a_blk_rows, sfb_mn = tc.n_blk * b_blk_rows;
+
+                uint32_t r_mn = Cfg::kSwap ? b_mn : a_mn, c_mn = Cfg::kSwap ? a_mn : b_mn;
+                const uint32_t r_k = Cfg::kSwap ? b_k : a_k, c_k = Cfg::kSwap ? a_k : b_k;
+                uint32_t sfr_mn = Cfg::kSwap ? sfb_mn : sfa_mn;
+                const uint32_t sfc_mn = Cfg::kSwap ? sfa_mn : sfb_mn;
+                const uint32_t sfr_k = Cfg::kSwap ? sfb_k : sfa_k, sfc_k = Cfg::kSwap ? sfa_k : sfb_k;
+                // This CTA's share: its own 128 R rows, its half of the C rows
+                r_mn += cta_rank * 128, sfr_mn += cta_rank * 128;
+                c_mn += cta_rank * Cfg::C_ROWS_PER_CTA;
+                (void)pa, (void)pb;
+
+                const uint32_t num_kb = max(1u, (tc.k_len + 127u) / 128u);
+                for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
+                    ok = wait_barrier<false>(&bars->empty[stage], phase ^ 1, abort_flag, peer_abort, p,
+                                             kSiteProducerEmpty, iter, kb, stage);
+                    if (!ok) break;
+                    // Scale factors first: the transposer works while the operand tiles are in flight
+                    uint32_t sf_bytes = 0;
+                    const uint32_t sf_bar = smem_u32(&bars->sf_full[stage]);
+                    if (kb % first_k_block_words_r == 0) {
+                        tma_load_2d<false>(smem_sfr + stage * Cfg::SFR_STAGE, &p.tm_sfr, sf_bar,
+                                           static_cast<int32_t>(sfr_mn),
+                                           static_cast<int32_t>(sfr_k + kb / first_k_block_words_r));
+                        sf_bytes += Cfg::SFR_STAGE;
+                    }
+                    if (kb % first_k_block_words_c == 0) {
+                        tma_load_2d<false>(smem_sfc + stage * Cfg::SFC_STAGE, &p.tm_sfc, sf_bar,
+                                           static_cast<int32_t>(sfc_mn),
+                                           static_cast<int32_t>(sfc_k + kb / first_k_block_words_c));
+                        sf_bytes += Cfg::SFC_STAGE;
+                    }
+                    mbar_arrive_expect_tx(&bars->sf_full[stage], sf_bytes);
+
+                    // Operand tiles land on the leader's barrier (both CTAs of a pair feed one UMMA)
+                    const uint32_t full_bar = leader_addr(&bars->full[stage]);
+                    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(
+                                     full_bar),
+                                 "r"(p.r.tx_bytes + p.c.tx_bytes)
+                                 : "memory");
+                    const uint32_t kr = r_k + kb * 128, kc = c_k + kb * 128;
+                    for (uint32_t b = 0; b < p.r.num_boxes; ++b) {
+                        const uint32_t dst = smem_r + stage * Cfg::R_STAGE + b * p.r.box_bytes;
+                        const uint32_t mn = r_mn + b * p.r.box_mn;
+                        if (p.r.mn_major) tma_load_2d<kPair>(dst, &p.tm_r, full_bar, mn, kr);
+                        else              tma_load_2d<kPair>(dst, &p.tm_r, full_bar, kr, mn);
+                    }
+                    for (uint32_t b = 0; b < p.c.num_boxes; ++b) {
+                        const uint32_t dst = smem_c + stage * Cfg::C_STAGE + b * p.c.box_bytes;
+                        const uint32_t mn = c_mn + b * p.c.box_mn;
+                        if (p.c.mn_major) tma_load_2d<kPair>(dst, &p.tm_c, full_bar, mn, kc);
+                        else              tma_load_2d<kPair>(dst, &p.tm_c, full_bar, kc, mn);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ============================================================ UMMA issuer (leader CTA only)
+        if (is_leader && lane == 0) {
+            TileWalker walker(p, Cfg::UNIT_M, Cfg::UNIT_N);
+            TileCoord tc;
+            bool ok = true;
+            const uint32_t idesc_base = make_idesc_mxf8f6f4(p.r.fmt, p.c.fmt, p.r.mn_major != 0, p.c.mn_major != 0,
+                                                            128 * kCtas, BN);
+            const uint64_t sf_desc_hi = make_smem_desc(0, 0, 128, kSwizzleNone);
+            for (uint32_t iter = 0; ok && walker.next(iter * p.num_units + unit, tc); ++iter) {
+                const uint32_t acc = iter % kAccStages;
+                const uint32_t acc_phase = (iter / kAccStages) & 1;
+                ok = wait_barrier<kPair>(&bars->tmem_empty[acc], acc_phase ^ 1, abort_flag, peer_abort, p,
+                                         kSiteMmaTmemEmpty, iter, 0, acc);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                const uint32_t num_kb = max(1u, (tc.k_len + 127u) / 128u);
+                for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
+                    ok = wait_barrier<kPair>(&bars->full[stage], phase, abort_flag, peer_abort, p, kSiteMmaFull, iter,
+                                             kb, stage);
+                    if (!ok) break;
+                    tc_fence_after();
+                    // Fresh scale factors: shared memory (already in 32x4 order) -> TMEM
+                    if (kb % first_k_block_words_r == 0) {
+                        const uint32_t a = smem_sfr + stage * Cfg::SFR_STAGE;
+                        utccp_32x128b_warpx4<kCtas>(tmem_base + Cfg::kSfrCol, sf_desc_hi | ((a >> 4) & 0x3FFF));
+                    }
+                    if (kb % first_k_block_words_c == 0) {
+#pragma unroll
+                        for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i) {
+                            const uint32_t a = smem_sfc + stage * Cfg::SFC_STAGE + i * 512;
+                            utccp_32x128b_warpx4<kCtas>(tmem_base + Cfg::kSfcCol + i * 4,
+                                                        sf_desc_hi | ((a >> 4) & 0x3FFF));
+                        }
+                    }
+                    const uint64_t r_desc = make_smem_desc(smem_r + stage * Cfg::R_STAGE, p.r.desc_lbo, p.r.desc_sbo,
+                                                           kSwizzle128B);
+                    const uint64_t c_desc = make_smem_desc(smem_c + stage * Cfg::C_STAGE, p.c.desc_lbo, p.c.desc_sbo,
+                                                           kSwizzle128B);
+#pragma unroll
+                    for (uint32_t ks = 0; ks < 4; ++ks) {
+                        const uint32_t id_r = p.r.gran_k == 32 ? ks : (kb & 3);
+                        const uint32_t id_c = p.c.gran_k == 32 ? ks : (kb & 3);
+                        umma_mxf8f6f4<kCtas>(d_tmem, r_desc + ((ks * p.r.desc_kstep) >> 4),
+                                             c_desc + ((ks * p.c.desc_kstep) >> 4),
+                                             idesc_with_sf_ids(idesc_base, id_r, id_c), tmem_base + Cfg::kSfrCol,
+                                             tmem_base + Cfg::kSfcCol, (kb | ks) != 0);
+                    }
+                    umma_commit<kCtas>(&bars->empty[stage]);   // frees the stage (in both CTAs)
+                    if (kb + 1 == num_kb) umma_commit<kCtas>(&bars->tmem_full[acc]);
+                }
+            }
+        }
+    } else if (warp == 2) {
+        // ============================================================ scale-factor transposer
+        // tcgen05.cp 32x128b.warpx4 wants, per 128 rows, row i's word at position (i % 32) * 4 + i / 32.
+        TileWalker walker(p, Cfg::UNIT_M, Cfg::UNIT_N);
+        TileCoord tc;
+        bool ok = true;
+        const uint32_t full_bar = leader_addr(&bars->full[0]);
+        for (uint32_t iter = 0; ok && walker.next(iter * p.num_units + unit, tc); ++iter) {
+            const uint32_t num_kb = max(1u, (tc.k_len + 127u) / 128u);
+            for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
+                ok = wait_barrier<false>(&bars->sf_full[stage], phase, abort_flag, peer_abort, p,
+                                         kSiteTransposerSfFull, iter, kb, stage);
+                if (!ok) break;
+                auto transpose_128 = [&](uint32_t* w) {
+                    uint32_t v0 = w[lane], v1 = w[32 + lane], v2 = w[64 + lane], v3 = w[96 + lane];
+                    __syncwarp();
+                    reinterpret_cast<uint4*>(w)[lane] = make_uint4(v0, v1, v2, v3);
+                };
+                if (kb % first_k_block_words_r == 0) transpose_128(sf_words_r + stage * 128);
+                if (kb % first_k_block_words_c == 0) {
+#pragma unroll
+                    for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i)
+                        transpose_128(sf_words_c + stage * Cfg::SFC_ROWS + i * 128);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(full_bar + stage * 8);
+            }
+        }
+    } else if (warp >= 4) {
+        // ============================================================ epilogue
+        const uint32_t q = warp - 4;   // TMEM lane quadrant == warp % 4
+        TileWalker walker(p, Cfg::UNIT_M, Cfg::UNIT_N);
+        TileCoord tc;
+        bool ok = true;
+        const uint32_t tmem_empty_bar = leader_addr(&bars->tmem_empty[0]);
+        const uint32_t slab0 = smem_cd + q * Cfg::SLAB_BYTES;
+        uint8_t* slab0_gen = smem_gen + (slab0 - smem_base);
+        uint32_t buf = 0;
+        for (uint32_t iter = 0; ok && walker.next(iter * p.num_units + unit, tc); ++iter) {
+            const uint32_t acc = iter % kAccStages;
+            const uint32_t acc_phase = (iter / kAccStages) & 1;
+            ok = wait_barrier<false>(&bars->tmem_full[acc], acc_phase, abort_flag, peer_abort, p,
+                                     kSiteEpilogueTmemFull, iter, 0, acc);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_acc = tmem_base + acc * BN + ((q * 32) << 16);
+            // Where this warp's 32 lanes land in D
+            //   D tile  : rows m0 + q*32 .. +31, columns n0 + chunk
+            //   D^T tile: columns n0 + q*32 .. +31 (lanes), rows m0 + chunk (TMEM columns)
+            const uint32_t m0 = tc.m_blk * Cfg::UNIT_M + (Cfg::kSwap ? 0 : cta_rank * 128);
+            const uint32_t n0 = tc.n_blk * Cfg::UNIT_N + (Cfg::kSwap ? cta_rank * 128 : 0);
+            constexpr uint32_t kChunks = BN / Cfg::CHUNK_COLS;
+#pragma unroll 1
+            for (uint32_t ch = 0; ch < kChunks; ++ch) {
+                uint32_t v[Cfg::CHUNK_COLS];
+#pragma unroll
+                for (uint32_t i = 0; i < Cfg::CHUNK_COLS / 32; ++i)
+                    tmem_ld_32x32b_x32(t_acc + ch * Cfg::CHUNK_COLS + i * 32, v + i * 32);
+                tmem_ld_wait();
+                if (ch + 1 == kChunks) {
+                    // Accumulator is in registers: hand the TMEM stage back to the UMMA issuer
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(tmem_empty_bar + acc * 8);
+                }
+                // The slab we are about to overwrite must have been read by its previous store
+                if (lane == 0) tma_store_wait_read<Cfg::kStoreBufs - 1>();
+                __syncwarp();
+                const uint32_t slab = slab0 + buf * 4 * Cfg::SLAB_BYTES;
+                uint8_t* slab_gen = slab0_gen + buf * 4 * Cfg::SLAB_BYTES;
+                if constexpr (!Cfg::kSwap) {
+                    // Row `lane` of the slab: 128 B, 16 B chunks XOR-swizzled by (row % 8)
+                    uint4* row = reinterpret_cast<uint4*>(slab_gen + lane * 128);
+                    if constexpr (Cfg::kCdF32) {
+#pragma unroll
+                        for (uint32_t c16 = 0; c16 < 8; ++c16) {
+                            float4 f;
+                            f.x = __uint_as_float(v[c16 * 4 + 0]) * p.alpha;
+                            f.y = __uint_as_float(v[c16 * 4 + 1]) * p.alpha;
+                            f.z = __uint_as_float(v[c16 * 4 + 2]) * p.alpha;
+                            f.w = __uint_as_float(v[c16 * 4 + 3]) * p.alpha;
+                            reinterpret_cast<float4*>(row)[c16 ^ (lane & 7)] = f;
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t c16 = 0; c16 < 8; ++c16) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (uint32_t j = 0; j < 4; ++j) {
+                                const float lo = __uint_as_float(v[c16 * 8 + j * 2]) * p.alpha;
+                                const float hi = __uint_as_float(v[c16 * 8 + j * 2 + 1]) * p.alpha;
+                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+                                w[j] = *reinterpret_cast<const uint32_t*>(&b2);
+                            }
+                            row[c16 ^ (lane & 7)] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                } else {
+                    // D^T: lane holds column n0 + q*32 + lane for 32 tokens; slab is [token][32 n] BF16
+                    __nv_bfloat16* s = reinterpret_cast<__nv_bfloat16*>(slab_gen);
+#pragma unroll
+                    for (uint32_t t = 0; t < 32; ++t)
+                        s[t * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[t]) * p.alpha);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    int32_t cn, cm;
+                    if constexpr (!Cfg::kSwap) {
+                        cn = static_cast<int32_t>(n0 + ch * Cfg::CHUNK_COLS);
+                        cm = static_cast<int32_t>(m0 + q * 32);
+                    } else {
+                        cn = static_cast<int32_t>(n0 + q * 32);
+                        cm = static_cast<int32_t>(m0 + ch * 32);
+                    }
+                    const int32_t cg = p.d_grouped ? static_cast<int32_t>(tc.group) : 0;
+                    if (p.accumulate) tma_reduce_add_3d(&p.tm_d, slab, cn, cm, cg);
+                    else              tma_store_3d(&p.tm_d, slab, cn, cm, cg);
+                    tma_store_commit();
+                }
+                buf = buf + 1 == Cfg::kStoreBufs ? 0 : buf + 1;
+            }
+        }
+        if (lane == 0) tma_store_wait<0>();
+    }
+
+    // ---------------------------------------------------------------- tear-down
+    if (*abort_flag) {
+        // Copies issued before the abort may still be landing in this CTA's shared memory
+        for (int i = 0; i < 20; ++i) __nanosleep(10000);
+    }
+    __syncwarp();
+    tc_fence_before();
+    if (kPair) cluster_sync(); else __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<kCtas>(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+}  // namespace dg

@@ -1,0 +1,500 @@
+// Host side of libdeepgemm_b200.so: argument checks, tile selection, tensor-map encoding and
+// launches behind the C ABI declared in include/deepgemm_b200.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+
+#include "../../include/deepgemm_b200.h"
+#include "gemm_bs.cuh"
+#include "sf_pack.cuh"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+#define DG_REQUIRE(cond, ...)                                                          \
+    do {                                                                               \
+        if (!(cond)) return fail(DG_ERR_INVALID, "Assertion failed: " #cond " (" __VA_ARGS__ ")"); \
+    } while (0)
+
+#define DG_CUDA(call)                                                                                   \
+    do {                                                                                                \
+        cudaError_t e_ = (call);                                                                        \
+        if (e_ != cudaSuccess) return fail(DG_ERR_CUDA, "CUDA error: %s at %s", cudaGetErrorString(e_), #call); \
+    } while (0)
+
+// Device status block the kernels report abandoned waits into (one per device, zero at load).
+__device__ uint32_t g_status[16];
+
+struct Knobs {
+    std::mutex mu;
+    int num_sms = 0;        // 0: use the device's count
+    int tc_util = 100;
+    int mk_alignment = 128;
+    int timeout_ms = 2000;
+} g_knobs;
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+int encode_tmap(CUtensorMap* tm, CUtensorMapDataType dtype, uint32_t rank, const void* base, const uint64_t* dims,
+                const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle, const char* what) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (fn == nullptr) return fail(DG_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t gdims[5];
+    cuuint64_t gstrides[4];
+    cuuint32_t bdims[5], estr[5];
+    for (uint32_t i = 0; i < rank; ++i) gdims[i] = dims[i], bdims[i] = box[i], estr[i] = 1;
+    for (uint32_t i = 0; i + 1 < rank; ++i) gstrides[i] = strides_bytes[i];
+    if (reinterpret_cast<uintptr_t>(base) % 16 != 0)
+        return fail(DG_ERR_INVALID, "Assertion failed: %s base address is 16-byte aligned", what);
+    for (uint32_t i = 0; i + 1 < rank; ++i)
+        if (gstrides[i] % 16 != 0)
+            return fail(DG_ERR_INVALID, "Assertion failed: %s stride %llu bytes is a multiple of 16", what,
+                        static_cast<unsigned long long>(gstrides[i]));
+    CUresult r = fn(tm, dtype, rank, const_cast<void*>(base), gdims, gstrides, bdims, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(DG_ERR_CUDA,
+                    "cuTensorMapEncodeTiled(%s) failed with %d (rank %u dims %llu,%llu,%llu box %u,%u,%u)", what,
+                    static_cast<int>(r), rank, static_cast<unsigned long long>(dims[0]),
+                    static_cast<unsigned long long>(rank > 1 ? dims[1] : 0),
+                    static_cast<unsigned long long>(rank > 2 ? dims[2] : 0), box[0], rank > 1 ? box[1] : 0,
+                    rank > 2 ? box[2] : 0);
+    return DG_OK;
+}
+
+int device_sm_count(int* out) {
+    static int cached[64] = {0};
+    int dev = 0;
+    DG_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && cached[dev] != 0) {
+        *out = cached[dev];
+        return DG_OK;
+    }
+    int n = 0;
+    DG_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    if (dev < 64) cached[dev] = n;
+    *out = n;
+    return DG_OK;
+}
+
+// --------------------------------------------------------------------------- GEMM launch
+struct TileChoice {
+    int ctas, bn;
+    bool swap;
+};
+
+template <class Cfg>
+int launch_gemm(dg::GemmParams& p, const dg_gemm_args& a, uint32_t num_units) {
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    // The attribute is per device; set it on every call (cheap) so that multi-device processes work.
+    attr_err = cudaFuncSetAttribute(dg::gemm_bs_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(Cfg::kSmemBytes));
+    (void)once;
+    if (attr_err != cudaSuccess)
+        return fail(DG_ERR_CUDA, "CUDA error: %s setting %u bytes of dynamic shared memory",
+                    cudaGetErrorString(attr_err), Cfg::kSmemBytes);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(num_units * Cfg::kCtas, 1, 1);
+    cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = static_cast<cudaStream_t>(a.stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = Cfg::kCtas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DG_CUDA(cudaLaunchKernelEx(&cfg, dg::gemm_bs_kernel<Cfg>, p));
+    return DG_OK;
+}
+
+struct OperandPlan {
+    CUtensorMap tm, tm_sf;
+    dg::OperandParams params;
+    uint32_t rows_per_group, k_rows_per_group, sf_groups;
+};
+
+// Build the tensor maps and kernel parameters of one GEMM operand in the role of R (128 rows per
+// CTA) or C (`box_rows` rows per CTA).
+int plan_operand(const dg_gemm_args& a, const dg_operand& op, bool is_a, uint32_t box_rows, uint32_t sf_box_rows,
+                 OperandPlan* out) {
+    const uint32_t mn = is_a ? a.m : a.n;
+    const bool fp4 = op.dtype == DG_E2M1_PACKED;
+    const bool k_grouped = a.gemm_type == DG_GEMM_K_GROUPED || a.gemm_type == DG_GEMM_K_GROUPED_PSUM;
+    const bool m_grouped = a.gemm_type == DG_GEMM_M_CONTIGUOUS || a.gemm_type == DG_GEMM_M_PSUM ||
+                           a.gemm_type == DG_GEMM_M_MASKED;
+    // Which operands carry a group axis
+    uint32_t groups = 1;
+    if (a.gemm_type == DG_GEMM_M_MASKED) groups = a.num_groups;
+    if ((a.gemm_type == DG_GEMM_M_CONTIGUOUS || a.gemm_type == DG_GEMM_M_PSUM) && !is_a) groups = a.num_groups;
+    (void)m_grouped;
+    dg::OperandParams& q = out->params;
+    memset(&q, 0, sizeof(q));
+    q.gran_k = op.gran_k;
+    q.fmt = fp4 ? dg::kFmtE2M1 : dg::kFmtE4M3;
+    q.mn_major = op.mn_major ? 1 : 0;
+    out->rows_per_group = out->k_rows_per_group = out->sf_groups = 0;
+    const char* name = is_a ? "a" : "b";
+    int rc;
+    if (!op.mn_major) {
+        // [groups * mn, k] with K contiguous
+        const uint64_t dims[2] = {static_cast<uint64_t>(a.k), static_cast<uint64_t>(mn) * groups};
+        const uint64_t strides[1] = {static_cast<uint64_t>(op.ld)};
+        const uint32_t box[2] = {128, box_rows};
+        rc = encode_tmap(&out->tm, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                         op.data, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, name);
+        if (rc != DG_OK) return rc;
+        q.num_boxes = 1;
+        q.box_bytes = box_rows * 128;
+        q.box_mn = box_rows;
+        q.tx_bytes = box_rows * 128 / (fp4 ? 2 : 1);
+        q.desc_lbo = 0, q.desc_sbo = 1024, q.desc_kstep = 32;
+        if (groups > 1) out->rows_per_group = mn;
+    } else {
+        // [groups * k, mn] with MN contiguous (E4M3 only)
+        if (fp4) return fail(DG_ERR_INVALID, "Assertion failed: packed FP4 operands are K-major (%s)", name);
+        if (box_rows % 128 != 0)
+            return fail(DG_ERR_INVALID, "Assertion failed: MN-major %s needs a tile of whole 128-row atoms", name);
+        const uint64_t k_rows = k_grouped ? static_cast<uint64_t>(a.k) : static_cast<uint64_t>(a.k) * groups;
+        const uint64_t dims[2] = {static_cast<uint64_t>(mn), k_rows};
+        const uint64_t strides[1] = {static_cast<uint64_t>(op.ld)};
+        const uint32_t box[2] = {128, 128};
+        rc = encode_tmap(&out->tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, op.data, dims, strides, box,
+                         CU_TENSOR_MAP_SWIZZLE_128B, name);
+        if (rc != DG_OK) return rc;
+        q.num_boxes = box_rows / 128;
+        q.box_bytes = 128 * 128;
+        q.box_mn = 128;
+        q.tx_bytes = box_rows * 128;
+        q.desc_lbo = 128 * 128, q.desc_sbo = 1024, q.desc_kstep = 32 * 128;
+        if (groups > 1) out->k_rows_per_group = a.k;
+    }
+    // Scale factors: int32 [groups * packed_k, mn] seen with MN innermost
+    uint64_t packed_k;
+    if (k_grouped) {
+        // Upper bound of the packed rows actually present: every group may round up once
+        packed_k = (static_cast<uint64_t>(a.k) / op.gran_k + 3 * static_cast<uint64_t>(a.num_groups)) / 4 + 1;
+    } else {
+        packed_k = (static_cast<uint64_t>(a.k) + op.gran_k * 4 - 1) / (op.gran_k * 4);
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(mn), packed_k * groups};
+        const uint64_t strides[1] = {static_cast<uint64_t>(op.sf_ld) * 4};
+        const uint32_t box[2] = {sf_box_rows, 1};
+        rc = encode_tmap(&out->tm_sf, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, op.sf, dims, strides, box,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, is_a ? "sfa" : "sfb");
+        if (rc != DG_OK) return rc;
+        if (groups > 1) out->sf_groups = static_cast<uint32_t>(packed_k);
+    }
+    return DG_OK;
+}
+
+int choose_tile(const dg_gemm_args& a, int num_sms, TileChoice* t) {
+    const bool m_grouped = a.gemm_type == DG_GEMM_M_CONTIGUOUS || a.gemm_type == DG_GEMM_M_PSUM ||
+                           a.gemm_type == DG_GEMM_M_MASKED;
+    const bool k_grouped = a.gemm_type == DG_GEMM_K_GROUPED || a.gemm_type == DG_GEMM_K_GROUPED_PSUM;
+    TileChoice c;
+    if (m_grouped) {
+        // Tokens on the UMMA N axis: a CTA pair shares one token block of any expert.
+        c.swap = true;
+        c.bn = 128;
+        if (a.gemm_type == DG_GEMM_M_MASKED && a.expected_m > 0 && a.expected_m <= 64) c.bn = 64;
+        c.ctas = (a.n % 256 == 0 && num_sms % 2 == 0) ? 2 : 1;
+    } else if (k_grouped) {
+        c.swap = false;
+        c.bn = a.n % 256 == 0 ? 256 : 128;
+        c.ctas = (a.m % 256 == 0 && c.bn == 256 && num_sms % 2 == 0) ? 2 : 1;
+    } else {
+        c.swap = false;
+        const bool mn_major_b = a.b.mn_major != 0;
+        c.ctas = (a.m > 128 && num_sms % 2 == 0) ? 2 : 1;
+        c.bn = a.n >= 256 ? 256 : 128;
+        if (c.ctas == 2 && c.bn == 128 && mn_major_b) c.ctas = 1;   // half tiles of an MN-major B need 128 rows
+        if (a.d_dtype == DG_F32 && false) c.bn = 128;
+    }
+    if (a.force_cta_group) c.ctas = a.force_cta_group;
+    if (a.force_block_n) c.bn = a.force_block_n;
+    if (a.force_swap) c.swap = a.force_swap == 2;
+    *t = c;
+    return DG_OK;
+}
+
+uint32_t choose_raster(uint32_t num_m_blocks, uint32_t unit_m, uint32_t unit_n, uint32_t units) {
+    uint32_t best = 1;
+    uint64_t best_cost = ~0ull;
+    for (uint32_t cand : {1u, 2u, 4u, 8u, 16u, 32u}) {
+        if (cand > num_m_blocks && cand != 1) continue;
+        const uint64_t cost = static_cast<uint64_t>(cand) * unit_m + static_cast<uint64_t>((units + cand - 1) / cand) * unit_n;
+        if (cost < best_cost) best_cost = cost, best = cand;
+    }
+    return best;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* dg_last_error(void) { return g_last_error.c_str(); }
+const char* dg_version(void) { return "deepgemm_b200 0.1 (sm_100a)"; }
+
+int dg_set_num_sms(int32_t n) {
+    DG_REQUIRE(n >= 0, "num_sms");
+    std::lock_guard<std::mutex> lk(g_knobs.mu);
+    g_knobs.num_sms = n;
+    return DG_OK;
+}
+int dg_get_num_sms(void) {
+    {
+        std::lock_guard<std::mutex> lk(g_knobs.mu);
+        if (g_knobs.num_sms > 0) return g_knobs.num_sms;
+    }
+    int n = 0;
+    if (device_sm_count(&n) != DG_OK) return -1;
+    return n;
+}
+int dg_set_tc_util(int32_t v) {
+    DG_REQUIRE(v >= 0 && v <= 100, "tc_util");
+    std::lock_guard<std::mutex> lk(g_knobs.mu);
+    g_knobs.tc_util = v;
+    return DG_OK;
+}
+int dg_get_tc_util(void) {
+    std::lock_guard<std::mutex> lk(g_knobs.mu);
+    return g_knobs.tc_util;
+}
+int dg_set_mk_alignment_for_contiguous_layout(int32_t v) {
+    DG_REQUIRE(v > 0 && v % 16 == 0, "alignment");
+    std::lock_guard<std::mutex> lk(g_knobs.mu);
+    g_knobs.mk_alignment = v;
+    return DG_OK;
+}
+int dg_get_mk_alignment_for_contiguous_layout(void) {
+    std::lock_guard<std::mutex> lk(g_knobs.mu);
+    return g_knobs.mk_alignment;
+}
+int dg_get_theoretical_mk_alignment_for_contiguous_layout(int32_t expected_m) {
+    (void)expected_m;
+    return 128;
+}
+int dg_set_wait_timeout_ms(int32_t ms) {
+    DG_REQUIRE(ms > 0, "timeout");
+    std::lock_guard<std::mutex> lk(g_knobs.mu);
+    g_knobs.timeout_ms = ms;
+    return DG_OK;
+}
+
+int dg_check_status(uint32_t info[8]) {
+    uint32_t host[16];
+    DG_CUDA(cudaDeviceSynchronize());
+    DG_CUDA(cudaMemcpyFromSymbol(host, g_status, sizeof(host)));
+    if (info != nullptr) memcpy(info, host, 8 * sizeof(uint32_t));
+    if (host[0] == dg::kStatusOk) return DG_OK;
+    uint32_t zero[16] = {0};
+    DG_CUDA(cudaMemcpyToSymbol(g_status, zero, sizeof(zero)));
+    return fail(DG_ERR_DEVICE,
+                "a kernel abandoned a bounded wait: code %u site %u block %u tile-iteration %u k-block %u stage %u",
+                host[0], host[1], host[2], host[3], host[4], host[5]);
+}
+
+int dg_sf_pack_ue8m0(const float* sf, int32_t* out, int32_t num_batches, int32_t mn, int32_t sf_k, int32_t gran_mn,
+                     int64_t stride_b, int64_t stride_mn, int64_t stride_k, const int32_t* psum_layout,
+                     int32_t num_psum_groups, int32_t psum_alignment, void* stream) {
+    DG_REQUIRE(sf != nullptr && out != nullptr, "sf/out");
+    DG_REQUIRE(num_batches >= 0 && mn >= 0 && sf_k >= 0 && gran_mn >= 1, "shape");
+    if (num_batches == 0 || mn == 0 || sf_k == 0) return DG_OK;
+    DG_REQUIRE(psum_layout == nullptr || (num_psum_groups > 0 && psum_alignment > 0), "psum_layout");
+    dg::SfPackParams p;
+    p.sf = sf, p.out = out, p.mn = mn, p.sf_k = sf_k;
+    p.packed_k = (sf_k + 3) / 4;
+    p.aligned_mn = (mn + 3) / 4 * 4;
+    p.gran_mn = gran_mn;
+    p.stride_b = stride_b, p.stride_mn = stride_mn, p.stride_k = stride_k;
+    p.psum_layout = psum_layout, p.num_psum_groups = num_psum_groups, p.psum_alignment = psum_alignment;
+    DG_REQUIRE(num_batches <= 65535 && (p.packed_k + 31) / 32 <= 65535, "grid");
+    dim3 grid((mn + 31) / 32, (p.packed_k + 31) / 32, num_batches);
+    dg::sf_pack_ue8m0_kernel<<<grid, dim3(32, 8, 1), 0, static_cast<cudaStream_t>(stream)>>>(p);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+int dg_sf_pack_ue8m0_k_grouped(const float* sf, int32_t* out, const int32_t* grouped_layout, int32_t num_groups,
+                               int32_t mn, int32_t sf_k_rows, int32_t packed_rows, int32_t gran_k, int32_t k_alignment,
+                               int32_t use_psum, void* stream) {
+    DG_REQUIRE(sf != nullptr && out != nullptr && grouped_layout != nullptr, "pointers");
+    DG_REQUIRE(gran_k == 32 || gran_k == 128, "gran_k");
+    DG_REQUIRE(k_alignment > 0 && k_alignment % 128 == 0, "k_alignment");
+    if (packed_rows == 0 || mn == 0) return DG_OK;
+    DG_REQUIRE(packed_rows <= 65535, "grid");
+    dg::SfPackKGroupedParams p;
+    p.sf = sf, p.out = out, p.grouped_layout = grouped_layout, p.num_groups = num_groups, p.mn = mn;
+    p.sf_k_rows = sf_k_rows, p.packed_rows = packed_rows, p.gran_k = gran_k, p.k_alignment = k_alignment;
+    p.use_psum = use_psum;
+    dim3 grid((mn + 255) / 256, packed_rows, 1);
+    dg::sf_pack_ue8m0_k_grouped_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+int dg_gemm_bs(const dg_gemm_args* args) {
+    DG_REQUIRE(args != nullptr, "args");
+    const dg_gemm_args& a = *args;
+    DG_REQUIRE(a.gemm_type >= DG_GEMM_NORMAL && a.gemm_type <= DG_GEMM_K_GROUPED_PSUM, "gemm_type");
+    DG_REQUIRE(a.m >= 0 && a.n >= 0 && a.k >= 0, "shape");
+    if (a.m == 0 || a.n == 0) return DG_OK;
+    DG_REQUIRE(a.k > 0, "k == 0 is handled by the caller");
+    DG_REQUIRE(a.a.data && a.b.data && a.a.sf && a.b.sf && a.d, "null tensor");
+    DG_REQUIRE(a.a.dtype == DG_E4M3 || a.a.dtype == DG_E2M1_PACKED, "a dtype");
+    DG_REQUIRE(a.b.dtype == DG_E4M3 || a.b.dtype == DG_E2M1_PACKED, "b dtype");
+    DG_REQUIRE(!(a.a.dtype == DG_E2M1_PACKED && a.b.dtype == DG_E2M1_PACKED),
+               "FP4 x FP4 (kind::mxf4) is not built yet");
+    DG_REQUIRE(a.d_dtype == DG_BF16 || a.d_dtype == DG_F32, "d dtype");
+    DG_REQUIRE(a.a.gran_k == 32 || a.a.gran_k == 128, "gran_k of a");
+    DG_REQUIRE(a.b.gran_k == 32 || a.b.gran_k == 128, "gran_k of b");
+    const bool grouped = a.gemm_type != DG_GEMM_NORMAL;
+    DG_REQUIRE(!grouped || (a.grouped_layout != nullptr && a.num_groups > 0), "grouped_layout");
+    const bool k_grouped = a.gemm_type == DG_GEMM_K_GROUPED || a.gemm_type == DG_GEMM_K_GROUPED_PSUM;
+    const bool m_grouped = grouped && !k_grouped;
+    DG_REQUIRE(!k_grouped || (a.a.mn_major && a.b.mn_major && a.a.gran_k == a.b.gran_k), "k-grouped layout");
+    DG_REQUIRE(!m_grouped || !a.a.mn_major, "m-grouped A is K-major");
+    DG_REQUIRE(!m_grouped || a.d_dtype == DG_BF16, "m-grouped D is BF16");
+    DG_REQUIRE(a.a.dtype == DG_E4M3 || a.k % 128 == 0, "FP4 K is a multiple of 128");
+    DG_REQUIRE(a.b.dtype == DG_E4M3 || a.k % 128 == 0, "FP4 K is a multiple of 128");
+
+    int num_sms = dg_get_num_sms();
+    DG_REQUIRE(num_sms > 0, "num_sms");
+    TileChoice t;
+    choose_tile(a, num_sms, &t);
+    DG_REQUIRE(t.ctas == 1 || t.ctas == 2, "cta group");
+    DG_REQUIRE(!(t.swap && a.d_dtype == DG_F32), "swapped tiles write BF16 only");
+    DG_REQUIRE(!(t.swap && a.accumulate), "swapped tiles do not accumulate");
+
+    const uint32_t unit_m = t.swap ? t.bn : 128 * t.ctas;
+    const uint32_t unit_n = t.swap ? 128 * t.ctas : t.bn;
+    if (a.gemm_type == DG_GEMM_M_CONTIGUOUS || a.gemm_type == DG_GEMM_M_PSUM) {
+        const int align = a.gemm_type == DG_GEMM_M_PSUM ? a.alignment : dg_get_mk_alignment_for_contiguous_layout();
+        DG_REQUIRE(align > 0 && align % unit_m == 0, "group alignment is a multiple of the token tile");
+    }
+    if (k_grouped) DG_REQUIRE(a.alignment > 0 && a.alignment % 128 == 0, "k alignment");
+
+    // Operand roles
+    const dg_operand& op_r = t.swap ? a.b : a.a;
+    const dg_operand& op_c = t.swap ? a.a : a.b;
+    const uint32_t c_rows_per_cta = t.bn / t.ctas;
+    const uint32_t sfc_rows = (t.bn + 127) / 128 * 128;
+    OperandPlan plan_r, plan_c;
+    int rc = plan_operand(a, op_r, /*is_a=*/!t.swap, 128, 128, &plan_r);
+    if (rc != DG_OK) return rc;
+    rc = plan_operand(a, op_c, /*is_a=*/t.swap, c_rows_per_cta, sfc_rows, &plan_c);
+    if (rc != DG_OK) return rc;
+
+    dg::GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.tm_r = plan_r.tm, p.tm_c = plan_c.tm, p.tm_sfr = plan_r.tm_sf, p.tm_sfc = plan_c.tm_sf;
+    p.r = plan_r.params, p.c = plan_c.params;
+    p.rows_per_group_r = plan_r.rows_per_group, p.rows_per_group_c = plan_c.rows_per_group;
+    p.k_rows_per_group_r = plan_r.k_rows_per_group, p.k_rows_per_group_c = plan_c.k_rows_per_group;
+    p.sf_groups_r = plan_r.sf_groups, p.sf_groups_c = plan_c.sf_groups;
+    p.gemm_type = a.gemm_type;
+    p.m = a.m, p.n = a.n, p.k = a.k;
+    p.num_groups = grouped ? a.num_groups : 1;
+    p.alignment = a.alignment > 0 ? a.alignment : 128;
+    p.grouped_layout = a.grouped_layout;
+    p.num_m_blocks = (a.m + unit_m - 1) / unit_m;
+    p.num_n_blocks = (a.n + unit_n - 1) / unit_n;
+    p.alpha = a.alpha;
+    p.accumulate = a.accumulate ? 1 : 0;
+    p.d_grouped = (a.gemm_type == DG_GEMM_M_MASKED || k_grouped) ? 1 : 0;
+    {
+        std::lock_guard<std::mutex> lk(g_knobs.mu);
+        p.timeout_ms = g_knobs.timeout_ms;
+    }
+    void* status_ptr = nullptr;
+    DG_CUDA(cudaGetSymbolAddress(&status_ptr, g_status));
+    p.status = static_cast<uint32_t*>(status_ptr);
+
+    // D: [groups, m, n] row-major
+    {
+        const uint32_t es = a.d_dtype == DG_F32 ? 4 : 2;
+        const uint64_t d_groups = p.d_grouped ? a.num_groups : 1;
+        const uint64_t dims[3] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.m), d_groups};
+        const uint64_t strides[2] = {static_cast<uint64_t>(a.ldd), static_cast<uint64_t>(a.ldd) * a.m};
+        uint32_t box[3];
+        CUtensorMapSwizzle sw;
+        if (t.swap) {
+            box[0] = 32, box[1] = 32, box[2] = 1, sw = CU_TENSOR_MAP_SWIZZLE_NONE;
+        } else {
+            box[0] = 128 / es, box[1] = 32, box[2] = 1, sw = CU_TENSOR_MAP_SWIZZLE_128B;
+        }
+        rc = encode_tmap(&p.tm_d, a.d_dtype == DG_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                         3, a.d, dims, strides, box, sw, "d");
+        if (rc != DG_OK) return rc;
+    }
+
+    // Grid: persistent units, never more than there are tiles (when the host can know)
+    uint32_t units = static_cast<uint32_t>(num_sms) / t.ctas;
+    uint64_t tiles = static_cast<uint64_t>(p.num_m_blocks) * p.num_n_blocks;
+    if (k_grouped) tiles *= a.num_groups;
+    if (a.gemm_type == DG_GEMM_M_MASKED) tiles *= a.num_groups;   // upper bound: m = max rows per group
+    if (a.gemm_type != DG_GEMM_M_PSUM && tiles < units) units = static_cast<uint32_t>(tiles);
+    DG_REQUIRE(units > 0, "empty grid");
+    p.num_units = units;
+    p.raster = choose_raster(p.num_m_blocks, unit_m, unit_n, units);
+
+#define DG_TRY(CT, BNV, SW, F32)                                                           \
+    if (t.ctas == CT && t.bn == BNV && t.swap == SW && (a.d_dtype == DG_F32) == F32)       \
+        return launch_gemm<dg::GemmConfig<CT, BNV, SW, F32>>(p, a, units);
+    DG_TRY(1, 128, false, false)
+    DG_TRY(1, 256, false, false)
+    DG_TRY(2, 128, false, false)
+    DG_TRY(2, 256, false, false)
+    DG_TRY(1, 128, false, true)
+    DG_TRY(1, 256, false, true)
+    DG_TRY(2, 128, false, true)
+    DG_TRY(2, 256, false, true)
+    DG_TRY(1, 64, true, false)
+    DG_TRY(1, 128, true, false)
+    DG_TRY(2, 64, true, false)
+    DG_TRY(2, 128, true, false)
+    DG_TRY(2, 256, true, false)
+#undef DG_TRY
+    return fail(DG_ERR_INVALID, "no kernel built for cta_group %d, block_n %d, swap %d, f32 %d", t.ctas, t.bn,
+                static_cast<int>(t.swap), static_cast<int>(a.d_dtype == DG_F32));
+}
+
+}  // extern "C"

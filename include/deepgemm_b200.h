@@ -1,0 +1,139 @@
+/* C ABI of libdeepgemm_b200.so: block-scaled FP8 / FP8xFP4 GEMMs for NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers and sizes only; every tensor is borrowed for the duration of the enqueued
+ * work and must be device memory of the current CUDA device unless stated otherwise.  All
+ * entry points return 0 on success and a non-zero code on failure, in which case
+ * dg_last_error() (thread-local) describes the failed check.  Work is enqueued on the
+ * given stream and the call returns without synchronising.
+ *
+ * Each entry point names the function of the reference (fw-ai/DeepGEMM, paths relative to
+ * its root) whose role it takes behind the `deep_gemm` Python operator surface.
+ */
+#ifndef DEEPGEMM_B200_H_
+#define DEEPGEMM_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum dg_status {
+    DG_OK = 0,
+    DG_ERR_INVALID = 1,   /* an argument check failed; see dg_last_error() */
+    DG_ERR_CUDA = 2,      /* a CUDA runtime / driver call failed */
+    DG_ERR_DEVICE = 3,    /* a kernel gave up on a bounded wait; see dg_check_status() */
+};
+
+enum dg_gemm_type {
+    DG_GEMM_NORMAL = 0,
+    DG_GEMM_M_CONTIGUOUS = 1,    /* grouped_layout: int32[M], expert id per row, -1 = padding */
+    DG_GEMM_M_MASKED = 2,        /* grouped_layout: int32[G], valid rows per group (read on device) */
+    DG_GEMM_M_PSUM = 3,          /* grouped_layout: int32[G], cumulative un-aligned row ends */
+    DG_GEMM_K_GROUPED = 4,       /* grouped_layout: int32[G], padded K per group */
+    DG_GEMM_K_GROUPED_PSUM = 5,  /* grouped_layout: int32[G], cumulative un-aligned K ends */
+};
+
+enum dg_dtype { DG_E4M3 = 0, DG_E2M1_PACKED = 1, DG_BF16 = 2, DG_F32 = 3 };
+
+/* One quantised operand: data plus packed UE8M0 scale factors.
+ *   data : E4M3 bytes, or E2M1 codes two per byte (low nibble first).
+ *   ld   : distance in bytes between consecutive rows of the non-contiguous axis
+ *          (K-major: between MN rows; MN-major: between K rows).
+ *   sf   : int32, four UE8M0 exponents per word in K order, MN-major:
+ *          element (g, mn, kw) at  g * sf_group_stride + kw * sf_ld + mn   (in words).
+ *          K-grouped GEMMs: (kw, mn) at kw * sf_ld + mn with groups stacked along kw.
+ */
+typedef struct dg_operand {
+    const void* data;
+    const int32_t* sf;
+    int64_t ld;
+    int64_t sf_ld;
+    int32_t dtype;      /* DG_E4M3 or DG_E2M1_PACKED */
+    int32_t mn_major;   /* 0: K contiguous, 1: MN contiguous (E4M3 only) */
+    int32_t gran_k;     /* K elements per scale: 32 or 128 */
+    int32_t reserved;
+} dg_operand;
+
+/* Arguments of dg_gemm_bs.  Shapes are logical GEMM shapes: D[m, n] = A[m, k] * B[n, k]^T.
+ *   NORMAL        : a [m,k], b [n,k], d [m,n]
+ *   M_CONTIGUOUS  : a [m,k] (m = all groups' rows), b [G,n,k], d [m,n]
+ *   M_PSUM        : as M_CONTIGUOUS; group g owns rows [align(end[g-1], alignment), end[g])
+ *   M_MASKED      : a [G,m,k], b [G,n,k], d [G,m,n] (m = max rows per group)
+ *   K_GROUPED*    : a [sum_k, m], b [sum_k, n] (both MN-major), d [G,m,n], k = sum of padded K
+ */
+typedef struct dg_gemm_args {
+    int32_t gemm_type;
+    int32_t m, n, k;
+    int32_t num_groups;
+    int32_t alignment;        /* M (psum) or K (k-grouped) group alignment */
+    dg_operand a, b;
+    void* d;
+    int64_t ldd;              /* bytes between rows of d */
+    int32_t d_dtype;          /* DG_BF16 or DG_F32 */
+    int32_t accumulate;       /* d += result instead of d = result */
+    float alpha;              /* result scale; pass 1.0f when unused */
+    int32_t expected_m;       /* heuristic hint for grouped layouts; 0 = none */
+    const int32_t* grouped_layout;
+    void* stream;             /* cudaStream_t */
+    /* Tile selection override for tests and tuning; 0 = choose automatically. */
+    int32_t force_cta_group;  /* 1 or 2 */
+    int32_t force_block_n;    /* UMMA N: 32, 64, 128, 256 */
+    int32_t force_swap;       /* 1 = plain, 2 = swapped operands */
+    int32_t reserved;
+} dg_gemm_args;
+
+/* Block-scaled GEMM, all layouts.  Takes the role of sm100_fp8_fp4_gemm_1d1d and its grouped
+ * variants (csrc/jit_kernels/impls/sm100_fp8_fp4_gemm_1d1d.hpp:101-561) as called from
+ * fp8_fp4_gemm_nt, m_grouped_fp8_fp4_gemm_nt_contiguous, m_grouped_fp8_fp4_gemm_nt_masked and
+ * k_grouped_fp8_gemm_tn_contiguous (csrc/apis/gemm.hpp:78-375). */
+int dg_gemm_bs(const dg_gemm_args* args);
+
+/* FP32 power-of-two scales -> packed UE8M0, MN-major, 16-byte-aligned columns.
+ *   sf  : float32, the scale of row mn is element (b, mn / gran_mn, k) at
+ *         b * stride_b + (mn / gran_mn) * stride_mn + k * stride_k (elements); gran_mn = 1 for
+ *         per-row scales, 128 to broadcast 128x128 block scales to rows (csrc/apis/layout.hpp:47-50)
+ *   out : int32 [num_batches, mn, ceil(sf_k / 4)], element (b, mn, kw) at
+ *         b * ceil(sf_k/4) * align(mn, 4) + kw * align(mn, 4) + mn
+ *   psum_layout (optional, int32[num_psum_groups], device): rows outside
+ *         [align(end[g-1], psum_alignment), end[g]) are written as zero.
+ * Takes the role of get_mn_major_tma_aligned_packed_ue8m0_tensor
+ * (csrc/jit_kernels/impls/smxx_layout.hpp:133-246) and its kernel
+ * transpose_and_pack_fp32_into_ue8m0 (deep_gemm/include/deep_gemm/impls/smxx_layout.cuh:76-191). */
+int dg_sf_pack_ue8m0(const float* sf, int32_t* out, int32_t num_batches, int32_t mn, int32_t sf_k,
+                     int32_t gran_mn, int64_t stride_b, int64_t stride_mn, int64_t stride_k,
+                     const int32_t* psum_layout, int32_t num_psum_groups, int32_t psum_alignment, void* stream);
+
+/* K-grouped packing: sf float32 [sum(sf_k_g), mn] (mn contiguous) -> out int32 [sum(ceil(sf_k_g / 4)), mn];
+ * every group starts a new packed row and zero-fills the unused bytes of its last row.
+ *   grouped_layout (device int32[num_groups]): padded K per group, or (use_psum) cumulative K ends.
+ * Takes the role of get_k_grouped_mn_major_tma_aligned_packed_ue8m0_tensor
+ * (csrc/jit_kernels/impls/smxx_layout.hpp:248-313, kernel pack_fp32_into_ue8m0,
+ * deep_gemm/include/deep_gemm/impls/smxx_layout.cuh:305-405). */
+int dg_sf_pack_ue8m0_k_grouped(const float* sf, int32_t* out, const int32_t* grouped_layout, int32_t num_groups,
+                               int32_t mn, int32_t sf_k_rows, int32_t packed_rows, int32_t gran_k,
+                               int32_t k_alignment, int32_t use_psum, void* stream);
+
+/* Process-wide knobs (csrc/apis/config.hpp:8-48, csrc/apis/layout.hpp:138-146 of the reference). */
+int dg_set_num_sms(int32_t num_sms);
+int dg_get_num_sms(void);           /* device SM count unless overridden */
+int dg_set_tc_util(int32_t percent);
+int dg_get_tc_util(void);
+int dg_set_mk_alignment_for_contiguous_layout(int32_t alignment);
+int dg_get_mk_alignment_for_contiguous_layout(void);
+int dg_get_theoretical_mk_alignment_for_contiguous_layout(int32_t expected_m);
+int dg_set_wait_timeout_ms(int32_t ms);  /* budget of every device-side wait; default 2000 */
+
+/* Synchronises the device and reports whether any kernel of this library abandoned a wait
+ * since the last call.  Returns DG_OK, or DG_ERR_DEVICE with the record in info[0..7]
+ * ([0] code, [1] wait site, [2] block, [3] tile iteration, [4] K block, [5] stage) and in
+ * dg_last_error().  The record is cleared. */
+int dg_check_status(uint32_t info[8]);
+
+const char* dg_last_error(void);
+const char* dg_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DEEPGEMM_B200_H_ */

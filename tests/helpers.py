@@ -1,0 +1,106 @@
+"""Shared input generators and oracle glue for the GPU parity tests.
+
+Inputs follow the reference's generators (tests/generators.py:350-485): seeded BF16 normal
+matrices, quantised per token (1 x gran_k) for activations and per 128 x 128 block (FP8) or
+1 x 32 (FP4) for weights, power-of-two scales.  Expected values come from the numpy oracle
+(oracle/), which dequantises exactly what the kernel is given.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from oracle import gemm as OG
+from oracle import layout as OL
+from oracle import quant as OQ
+
+import deepgemm_b200 as dg
+from deepgemm_b200.utils import math as M
+
+
+def to_np(t: torch.Tensor) -> np.ndarray:
+    t = t.detach().cpu()
+    if t.dtype == torch.float8_e4m3fn or t.dtype == torch.int8:
+        return t.contiguous().view(torch.uint8).numpy()
+    if t.dtype == torch.bfloat16:
+        return t.float().numpy()
+    return t.numpy()
+
+
+def packed_sf_to_torch(view: np.ndarray, device="cuda") -> torch.Tensor:
+    """Upload an oracle packed-SF strided view keeping its MN-major strides."""
+    shape = view.shape
+    strides = OL.element_strides(view)
+    n_store = sum((s - 1) * st for s, st in zip(shape, strides)) + 1
+    # rebuild the storage in the same order
+    storage = np.zeros(n_store, dtype=np.int32)
+    np.lib.stride_tricks.as_strided(storage, shape=shape, strides=[s * 4 for s in strides])[...] = view
+    t = torch.from_numpy(storage).to(device)
+    return t.as_strided(shape, strides)
+
+
+def quant_act(x: torch.Tensor, gran_k: int):
+    """Per-token FP8 (activations): returns (e4m3 tensor, fp32 scales)."""
+    return M.per_token_cast_to_fp8(x, use_ue8m0=True, gran_k=gran_k)
+
+
+def quant_weight_fp8_block(w: torch.Tensor):
+    return M.per_block_cast_to_fp8(w, use_ue8m0=True, gran_k=128)
+
+
+def quant_weight_fp4(w: torch.Tensor):
+    return M.per_token_cast_to_fp4(w, use_ue8m0=True, gran_k=32)
+
+
+def dequant(data: torch.Tensor, sf: torch.Tensor, gran_mn: int, gran_k: int) -> np.ndarray:
+    """Oracle dequantisation of one [.., mn, k] operand given exactly as the kernel gets it."""
+    is_fp4 = data.dtype == torch.int8
+    return OG.dequant_operand(to_np(data), to_np(sf), gran_mn, gran_k, is_fp4)
+
+
+def calc_diff(x, y) -> float:
+    return OQ.calc_diff(np.asarray(x, dtype=np.float64), np.asarray(y, dtype=np.float64))
+
+
+def make_dense(m, n, k, *, gran_a=128, b_kind="fp8_block", seed=0, device="cuda", scale_b=1.0):
+    """A per-token FP8; B 128x128-block FP8 ('fp8_block'), per-row FP8 ('fp8_row', gran from b_gran)
+    or MXFP4 1x32 ('fp4')."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    a = torch.randn((m, k), generator=g, dtype=torch.float32).to(torch.bfloat16).to(device)
+    b = (torch.randn((n, k), generator=g, dtype=torch.float32) * scale_b).to(torch.bfloat16).to(device)
+    qa = quant_act(a, gran_a)
+    if b_kind == "fp8_block":
+        qb, gran_mn_b, gran_b = quant_weight_fp8_block(b), 128, 128
+    elif b_kind == "fp8_row128":
+        qb, gran_mn_b, gran_b = M.per_token_cast_to_fp8(b, True, 128), 1, 128
+    elif b_kind == "fp8_row32":
+        qb, gran_mn_b, gran_b = M.per_token_cast_to_fp8(b, True, 32), 1, 32
+    elif b_kind == "fp4":
+        qb, gran_mn_b, gran_b = quant_weight_fp4(b), 1, 32
+    else:
+        raise ValueError(b_kind)
+    ref_a = dequant(qa[0], qa[1], 1, gran_a)
+    ref_b = dequant(qb[0], qb[1], gran_mn_b, gran_b)
+    return qa, qb, (gran_a, gran_mn_b, gran_b), ref_a, ref_b
+
+
+def recipes(gran_a, gran_mn_b, gran_b):
+    return dict(recipe_a=(1, gran_a), recipe_b=(gran_mn_b, gran_b))
+
+
+class force_tile:
+    """Context manager: pin the tile the library picks (tests only)."""
+
+    def __init__(self, **kw):
+        self.kw = kw
+
+    def __enter__(self):
+        from deepgemm_b200 import ops
+        self.old = dict(ops._force_tile)
+        ops._force_tile.clear()
+        ops._force_tile.update({k: v for k, v in self.kw.items() if v})
+
+    def __exit__(self, *exc):
+        from deepgemm_b200 import ops
+        ops._force_tile.clear()
+        ops._force_tile.update(self.old)

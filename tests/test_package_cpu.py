@@ -1,0 +1,108 @@
+"""CPU checks of the shipped package: torch quantisation helpers against the reference-generated
+golden vectors, the C ABI's exported symbols, and host-side argument validation."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import deepgemm_b200 as dg
+from deepgemm_b200 import _lib
+from deepgemm_b200.utils import math as M
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def bits(t):
+    return t.contiguous().view(torch.uint8).numpy()
+
+
+def test_torch_quant_helpers_match_reference_vectors(golden):
+    for tag, g in (("pt128", 128), ("pt32", 32), ("pt128_ragged", 128)):
+        for ue in (0, 1):
+            x = torch.from_numpy(golden[f"{tag}_ue{ue}_x"]).to(torch.bfloat16)
+            q, sf = M.per_token_cast_to_fp8(x, bool(ue), g)
+            assert np.array_equal(bits(q), golden[f"{tag}_ue{ue}_q"])
+            assert np.array_equal(sf.numpy().view(np.uint32), golden[f"{tag}_ue{ue}_sf"].view(np.uint32))
+        q, psf = M.per_token_cast_to_fp8(x, True, g, use_packed_ue8m0=True)
+        assert np.array_equal(psf.numpy(), golden[f"{tag}_packed_sf"])
+        back = M.cast_back_from_fp8(q, psf, g, use_packed_ue8m0=True)
+        assert np.array_equal(back.numpy().view(np.uint32), golden[f"{tag}_back"].view(np.uint32))
+    x = torch.from_numpy(golden["pb_x"]).to(torch.bfloat16)
+    for ue in (0, 1):
+        q, sf = M.per_block_cast_to_fp8(x, bool(ue), 128)
+        assert np.array_equal(bits(q), golden[f"pb_ue{ue}_q"])
+        assert np.array_equal(sf.numpy(), golden[f"pb_ue{ue}_sf"])
+    x = torch.from_numpy(golden["pc_x"]).to(torch.bfloat16)
+    for g in (32, 128):
+        q, sf = M.per_channel_cast_to_fp8(x, True, g)
+        assert np.array_equal(bits(q), golden[f"pc{g}_q"]) and np.array_equal(sf.numpy(), golden[f"pc{g}_sf"])
+    x = torch.from_numpy(golden["fp4_x"]).to(torch.bfloat16)
+    for ue in (0, 1):
+        p, sf = M.per_token_cast_to_fp4(x, bool(ue), 32)
+        assert np.array_equal(bits(p), golden[f"fp4_ue{ue}_p"]) and np.array_equal(sf.numpy(), golden[f"fp4_ue{ue}_sf"])
+    p, psf = M.per_token_cast_to_fp4(x, True, 32, use_packed_ue8m0=True)
+    assert np.array_equal(psf.numpy(), golden["fp4_packed_sf"])
+    assert np.array_equal(M.cast_back_from_fp4(p, psf, 32, use_packed_ue8m0=True).numpy(), golden["fp4_back"])
+    t_in = torch.from_numpy(golden["fp4_t_in"]).view(torch.int8)
+    assert np.array_equal(bits(M.transpose_packed_fp4(t_in)), golden["fp4_t_out"])
+    assert np.array_equal(M.ceil_to_ue8m0(torch.from_numpy(golden["ceil_in"])).numpy().view(np.uint32),
+                          golden["ceil_out"].view(np.uint32))
+    assert abs(dg.testing.calc_diff(torch.from_numpy(golden["diff_a"]), torch.from_numpy(golden["diff_b"]))
+               - float(golden["diff_val"])) < 1e-12
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "deepgemm_b200.h")).read()
+    declared = set(re.findall(r"\b(dg_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    lib = _lib.lib()
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    assert declared == set(_lib.EXPORTS)
+    assert b"sm_100a" in lib.dg_version()
+
+
+def test_knobs_roundtrip():
+    old = dg.get_mk_alignment_for_contiguous_layout()
+    try:
+        dg.set_mk_alignment_for_contiguous_layout(256)
+        assert dg.get_mk_alignment_for_contiguous_layout() == 256
+        with pytest.raises(RuntimeError):
+            dg.set_mk_alignment_for_contiguous_layout(7)
+    finally:
+        dg.set_mk_alignment_for_contiguous_layout(old)
+    assert dg.get_tc_util() == 100
+    dg.set_tc_util(80)
+    assert dg.get_tc_util() == 80
+    dg.set_tc_util(100)
+    assert dg.get_theoretical_mk_alignment_for_contiguous_layout() in (128, 256)
+    assert dg.utils.get_m_alignment_for_contiguous_layout() == old
+
+
+def test_gemm_argument_checks_raise_runtime_error():
+    lib = _lib.lib()
+    args = _lib.GemmArgs()
+    args.gemm_type, args.m, args.n, args.k = 0, 128, 128, 128
+    assert lib.dg_gemm_bs(ctypes.byref(args)) != 0          # null tensors
+    assert b"Assertion failed" in lib.dg_last_error()
+    args.gemm_type = 99
+    assert lib.dg_gemm_bs(ctypes.byref(args)) != 0
+    args.gemm_type, args.m = 0, 0
+    assert lib.dg_gemm_bs(ctypes.byref(args)) == 0          # empty problem: nothing to do
+
+
+def test_sf_layout_validation_messages():
+    sf = torch.zeros((64, 3), dtype=torch.int32)
+    with pytest.raises(RuntimeError, match=r"sf\.size\(-1\)"):
+        dg.transform_sf_into_required_layout(sf, 64, 128 * 4 * 2, (1, 128))
+    good = torch.zeros((2, 64), dtype=torch.int32).t()     # MN-major [64, 2]
+    out = dg.transform_sf_into_required_layout(good, 64, 1024, (1, 128))
+    assert out.data_ptr() == good.data_ptr()
+    bad = torch.zeros((64, 2), dtype=torch.int32)           # K-major packed scales are rejected
+    with pytest.raises(RuntimeError, match=r"stride\(-2\) == 1"):
+        dg.transform_sf_into_required_layout(bad, 64, 1024, (1, 128))
+    with pytest.raises(RuntimeError, match="is_sfa"):
+        dg.transform_sf_into_required_layout(good, 64, 1024, (1, 1, 128))
