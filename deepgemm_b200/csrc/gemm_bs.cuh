@@ -80,7 +80,18 @@ struct GemmParams {
     uint32_t d_grouped;         // D has a group axis (masked / K-grouped): third store coordinate = group
     uint32_t timeout_ms;
     uint32_t* status;           // 16 words: [0] code, [1] site, [2] block, [3] tile iter, [4] k block, [5] stage
+    unsigned long long* trace;  // optional clock samples of block 0's first tile (builds with DG_TRACE only)
 };
+
+#ifdef DG_TRACE
+#define DG_TRACE_AT(role, kb_)                                                                  \
+    do {                                                                                        \
+        if (p.trace != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && iter == 0 && (kb_) < 64)                   \
+            p.trace[(role) * 64 + (kb_)] = static_cast<unsigned long long>(clock64());          \
+    } while (0)
+#else
+#define DG_TRACE_AT(role, kb_) do { } while (0)
+#endif
 
 struct TileCoord {
     uint32_t m_blk, n_blk, group;
@@ -344,8 +355,9 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
         return kPair ? map_to_cta(smem_u32(bar), 0) : smem_u32(bar);
     };
 
-    const uint32_t first_k_block_words_r = p.r.gran_k == 128 ? 4 : 1;   // k-blocks covered by one SF word
-    const uint32_t first_k_block_words_c = p.c.gran_k == 128 ? 4 : 1;
+    // K-blocks covered by one packed scale word: 4 (one scale per 128 K) or 1 (one per 32 K)
+    const uint32_t sf_mask_r = p.r.gran_k == 128 ? 3 : 0, sf_shift_r = p.r.gran_k == 128 ? 2 : 0;
+    const uint32_t sf_mask_c = p.c.gran_k == 128 ? 3 : 0, sf_shift_c = p.c.gran_k == 128 ? 2 : 0;
 
     // Role loops share: tile iteration, stage / phase bookkeeping.
     uint32_t stage = 0, phase = 0;
@@ -356,10 +368,17 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
 
     if (warp == 0) {
         // ============================================================ TMA producer
-        if (lane == 0) {
+        // The whole warp runs the loop (uniform control flow keeps addresses and coordinates in
+        // uniform registers); one elected lane issues the copies.
+        {
             TileWalker walker(p, Cfg::UNIT_M, Cfg::UNIT_N);
             TileCoord tc;
             bool ok = true;
+            const uint32_t full_bar0 = leader_addr(&bars->full[0]);
+            const uint32_t stage_tx_bytes = p.r.tx_bytes + p.c.tx_bytes;
+            const uint32_t r_boxes = p.r.num_boxes, r_box_bytes = p.r.box_bytes, r_box_mn = p.r.box_mn;
+            const uint32_t c_boxes = p.c.num_boxes, c_box_bytes = p.c.box_bytes, c_box_mn = p.c.box_mn;
+            const bool r_mn_major = p.r.mn_major != 0, c_mn_major = p.c.mn_major != 0;
             for (uint32_t iter = 0; ok && walker.next(iter * p.num_units + unit, tc); ++iter) {
                 // Operand coordinates of this tile (GEMM A / B, then mapped to R / C)
                 const uint32_t a_blk_rows = Cfg::kSwap ? BN : 128 * kCtas;
@@ -392,57 +411,68 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
 
                 const uint32_t num_kb = max(1u, (tc.k_len + 127u) / 128u);
                 for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
+                    DG_TRACE_AT(0, kb);
                     ok = wait_barrier<false>(&bars->empty[stage], phase ^ 1, abort_flag, peer_abort, p,
                                              kSiteProducerEmpty, iter, kb, stage);
                     if (!ok) break;
+                    DG_TRACE_AT(1, kb);
+                    if (elect_one()) {
                     // Scale factors first: the transposer works while the operand tiles are in flight
                     uint32_t sf_bytes = 0;
                     const uint32_t sf_bar = smem_u32(&bars->sf_full[stage]);
-                    if (kb % first_k_block_words_r == 0) {
+                    if ((kb & sf_mask_r) == 0) {
                         tma_load_2d<false>(smem_sfr + stage * Cfg::SFR_STAGE, &p.tm_sfr, sf_bar,
                                            static_cast<int32_t>(sfr_mn),
-                                           static_cast<int32_t>(sfr_k + kb / first_k_block_words_r));
+                                           static_cast<int32_t>(sfr_k + (kb >> sf_shift_r)));
                         sf_bytes += Cfg::SFR_STAGE;
                     }
-                    if (kb % first_k_block_words_c == 0) {
+                    if ((kb & sf_mask_c) == 0) {
                         tma_load_2d<false>(smem_sfc + stage * Cfg::SFC_STAGE, &p.tm_sfc, sf_bar,
                                            static_cast<int32_t>(sfc_mn),
-                                           static_cast<int32_t>(sfc_k + kb / first_k_block_words_c));
+                                           static_cast<int32_t>(sfc_k + (kb >> sf_shift_c)));
                         sf_bytes += Cfg::SFC_STAGE;
                     }
                     mbar_arrive_expect_tx(&bars->sf_full[stage], sf_bytes);
 
                     // Operand tiles land on the leader's barrier (both CTAs of a pair feed one UMMA)
-                    const uint32_t full_bar = leader_addr(&bars->full[stage]);
-                    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(
-                                     full_bar),
-                                 "r"(p.r.tx_bytes + p.c.tx_bytes)
-                                 : "memory");
+                    const uint32_t full_bar = full_bar0 + stage * 8;
+                    mbar_arrive_expect_tx_cluster(full_bar, stage_tx_bytes);
                     const uint32_t kr = r_k + kb * 128, kc = c_k + kb * 128;
-                    for (uint32_t b = 0; b < p.r.num_boxes; ++b) {
-                        const uint32_t dst = smem_r + stage * Cfg::R_STAGE + b * p.r.box_bytes;
-                        const uint32_t mn = r_mn + b * p.r.box_mn;
-                        if (p.r.mn_major) tma_load_2d<kPair>(dst, &p.tm_r, full_bar, mn, kr);
+                    for (uint32_t b = 0; b < r_boxes; ++b) {
+                        const uint32_t dst = smem_r + stage * Cfg::R_STAGE + b * r_box_bytes;
+                        const uint32_t mn = r_mn + b * r_box_mn;
+                        if (r_mn_major) tma_load_2d<kPair>(dst, &p.tm_r, full_bar, mn, kr);
                         else              tma_load_2d<kPair>(dst, &p.tm_r, full_bar, kr, mn);
                     }
-                    for (uint32_t b = 0; b < p.c.num_boxes; ++b) {
-                        const uint32_t dst = smem_c + stage * Cfg::C_STAGE + b * p.c.box_bytes;
-                        const uint32_t mn = c_mn + b * p.c.box_mn;
-                        if (p.c.mn_major) tma_load_2d<kPair>(dst, &p.tm_c, full_bar, mn, kc);
+                    for (uint32_t b = 0; b < c_boxes; ++b) {
+                        const uint32_t dst = smem_c + stage * Cfg::C_STAGE + b * c_box_bytes;
+                        const uint32_t mn = c_mn + b * c_box_mn;
+                        if (c_mn_major) tma_load_2d<kPair>(dst, &p.tm_c, full_bar, mn, kc);
                         else              tma_load_2d<kPair>(dst, &p.tm_c, full_bar, kc, mn);
                     }
+                    }
+                    __syncwarp();
                 }
             }
         }
     } else if (warp == 1) {
         // ============================================================ UMMA issuer (leader CTA only)
-        if (is_leader && lane == 0) {
+        // Whole warp in the loop, one elected lane issues (always the same lane, so that
+        // tcgen05.commit covers every UMMA issued before it).
+        if (is_leader) {
             TileWalker walker(p, Cfg::UNIT_M, Cfg::UNIT_N);
             TileCoord tc;
             bool ok = true;
             const uint32_t idesc_base = make_idesc_mxf8f6f4(p.r.fmt, p.c.fmt, p.r.mn_major != 0, p.c.mn_major != 0,
                                                             128 * kCtas, BN);
             const uint64_t sf_desc_hi = make_smem_desc(0, 0, 128, kSwizzleNone);
+            // Operand descriptors: constant high word; the low word carries (address >> 4) and the LBO field
+            const uint32_t r_hi = static_cast<uint32_t>(make_smem_desc(0, p.r.desc_lbo, p.r.desc_sbo, kSwizzle128B) >> 32);
+            const uint32_t c_hi = static_cast<uint32_t>(make_smem_desc(0, p.c.desc_lbo, p.c.desc_sbo, kSwizzle128B) >> 32);
+            const uint32_t r_lo0 = static_cast<uint32_t>(make_smem_desc(smem_r, p.r.desc_lbo, p.r.desc_sbo, kSwizzle128B));
+            const uint32_t c_lo0 = static_cast<uint32_t>(make_smem_desc(smem_c, p.c.desc_lbo, p.c.desc_sbo, kSwizzle128B));
+            const uint32_t r_kstep = p.r.desc_kstep >> 4, c_kstep = p.c.desc_kstep >> 4;
+            const bool r_per32 = p.r.gran_k == 32, c_per32 = p.c.gran_k == 32;
             for (uint32_t iter = 0; ok && walker.next(iter * p.num_units + unit, tc); ++iter) {
                 const uint32_t acc = iter % kAccStages;
                 const uint32_t acc_phase = (iter / kAccStages) & 1;
@@ -453,16 +483,19 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 const uint32_t num_kb = max(1u, (tc.k_len + 127u) / 128u);
                 for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
+                    DG_TRACE_AT(3, kb);
                     ok = wait_barrier<kPair>(&bars->full[stage], phase, abort_flag, peer_abort, p, kSiteMmaFull, iter,
                                              kb, stage);
                     if (!ok) break;
+                    DG_TRACE_AT(4, kb);
                     tc_fence_after();
+                    if (elect_one()) {
                     // Fresh scale factors: shared memory (already in 32x4 order) -> TMEM
-                    if (kb % first_k_block_words_r == 0) {
+                    if ((kb & sf_mask_r) == 0) {
                         const uint32_t a = smem_sfr + stage * Cfg::SFR_STAGE;
                         utccp_32x128b_warpx4<kCtas>(tmem_base + Cfg::kSfrCol, sf_desc_hi | ((a >> 4) & 0x3FFF));
                     }
-                    if (kb % first_k_block_words_c == 0) {
+                    if ((kb & sf_mask_c) == 0) {
 #pragma unroll
                         for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i) {
                             const uint32_t a = smem_sfc + stage * Cfg::SFC_STAGE + i * 512;
@@ -470,21 +503,23 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                                                         sf_desc_hi | ((a >> 4) & 0x3FFF));
                         }
                     }
-                    const uint64_t r_desc = make_smem_desc(smem_r + stage * Cfg::R_STAGE, p.r.desc_lbo, p.r.desc_sbo,
-                                                           kSwizzle128B);
-                    const uint64_t c_desc = make_smem_desc(smem_c + stage * Cfg::C_STAGE, p.c.desc_lbo, p.c.desc_sbo,
-                                                           kSwizzle128B);
+                    const uint32_t r_lo = r_lo0 + stage * (Cfg::R_STAGE >> 4);
+                    const uint32_t c_lo = c_lo0 + stage * (Cfg::C_STAGE >> 4);
+                    const uint32_t id128 = kb & 3;
 #pragma unroll
                     for (uint32_t ks = 0; ks < 4; ++ks) {
-                        const uint32_t id_r = p.r.gran_k == 32 ? ks : (kb & 3);
-                        const uint32_t id_c = p.c.gran_k == 32 ? ks : (kb & 3);
-                        umma_mxf8f6f4<kCtas>(d_tmem, r_desc + ((ks * p.r.desc_kstep) >> 4),
-                                             c_desc + ((ks * p.c.desc_kstep) >> 4),
-                                             idesc_with_sf_ids(idesc_base, id_r, id_c), tmem_base + Cfg::kSfrCol,
-                                             tmem_base + Cfg::kSfcCol, (kb | ks) != 0);
+                        const uint32_t id_r = r_per32 ? ks : id128;
+                        const uint32_t id_c = c_per32 ? ks : id128;
+                        const uint64_t r_desc = (static_cast<uint64_t>(r_hi) << 32) | (r_lo + ks * r_kstep);
+                        const uint64_t c_desc = (static_cast<uint64_t>(c_hi) << 32) | (c_lo + ks * c_kstep);
+                        umma_mxf8f6f4<kCtas>(d_tmem, r_desc, c_desc, idesc_base | (id_c << 4) | (id_r << 29),
+                                             tmem_base + Cfg::kSfrCol, tmem_base + Cfg::kSfcCol, (kb | ks) != 0);
                     }
                     umma_commit<kCtas>(&bars->empty[stage]);   // frees the stage (in both CTAs)
                     if (kb + 1 == num_kb) umma_commit<kCtas>(&bars->tmem_full[acc]);
+                    }
+                    __syncwarp();
+                    DG_TRACE_AT(5, kb);
                 }
             }
         }
@@ -501,19 +536,23 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                 ok = wait_barrier<false>(&bars->sf_full[stage], phase, abort_flag, peer_abort, p,
                                          kSiteTransposerSfFull, iter, kb, stage);
                 if (!ok) break;
+                if (lane == 0) DG_TRACE_AT(2, kb);
                 auto transpose_128 = [&](uint32_t* w) {
                     uint32_t v0 = w[lane], v1 = w[32 + lane], v2 = w[64 + lane], v3 = w[96 + lane];
                     __syncwarp();
                     reinterpret_cast<uint4*>(w)[lane] = make_uint4(v0, v1, v2, v3);
                 };
-                if (kb % first_k_block_words_r == 0) transpose_128(sf_words_r + stage * 128);
-                if (kb % first_k_block_words_c == 0) {
+                const bool new_r = (kb & sf_mask_r) == 0, new_c = (kb & sf_mask_c) == 0;
+                if (new_r) transpose_128(sf_words_r + stage * 128);
+                if (new_c) {
 #pragma unroll
                     for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i)
                         transpose_128(sf_words_c + stage * Cfg::SFC_ROWS + i * 128);
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
+                if (new_r || new_c) {
+                    fence_proxy_async_smem();   // generic-proxy writes -> visible to tcgen05.cp
+                    __syncwarp();
+                }
                 if (lane == 0) mbar_arrive_cluster(full_bar + stage * 8);
             }
         }

@@ -42,6 +42,8 @@ int fail(int code, const char* fmt, ...) {
 // Device status block the kernels report abandoned waits into (one per device, zero at load).
 __device__ uint32_t g_status[16];
 
+unsigned long long* g_trace = nullptr;   // clock-sample buffer for builds with DG_TRACE (tuning aid)
+
 struct Knobs {
     std::mutex mu;
     int num_sms = 0;        // 0: use the device's count
@@ -271,6 +273,9 @@ uint32_t choose_raster(uint32_t num_m_blocks, uint32_t unit_m, uint32_t unit_n, 
 extern "C" {
 
 const char* dg_last_error(void) { return g_last_error.c_str(); }
+#ifdef DG_TRACE
+void dg_debug_set_trace(void* device_buffer) { g_trace = static_cast<unsigned long long*>(device_buffer); }
+#endif
 const char* dg_version(void) { return "deepgemm_b200 0.1 (sm_100a)"; }
 
 int dg_set_num_sms(int32_t n) {
@@ -447,6 +452,7 @@ int dg_gemm_bs(const dg_gemm_args* args) {
     void* status_ptr = nullptr;
     DG_CUDA(cudaGetSymbolAddress(&status_ptr, g_status));
     p.status = static_cast<uint32_t*>(status_ptr);
+    p.trace = g_trace;
 
     // D: [groups, m, n] row-major
     {

@@ -20,6 +20,8 @@ def bench_events(fn, num_warmups: int = 3, num_tests: int = 10, flush_l2: bool =
     for _ in range(num_tests):
         if flush is not None:
             flush.zero_()
+        # Keep the GPU busy while the host enqueues fn(), so that host latency is not timed
+        torch.cuda._sleep(int(2e5))
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         fn()

@@ -30,7 +30,9 @@ def to_np(t: torch.Tensor) -> np.ndarray:
 def packed_sf_to_torch(view: np.ndarray, device="cuda") -> torch.Tensor:
     """Upload an oracle packed-SF strided view keeping its MN-major strides."""
     shape = view.shape
-    strides = OL.element_strides(view)
+    # numpy may report anything for size-1 axes; rebuild the canonical MN-major strides
+    amn = (shape[-2] + 3) // 4 * 4
+    strides = (1, amn) if view.ndim == 2 else (shape[-1] * amn, 1, amn)
     n_store = sum((s - 1) * st for s, st in zip(shape, strides)) + 1
     # rebuild the storage in the same order
     storage = np.zeros(n_store, dtype=np.int32)
