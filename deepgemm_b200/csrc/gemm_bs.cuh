@@ -133,7 +133,9 @@ struct TileWalker {
         } else {  // psum
             const uint32_t end = layout(group);
             row_start = (prev_end + p.alignment - 1) / p.alignment * p.alignment;
-            group_m_blocks = end > row_start ? (end - row_start + bm - 1) / bm : 0;
+            // Cover the group's whole aligned extent, so that zero padding rows of A give zero rows of D
+            const uint32_t end_aligned = (end + p.alignment - 1) / p.alignment * p.alignment;
+            group_m_blocks = end > row_start ? (end_aligned - row_start + bm - 1) / bm : 0;
             prev_end = end;
         }
     }

@@ -106,3 +106,115 @@ class force_tile:
         from deepgemm_b200 import ops
         ops._force_tile.clear()
         ops._force_tile.update(self.old)
+
+
+# --------------------------------------------------------------------------- grouped generators
+def align_up(x, a):
+    return (x + a - 1) // a * a
+
+
+def make_m_grouped_contiguous(num_groups, expected_m, n, k, *, alignment=128, use_psum=False, b_kind="fp8_block",
+                              gran_a=128, seed=0, device="cuda", scale_b=1.0):
+    """tests/generators.py:378-419 of the reference: ragged groups padded to `alignment` rows,
+    padding rows zero, layout either per-row expert ids (-1 = padding) or cumulative row ends."""
+    import random
+    rnd = random.Random(seed)
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    actual = [int(expected_m * rnd.uniform(0.7, 1.3)) for _ in range(num_groups)]
+    aligned = [align_up(x, alignment) for x in actual]
+    m = sum(aligned)
+    a = torch.randn((m, k), generator=g).to(torch.bfloat16)
+    b = (torch.randn((num_groups, n, k), generator=g) * scale_b).to(torch.bfloat16)
+    layout = torch.empty(num_groups if use_psum else m, dtype=torch.int32)
+    valid = torch.zeros(m, dtype=torch.bool)
+    start = 0
+    for i, (am, al) in enumerate(zip(actual, aligned)):
+        if use_psum:
+            layout[i] = start + am
+        else:
+            layout[start:start + am] = i
+            layout[start + am:start + al] = -1
+        valid[start:start + am] = True
+        a[start + am:start + al] = 0
+        start += al
+    a, b = a.to(device), b.to(device)
+    qa = quant_act(a, gran_a)
+    if b_kind == "fp8_block":
+        qb_list = [quant_weight_fp8_block(b[i]) for i in range(num_groups)]
+        gran_mn_b, gran_b = 128, 128
+    else:
+        qb_list = [quant_weight_fp4(b[i]) for i in range(num_groups)]
+        gran_mn_b, gran_b = 1, 32
+    qb = (torch.stack([q[0] for q in qb_list]), torch.stack([q[1] for q in qb_list]))
+    ref_a = dequant(qa[0], qa[1], 1, gran_a)
+    ref_b = np.stack([dequant(qb_list[i][0], qb_list[i][1], gran_mn_b, gran_b) for i in range(num_groups)])
+    return dict(m=m, a=qa, b=qb, layout=layout.to(device), valid=valid.numpy(), actual=actual, aligned=aligned,
+                grans=(gran_a, gran_mn_b, gran_b), ref_a=ref_a, ref_b=ref_b)
+
+
+def ref_m_grouped(case) -> np.ndarray:
+    """Oracle output on the valid rows' groups (padding rows stay zero)."""
+    ids = np.full(case["m"], -1, dtype=np.int64)
+    start = 0
+    for i, (am, al) in enumerate(zip(case["actual"], case["aligned"])):
+        ids[start:start + am] = i
+        start += al
+    return OG.m_grouped_contiguous(case["ref_a"], case["ref_b"], ids)
+
+
+def make_masked(num_groups, max_m, expected_m, n, k, *, b_kind="fp8_block", gran_a=128, seed=0, device="cuda",
+                scale_b=1.0):
+    """tests/generators.py:446-485 of the reference."""
+    import random
+    rnd = random.Random(seed)
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    a = torch.randn((num_groups, max_m, k), generator=g).to(torch.bfloat16).to(device)
+    b = (torch.randn((num_groups, n, k), generator=g) * scale_b).to(torch.bfloat16).to(device)
+    masked = torch.tensor([min(max_m, int(expected_m * rnd.uniform(0.5, 1.5))) for _ in range(num_groups)],
+                          dtype=torch.int32)
+    qa_list = [quant_act(a[i], gran_a) for i in range(num_groups)]
+    qa = (torch.stack([q[0] for q in qa_list]), torch.stack([q[1] for q in qa_list]))
+    for i in range(num_groups):
+        qa[1][i, int(masked[i]):] = 0          # scale rows beyond the valid count are zero
+    if b_kind == "fp8_block":
+        qb_list = [quant_weight_fp8_block(b[i]) for i in range(num_groups)]
+        gran_mn_b, gran_b = 128, 128
+    else:
+        qb_list = [quant_weight_fp4(b[i]) for i in range(num_groups)]
+        gran_mn_b, gran_b = 1, 32
+    qb = (torch.stack([q[0] for q in qb_list]), torch.stack([q[1] for q in qb_list]))
+    ref_a = np.stack([dequant(qa_list[i][0], qa_list[i][1], 1, gran_a) for i in range(num_groups)])
+    ref_b = np.stack([dequant(qb_list[i][0], qb_list[i][1], gran_mn_b, gran_b) for i in range(num_groups)])
+    return dict(a=qa, b=qb, masked=masked.to(device), masked_cpu=masked.numpy(), grans=(gran_a, gran_mn_b, gran_b),
+                ref_a=ref_a, ref_b=ref_b)
+
+
+def make_k_grouped(num_groups, m, n, ks, *, gran_k=128, seed=0, device="cuda"):
+    """tests/generators.py:527-608 of the reference (non-psum): A [sum_k, m], B [sum_k, n], per-channel scales."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    total = sum(ks)
+    a = torch.randn((total, m), generator=g).to(torch.bfloat16).to(device)
+    b = torch.randn((total, n), generator=g).to(torch.bfloat16).to(device)
+    qa_d, qa_s, qb_d, qb_s = [], [], [], []
+    off = 0
+    for kk in ks:
+        if kk == 0:
+            continue
+        da, sa = M.per_channel_cast_to_fp8(a[off:off + kk], True, gran_k)
+        db, sb = M.per_channel_cast_to_fp8(b[off:off + kk], True, gran_k)
+        qa_d.append(da), qa_s.append(sa), qb_d.append(db), qb_s.append(sb)
+        off += kk
+    qa = (torch.cat(qa_d), torch.cat(qa_s))
+    qb = (torch.cat(qb_d), torch.cat(qb_s))
+
+    def deq(d, s):
+        # per-channel: scale row r covers K rows [r*gran_k, (r+1)*gran_k)
+        dn = OQ.e4m3_bits_to_f32(to_np(d))
+        sn = to_np(s)
+        return dn * np.repeat(sn, gran_k, axis=0)
+
+    bounds, off = [], 0
+    for kk in ks:
+        bounds.append((off, off + kk))
+        off += kk
+    return dict(a=qa, b=qb, ref_a=deq(*qa), ref_b=deq(*qb), bounds=bounds)
