@@ -1,0 +1,407 @@
+"""Benchmark of the block-scaled GEMM hot path (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--all-configs]
+
+A step is one pass of the hot path over one batch of synthetic input.  The headline workload is
+the contiguous M-grouped FP8 GEMM (8 experts, N=4096, K=7168, rows per expert uniform in
+[0.7, 1.3] x 8192 padded to 128): seeded BF16 normal tensors quantised 1x128 (activations) and
+128x128 (weights) to E4M3 with UE8M0 scales, scale factors pre-packed.  Inputs (about 1.2 GB)
+are larger than L2, so consecutive timed steps do not find their operands cached.
+
+`value`   : TFLOPS of the kernel with inputs resident in HBM (CUDA events on the launch stream).
+`e2e`     : the same metric through the public operator with HOST buffers: pinned activations,
+            scales and layout are copied in, the BF16 result is copied out, every step.
+`roofline`: tensor-core bound; achieved = 2 * M_valid * N * K / kernel time; peak = 2 x the
+            measured dense BF16 figure of MEASURED_PEAKS.json (FP8 UMMA issues at twice the BF16
+            rate), fallback 2 x 1590 TFLOPS when that file is absent.
+`cpu_baseline`: the CPU oracle (dequantise + float32 BLAS matmul) timed on a bounded sample.
+
+With --gpus N > 1 the GEMM does not shard (no exchange step): N independent replicas run, one
+per GPU, and `value` is the aggregate.  --impl reference times the reference's only CPU-runnable
+formulation of this path (dequantise-then-matmul, here the oracle port) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+NOMINAL_FP8_TFLOPS = 4500.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return dict(bf16=float(p["bf16_tflops"]), bf16_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                    hbm=float(p["hbm_gbs"]), source="measured")
+    except Exception:
+        return dict(bf16=1590.0, bf16_sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled during the timed region."""
+
+    def __init__(self, gpu_index: int):
+        self.samples, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            parts = [x.strip() for x in s.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                mhz.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+# --------------------------------------------------------------------------- workloads
+def make_c2(device, seed=0):
+    """Contiguous M-grouped FP8 GEMM of BASELINE config 2 (tests/generators.py:378-419 of the reference)."""
+    import torch
+    import deepgemm_b200 as dg
+    rnd = random.Random(seed)
+    torch.manual_seed(seed)
+    groups, n, k, alignment = 8, 4096, 7168, 128
+    actual = [int(8192 * rnd.uniform(0.7, 1.3)) for _ in range(groups)]
+    aligned = [(x + alignment - 1) // alignment * alignment for x in actual]
+    m = sum(aligned)
+    layout = torch.full((m,), -1, dtype=torch.int32)
+    start = 0
+    for i, (am, al) in enumerate(zip(actual, aligned)):
+        layout[start:start + am] = i
+        start += al
+    a_q = torch.empty((m, k), dtype=torch.float8_e4m3fn, device=device)
+    a_sf = torch.empty((m, k // 128), dtype=torch.float32, device=device)
+    start = 0
+    for am, al in zip(actual, aligned):                       # quantise per group to bound temporaries
+        x = torch.randn((al, k), device=device, dtype=torch.bfloat16)
+        x[am:] = 0
+        q, s = dg.utils.per_token_cast_to_fp8(x, True, 128)
+        a_q[start:start + al], a_sf[start:start + al] = q, s
+        start += al
+    b_q = torch.empty((groups, n, k), dtype=torch.float8_e4m3fn, device=device)
+    b_sf = torch.empty((groups, n // 128, k // 128), dtype=torch.float32, device=device)
+    for g in range(groups):
+        w = torch.randn((n, k), device=device, dtype=torch.bfloat16)
+        b_q[g], b_sf[g] = dg.utils.per_block_cast_to_fp8(w, True, 128)
+    sfa = dg.transform_sf_into_required_layout(a_sf, m, k, (1, 128))
+    sfb = dg.transform_sf_into_required_layout(b_sf, n, k, (128, 128), num_groups=groups)
+    layout = layout.to(device)
+    d = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+    flops = 2.0 * sum(actual) * n * k
+    cfg = dict(workload="m_grouped_fp8_gemm_nt_contiguous (BASELINE config 2)", groups=groups, m=m,
+               m_valid=sum(actual), n=n, k=k, alignment=alignment, a="e4m3 1x128 UE8M0", b="e4m3 128x128 UE8M0",
+               out="bf16", sf="pre-packed int32", l2="inputs (1.2 GB) larger than L2")
+    return dict(a=(a_q, sfa), b=(b_q, sfb), a_fp32_sf=a_sf, b_fp32_sf=b_sf, layout=layout, d=d, flops=flops, cfg=cfg,
+                actual=actual, aligned=aligned)
+
+
+def run_c2(w):
+    import deepgemm_b200 as dg
+    dg.m_grouped_fp8_gemm_nt_contiguous(w["a"], w["b"], w["d"], w["layout"], recipe_a=(1, 128), recipe_b=(1, 128))
+
+
+def time_steps(fn, steps, warmup, flush=None):
+    """Per-step device times (ms) with CUDA events on the current stream."""
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(steps):
+        if flush is not None:
+            flush.zero_()
+        torch.cuda._sleep(200000)          # cover the host's enqueue latency: time the kernel, not the launch
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        e.synchronize()
+        times.append(s.elapsed_time(e))
+    return times
+
+
+def other_configs(device, steps, warmup):
+    """Kernel-only TFLOPS of the other single-GPU BASELINE configs (dense FP8, masked, FP8xFP4)."""
+    import torch
+    import deepgemm_b200 as dg
+    out = {}
+    flush = torch.empty(int(256e6), dtype=torch.int8, device=device)
+    torch.manual_seed(0)
+    # C1 dense 4096 x 4096 x 7168
+    m, n, k = 4096, 4096, 7168
+    a = dg.utils.per_token_cast_to_fp8(torch.randn((m, k), device=device, dtype=torch.bfloat16), True, 128)
+    b = dg.utils.per_block_cast_to_fp8(torch.randn((n, k), device=device, dtype=torch.bfloat16), True, 128)
+    sfa = dg.transform_sf_into_required_layout(a[1], m, k, (1, 128))
+    sfb = dg.transform_sf_into_required_layout(b[1], n, k, (128, 128))
+    d = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+    t = time_steps(lambda: dg.fp8_gemm_nt((a[0], sfa), (b[0], sfb), d, recipe_a=(1, 128), recipe_b=(1, 128)),
+                   steps, warmup, flush)
+    ms = sorted(t)[len(t) // 2]
+    out["c1_dense_fp8_4096x4096x7168"] = dict(ms=ms, tflops=2.0 * m * n * k / ms / 1e9)
+    # C4 FP8 x FP4 8192 x 7168 x 2048
+    m, n, k = 8192, 7168, 2048
+    a = dg.utils.per_token_cast_to_fp8(torch.randn((m, k), device=device, dtype=torch.bfloat16), True, 128)
+    b = dg.utils.per_token_cast_to_fp4(torch.randn((n, k), device=device, dtype=torch.bfloat16) * 0.02, True, 32)
+    sfa = dg.transform_sf_into_required_layout(a[1], m, k, (1, 128))
+    sfb = dg.transform_sf_into_required_layout(b[1], n, k, (1, 32))
+    d = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+    t = time_steps(lambda: dg.fp8_fp4_gemm_nt((a[0], sfa), (b[0], sfb), d, recipe_a=(1, 128), recipe_b=(1, 32)),
+                   steps, warmup, flush)
+    ms = sorted(t)[len(t) // 2]
+    out["c4_fp8xfp4_8192x7168x2048"] = dict(ms=ms, tflops=2.0 * m * n * k / ms / 1e9)
+    # C3 masked: 16 experts, max_m 1024, expected 256
+    g, max_m, n, k = 16, 1024, 4096, 7168
+    rnd = random.Random(0)
+    masked = [min(max_m, int(256 * rnd.uniform(0.5, 1.5))) for _ in range(g)]
+    a_q = torch.empty((g, max_m, k), dtype=torch.float8_e4m3fn, device=device)
+    a_s = torch.empty((g, max_m, k // 128), dtype=torch.float32, device=device)
+    b_q = torch.empty((g, n, k), dtype=torch.float8_e4m3fn, device=device)
+    b_s = torch.empty((g, n // 128, k // 128), dtype=torch.float32, device=device)
+    for i in range(g):
+        a_q[i], a_s[i] = dg.utils.per_token_cast_to_fp8(torch.randn((max_m, k), device=device, dtype=torch.bfloat16), True, 128)
+        a_s[i, masked[i]:] = 0
+        b_q[i], b_s[i] = dg.utils.per_block_cast_to_fp8(torch.randn((n, k), device=device, dtype=torch.bfloat16), True, 128)
+    sfa = dg.transform_sf_into_required_layout(a_s, max_m, k, (1, 128), num_groups=g)
+    sfb = dg.transform_sf_into_required_layout(b_s, n, k, (128, 128), num_groups=g)
+    mm = torch.tensor(masked, dtype=torch.int32, device=device)
+    d = torch.empty((g, max_m, n), dtype=torch.bfloat16, device=device)
+    t = time_steps(lambda: dg.m_grouped_fp8_gemm_nt_masked((a_q, sfa), (b_q, sfb), d, mm, 256, recipe_a=(1, 128),
+                                                           recipe_b=(1, 128)), steps, warmup, flush)
+    ms = sorted(t)[len(t) // 2]
+    valid = sum(masked)
+    nbytes = (a_q.numel() + d.numel() * 2) * valid / (g * max_m) + b_q.numel()
+    out["c3_masked_16x(256 of 1024)x4096x7168"] = dict(ms=ms, tflops=2.0 * valid * n * k / ms / 1e9,
+                                                       gbs=nbytes / ms / 1e6)
+    return out
+
+
+def cpu_baseline_sample(w, rows=2048):
+    """Oracle port on the host: dequantise the first `rows` rows of expert 0 and its weights, float32 matmul."""
+    import numpy as np
+    import torch
+    from oracle import gemm as OG
+    n, k = w["cfg"]["n"], w["cfg"]["k"]
+    rows = min(rows, w["actual"][0])
+    a_bits = w["a"][0][:rows].cpu().view(torch.uint8).numpy()
+    a_sf = w["a_fp32_sf"][:rows].cpu().numpy()
+    b_bits = w["b"][0][0].cpu().view(torch.uint8).numpy()
+    b_sf = w["b_fp32_sf"][0].cpu().numpy()
+    threads = torch.get_num_threads()
+    t0 = time.perf_counter()
+    a = OG.dequant_operand(a_bits, a_sf, 1, 128, False)
+    b = OG.dequant_operand(b_bits, b_sf, 128, 128, False)
+    d = OG.gemm_nt_f32(a, b)
+    dt = time.perf_counter() - t0
+    flops = 2.0 * rows * n * k
+    return dict(value=flops / dt / 1e12, unit="TFLOPS", cores=threads, kind="port",
+                sample=f"expert 0, first {rows} rows x N={n} x K={k}: dequantise + float32 BLAS matmul, {dt:.2f} s"), d, rows
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--all-configs", action="store_true", help="also time the other single-GPU configs")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    import deepgemm_b200 as dg
+
+    w = make_c2(device, seed=0)
+    peaks = measured_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- kernel-only: inputs resident in HBM
+    sampler = ClockSampler(local_rank)
+    for _ in range(args.warmup):
+        run_c2(w)
+    barrier()
+    sampler.start()
+    times = time_steps(lambda: run_c2(w), args.steps, 0)
+    barrier()
+    clocks = sampler.stop()
+    dg.check_status()
+    total_ms = sum(times)
+    t = torch.tensor([total_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+    value = world * w["flops"] / ms_per_step / 1e9
+
+    # ---- end to end through the public operator with host buffers
+    a_host = w["a"][0].view(torch.uint8).cpu().pin_memory()
+    sfa_store = torch.empty(w["a"][1].size(1) * w["a"][1].stride(1), dtype=torch.int32, device=device)
+    sfa_dev = sfa_store.as_strided(w["a"][1].shape, w["a"][1].stride())
+    sfa_dev.copy_(w["a"][1])
+    sfa_host = sfa_store.cpu().pin_memory()
+    layout_host = w["layout"].cpu().pin_memory()
+    d_host = torch.empty(w["d"].shape, dtype=torch.bfloat16).pin_memory()
+    a_dev = torch.empty_like(w["a"][0])
+    layout_dev = torch.empty_like(w["layout"])
+
+    def e2e_step():
+        a_dev.view(torch.uint8).copy_(a_host, non_blocking=True)
+        sfa_store.copy_(sfa_host, non_blocking=True)
+        layout_dev.copy_(layout_host, non_blocking=True)
+        dg.m_grouped_fp8_gemm_nt_contiguous((a_dev, sfa_dev), w["b"], w["d"], layout_dev, recipe_a=(1, 128),
+                                            recipe_b=(1, 128))
+        d_host.copy_(w["d"], non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e.record()
+    barrier()
+    e2e_ms = torch.tensor([s.elapsed_time(e) / e2e_steps], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_value = world * w["flops"] / float(e2e_ms.item()) / 1e9
+    h2d = a_host.numel() + sfa_host.numel() * 4 + layout_host.numel() * 4
+    d2h = d_host.numel() * 2
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- checks and baselines (rank 0)
+    cpu, d_cpu, rows = cpu_baseline_sample(w) if world == 1 else (None, None, 0)
+    parity = None
+    if d_cpu is not None:
+        from oracle.quant import calc_diff
+        parity = calc_diff(w["d"][:rows].float().cpu().numpy(), d_cpu)
+    kernel_ms = sorted(times)[len(times) // 2]
+    achieved = w["flops"] / kernel_ms / 1e9
+    peak = 2.0 * peaks["bf16"]
+    extra = other_configs(device, min(args.steps, 10), args.warmup) if (args.all_configs or world == 1) else {}
+    line = {
+        "metric": "fp8_fp4_gemm_tflops", "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate, bf16 out)", "data": "synthetic",
+        "config": dict(w["cfg"], replicas=world, parallelism="replicas only (no exchange step)"),
+        "e2e": {"value": e2e_value, "unit": "TFLOPS", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": float(e2e_ms.item())},
+        "gpu_launches": args.steps,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "peak_source": f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']}); FP8 UMMA issues at twice the BF16 rate",
+                     "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
+                     "frac_of_2x_bf16_sustained": achieved / (2.0 * peaks["bf16_sustained"]),
+                     "traffic": None, "kernel_ms": kernel_ms},
+        "cpu_baseline": cpu,
+        "clocks": clocks,
+        "parity_calc_diff_vs_cpu_oracle": parity,
+        "other_configs": extra,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def reference_arm(args):
+    """The reference's CPU-runnable formulation of the path (dequantise, then matmul) on the host cores."""
+    import numpy as np
+    import torch
+    from oracle import gemm as OG
+    from oracle import quant as OQ
+    groups, n, k = 8, 4096, 7168
+    rows = 2048
+    rng = np.random.default_rng(0)
+    x = OQ.bf16_round(rng.standard_normal((rows, k), dtype=np.float32))
+    wt = OQ.bf16_round(rng.standard_normal((n, k), dtype=np.float32))
+    a_bits, a_sf = OQ.per_token_cast_to_fp8(x, True, 128)
+    b_bits, b_sf = OQ.per_block_cast_to_fp8(wt, True, 128)
+    threads = torch.get_num_threads()
+
+    def step():
+        a = OG.dequant_operand(a_bits, a_sf, 1, 128, False)
+        b = OG.dequant_operand(b_bits, b_sf, 128, 128, False)
+        return OG.gemm_nt_f32(a, b)
+
+    for _ in range(min(args.warmup, 1)):
+        step()
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    value = 2.0 * rows * n * k / dt / 1e12
+    sample = f"{rows} rows of one expert x N={n} x K={k} per step (dequantise + float32 BLAS matmul), {steps} steps"
+    line = {
+        "impl": "reference", "metric": "fp8_fp4_gemm_tflops", "value": value, "unit": "TFLOPS", "n_gpus": args.gpus,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "float32 on host", "data": "synthetic",
+        "config": dict(workload="m_grouped_fp8_gemm_nt_contiguous (BASELINE config 2)", groups=groups, n=n, k=k,
+                       note="the reference has no CPU GEMM; this is its tests' dequantise-then-matmul on a bounded sample"),
+        "cpu_baseline": {"value": value, "unit": "TFLOPS", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -112,3 +112,9 @@ def k_grouped_tn(a: np.ndarray, b: np.ndarray, group_bounds: Sequence[tuple],
             acc = acc + c[g].astype(np.float64)
         out[g] = acc
     return to_cd(out, cd_dtype)
+
+
+def gemm_nt_f32(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """float32 BLAS contraction of dequantised operands: the timed CPU baseline (the reference's
+    tests contract in float32 too, tests/generators.py:363); BF16-rounded like the kernels' output."""
+    return bf16_round(np.asarray(a, dtype=np.float32) @ np.asarray(b, dtype=np.float32).T)
