@@ -45,6 +45,7 @@ enum WaitSite : uint32_t {
     kSiteMmaTmemEmpty = 3,
     kSiteMmaFull = 4,
     kSiteEpilogueTmemFull = 5,
+    kSiteMmaOverlap = 6,
 };
 
 // One UMMA operand as the kernel sees it (all values computed on the host).
@@ -78,6 +79,7 @@ struct GemmParams {
     float alpha;
     uint32_t accumulate;        // D += result (TMA reduce-add) instead of D = result
     uint32_t d_grouped;         // D has a group axis (masked / K-grouped): third store coordinate = group
+    uint32_t split_blocks;      // contiguous layout: a schedule slot spans two alignment units (may straddle experts)
     uint32_t timeout_ms;
     uint32_t* status;           // 16 words: [0] code, [1] site, [2] block, [3] tile iter, [4] k block, [5] stage
     unsigned long long* trace;  // optional clock samples of block 0's first tile (builds with DG_TRACE only)
@@ -93,27 +95,35 @@ struct GemmParams {
 #define DG_TRACE_AT(role, kb_) do { } while (0)
 #endif
 
+// One accumulator tile, in GEMM terms.
 struct TileCoord {
-    uint32_t m_blk, n_blk, group;
+    uint32_t row0;    // first GEMM-M row of the tile (inside its group for masked layouts)
+    uint32_t rows;    // swapped tiles: token rows covered = UMMA N (multiple of 16); plain tiles: unused
+    uint32_t n_blk, group;
     uint32_t k_start, k_len, sfk_base;
 };
 
-// Persistent tile walk shared by all roles: each role thread owns one instance and asks
-// for tile indices unit, unit + num_units, ...
+// Persistent tile walk shared by all roles: each role thread owns one instance and asks for the
+// schedule slots unit, unit + num_units, ...  A slot yields one tile, or two where a token block
+// of a contiguous layout straddles two experts (each half is then its own tile).
 struct TileWalker {
     const GemmParams& p;
-    const uint32_t bm, bn;   // GEMM-level tile extents of one unit
+    const uint32_t bm, bn;   // GEMM-level extents of one schedule slot
+    const bool swap;
     uint32_t group = 0;
     uint32_t m_blk_cum = 0;       // m-blocks of the groups before `group`
     uint32_t group_m_blocks = 0;  // m-blocks of `group`
+    uint32_t group_rows = 0;      // rows of `group` to cover (masked: valid rows; psum: aligned extent)
     uint32_t row_start = 0;       // psum: first row of `group`
     uint32_t prev_end = 0;        // psum: unaligned end of the previous group
     uint32_t k_start = 0, k_len = 0, sfk_base = 0;
     bool primed = false;
 
-    __device__ TileWalker(const GemmParams& p_, uint32_t bm_, uint32_t bn_) : p(p_), bm(bm_), bn(bn_) {}
+    __device__ TileWalker(const GemmParams& p_, uint32_t bm_, uint32_t bn_, bool swap_)
+        : p(p_), bm(bm_), bn(bn_), swap(swap_) {}
 
-    __device__ uint32_t layout(uint32_t i) const { return static_cast<uint32_t>(__ldg(p.grouped_layout + i)); }
+    __device__ int32_t layout(uint32_t i) const { return __ldg(p.grouped_layout + i); }
+    __device__ static uint32_t align16(uint32_t x) { return (x + 15u) & ~15u; }
 
     __device__ void swizzle(uint32_t idx, uint32_t num_m, uint32_t num_n, uint32_t& m_blk, uint32_t& n_blk) const {
         // Super-rows of `raster` m-blocks; inside one, n varies slowest so that concurrently
@@ -129,38 +139,58 @@ struct TileWalker {
 
     __device__ void load_group_m() {
         if (p.gemm_type == kGemmMMasked) {
-            group_m_blocks = (layout(group) + bm - 1) / bm;
-        } else {  // psum
-            const uint32_t end = layout(group);
+            group_rows = static_cast<uint32_t>(layout(group));
+        } else {  // psum: cover the group's whole aligned extent, so zero padding rows of A give zero rows of D
+            const uint32_t end = static_cast<uint32_t>(layout(group));
             row_start = (prev_end + p.alignment - 1) / p.alignment * p.alignment;
-            // Cover the group's whole aligned extent, so that zero padding rows of A give zero rows of D
             const uint32_t end_aligned = (end + p.alignment - 1) / p.alignment * p.alignment;
-            group_m_blocks = end > row_start ? (end_aligned - row_start + bm - 1) / bm : 0;
+            group_rows = end > row_start ? end_aligned - row_start : 0;
             prev_end = end;
         }
+        group_m_blocks = (group_rows + bm - 1) / bm;
     }
     __device__ void load_group_k() {
         if (p.gemm_type == kGemmKGroupedPsum) {
-            const uint32_t end = layout(group);
+            const uint32_t end = static_cast<uint32_t>(layout(group));
             k_start = (prev_end + p.alignment - 1) / p.alignment * p.alignment;
             k_len = end - k_start;
             prev_end = end;
         } else {
-            k_len = layout(group);
+            k_len = static_cast<uint32_t>(layout(group));
         }
     }
 
-    __device__ bool next(uint32_t t, TileCoord& tc) {
-        tc.k_start = 0, tc.k_len = p.k, tc.sfk_base = 0, tc.group = 0;
+    // Fills tc[0..return) for schedule slot t; 0 means the walk is over.
+    __device__ uint32_t next(uint32_t t, TileCoord* tc) {
+        TileCoord& c = tc[0];
+        c.k_start = 0, c.k_len = p.k, c.sfk_base = 0, c.group = 0, c.rows = bm;
         const uint32_t num_n = p.num_n_blocks;
+        uint32_t m_blk;
         if (p.gemm_type == kGemmNormal || p.gemm_type == kGemmMContiguous) {
-            if (t >= p.num_m_blocks * num_n) return false;
-            swizzle(t, p.num_m_blocks, num_n, tc.m_blk, tc.n_blk);
-            if (p.gemm_type == kGemmMContiguous) {
-                const int32_t g = static_cast<int32_t>(layout(tc.m_blk * bm));
-                tc.group = g < 0 ? 0u : static_cast<uint32_t>(g);
+            if (t >= p.num_m_blocks * num_n) return 0;
+            swizzle(t, p.num_m_blocks, num_n, m_blk, c.n_blk);
+            c.row0 = m_blk * bm;
+            if (swap) c.rows = min(bm, align16(p.m - c.row0));
+            if (p.gemm_type == kGemmNormal) return 1;
+            const int32_t g0 = layout(c.row0);
+            c.group = g0 < 0 ? 0u : static_cast<uint32_t>(g0);
+            if (!p.split_blocks) return 1;
+            // The slot spans two alignment units: one tile if they belong to one expert, else two
+            const uint32_t half = bm / 2, row1 = c.row0 + half;
+            if (row1 >= p.m) {
+                c.rows = half;
+                return 1;
             }
-            return true;
+            const int32_t g1 = layout(row1);
+            if (g1 < 0 || g1 == g0) return 1;          // same expert, or the second unit is pure padding
+            if (g0 < 0) {                              // first unit is pure padding: use the second's expert
+                c.group = static_cast<uint32_t>(g1);
+                return 1;
+            }
+            tc[1] = c;
+            c.rows = half;
+            tc[1].row0 = row1, tc[1].rows = min(half, align16(p.m - row1)), tc[1].group = static_cast<uint32_t>(g1);
+            return 2;
         }
         if (p.gemm_type == kGemmMMasked || p.gemm_type == kGemmMPsum) {
             if (!primed) {
@@ -168,14 +198,16 @@ struct TileWalker {
                 load_group_m();
             }
             while (t >= (m_blk_cum + group_m_blocks) * num_n) {
-                if (++group >= p.num_groups) return false;
+                if (++group >= p.num_groups) return 0;
                 m_blk_cum += group_m_blocks;
                 load_group_m();
             }
-            swizzle(t - m_blk_cum * num_n, group_m_blocks, num_n, tc.m_blk, tc.n_blk);
-            if (p.gemm_type == kGemmMPsum) tc.m_blk += row_start / bm;
-            tc.group = group;
-            return true;
+            swizzle(t - m_blk_cum * num_n, group_m_blocks, num_n, m_blk, c.n_blk);
+            const uint32_t in_group = m_blk * bm;
+            c.row0 = in_group + (p.gemm_type == kGemmMPsum ? row_start : 0);
+            if (swap) c.rows = min(bm, align16(group_rows - in_group));
+            c.group = group;
+            return 1;
         }
         // K-grouped: every group owns a full m x n tile grid and its own K range.
         const uint32_t per_group = p.num_m_blocks * num_n;
@@ -184,16 +216,17 @@ struct TileWalker {
             load_group_k();
         }
         while (t >= (group + 1) * per_group) {
-            if (++group >= p.num_groups) return false;
+            if (++group >= p.num_groups) return 0;
             const uint32_t aligned = (k_len + p.alignment - 1) / p.alignment * p.alignment;
             sfk_base += (aligned + p.r.gran_k * 4 - 1) / (p.r.gran_k * 4);
             if (p.gemm_type == kGemmKGrouped) k_start += k_len;
             load_group_k();
         }
-        if (group >= p.num_groups) return false;
-        swizzle(t - group * per_group, p.num_m_blocks, num_n, tc.m_blk, tc.n_blk);
-        tc.group = group, tc.k_start = k_start, tc.k_len = k_len, tc.sfk_base = sfk_base;
-        return true;
+        if (group >= p.num_groups) return 0;
+        swizzle(t - group * per_group, p.num_m_blocks, num_n, m_blk, c.n_blk);
+        c.row0 = m_blk * bm;
+        c.group = group, c.k_start = k_start, c.k_len = k_len, c.sfk_base = sfk_base;
+        return 1;
     }
 };
 
@@ -232,17 +265,23 @@ struct GemmConfig {
     static_assert(kStages >= 3, "pipeline too shallow");
     static constexpr uint32_t kSmemBytes = 1024 + kStages * STAGE_BYTES + CD_BYTES + kBarrierBytes;
 
-    // TMEM columns: accumulator stages, then the scale factors of R (4) and C (BN / 32, >= 4).
+    // TMEM columns: two accumulator stages, then the scale factors of R (4) and C (BN / 32, >= 4).
+    // When 2 BN + scale columns exceed the 512 columns of TMEM the two stages overlap in
+    // kOverlap columns: the last columns of stage 0 are the first columns of stage 1.  The epilogue
+    // drains the shared columns first (stage 0 back to front, stage 1 front to back) and tells the
+    // UMMA issuer, which only then lets the next tile write them.
     static constexpr uint32_t SFC_COLS = SFC_ROWS / 32;
-    static constexpr uint32_t kAccStages = (2 * BN + 4 + SFC_COLS <= 512) ? 2 : 1;
-    static constexpr uint32_t kSfrCol = kAccStages * BN;
+    static constexpr uint32_t kOverlap = (2 * BN + 4 + SFC_COLS > 512) ? 16 : 0;
+    static_assert(kOverlap <= CHUNK_COLS, "the shared columns must lie in one epilogue chunk");
+    static constexpr uint32_t kAccStride = BN - kOverlap;
+    static constexpr uint32_t kSfrCol = 2 * BN - kOverlap;
     static constexpr uint32_t kSfcCol = kSfrCol + 4;
     static constexpr uint32_t kUsedCols = kSfcCol + SFC_COLS;
     static constexpr uint32_t kTmemCols = kUsedCols <= 32 ? 32 : kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128
                                           : kUsedCols <= 256 ? 256 : 512;
     static_assert(kUsedCols <= 512, "TMEM overflow");
 
-    // GEMM-level extents of the tile one unit (CTA or CTA pair) produces.
+    // GEMM-level extents of one schedule slot (CTA or CTA pair).
     static constexpr uint32_t UNIT_M = kSwap ? BN : 128 * kCtas;
     static constexpr uint32_t UNIT_N = kSwap ? 128 * kCtas : BN;
 };
@@ -253,6 +292,7 @@ struct alignas(8) GemmBarriers {
     uint64_t sf_full[10];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
+    uint64_t overlap[2];
     uint32_t tmem_base;
     uint32_t abort;
 };
@@ -271,16 +311,14 @@ __device__ __noinline__ void report_timeout(const GemmParams& p, uint32_t site, 
 }
 
 // Bounded mbarrier wait.  Returns false if the CTA is aborting or the budget ran out.
-template <bool kClusterScope>
 DG_DEVICE bool wait_barrier(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t peer_abort_addr,
                             const GemmParams& p, uint32_t site, uint32_t iter, uint32_t kb, uint32_t stage) {
-    auto poll = [&]() { return kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
-    if (poll()) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     const uint64_t budget = static_cast<uint64_t>(p.timeout_ms) * 1000000ull;
     uint32_t spins = 0;
     while (true) {
-        if (poll()) return true;
+        if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 15u) == 0) {
             if (*abort_flag) return false;
             if (global_timer_ns() - t0 > budget) {
@@ -298,8 +336,8 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
     constexpr int kCtas = Cfg::kCtas;
     constexpr uint32_t BN = Cfg::BN;
     constexpr uint32_t kStages = Cfg::kStages;
-    constexpr uint32_t kAccStages = Cfg::kAccStages;
     constexpr bool kPair = kCtas == 2;
+    constexpr bool kSwap = Cfg::kSwap;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -338,6 +376,7 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
         for (uint32_t i = 0; i < 2; ++i) {
             mbar_init(&bars->tmem_full[i], 1);            // UMMA commit
             mbar_init(&bars->tmem_empty[i], kCtas * 4);   // one lane per epilogue warp
+            mbar_init(&bars->overlap[i], kCtas * 4);
         }
         bars->abort = 0;
         fence_mbar_init();
@@ -361,97 +400,93 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
     const uint32_t sf_mask_r = p.r.gran_k == 128 ? 3 : 0, sf_shift_r = p.r.gran_k == 128 ? 2 : 0;
     const uint32_t sf_mask_c = p.c.gran_k == 128 ? 3 : 0, sf_shift_c = p.c.gran_k == 128 ? 2 : 0;
 
-    // Role loops share: tile iteration, stage / phase bookkeeping.
+    // Shared by the role loops: smem stage / phase bookkeeping and the schedule walk.
     uint32_t stage = 0, phase = 0;
     auto advance = [&]() {
         stage = stage + 1 == kStages ? 0 : stage + 1;
         phase ^= (stage == 0);
     };
+    TileWalker walker(p, Cfg::UNIT_M, Cfg::UNIT_N, kSwap);
+    TileCoord tiles[2];
+    bool ok = true;
+    uint32_t acc_iter = 0;   // accumulator tiles handled so far by this role
 
     if (warp == 0) {
         // ============================================================ TMA producer
         // The whole warp runs the loop (uniform control flow keeps addresses and coordinates in
         // uniform registers); one elected lane issues the copies.
-        {
-            TileWalker walker(p, Cfg::UNIT_M, Cfg::UNIT_N);
-            TileCoord tc;
-            bool ok = true;
-            const uint32_t full_bar0 = leader_addr(&bars->full[0]);
-            const uint32_t stage_tx_bytes = p.r.tx_bytes + p.c.tx_bytes;
-            const uint32_t r_boxes = p.r.num_boxes, r_box_bytes = p.r.box_bytes, r_box_mn = p.r.box_mn;
-            const uint32_t c_boxes = p.c.num_boxes, c_box_bytes = p.c.box_bytes, c_box_mn = p.c.box_mn;
-            const bool r_mn_major = p.r.mn_major != 0, c_mn_major = p.c.mn_major != 0;
-            for (uint32_t iter = 0; ok && walker.next(iter * p.num_units + unit, tc); ++iter) {
+        const uint32_t full_bar0 = leader_addr(&bars->full[0]);
+        const uint32_t stage_tx_bytes = p.r.tx_bytes + p.c.tx_bytes;
+        const uint32_t r_boxes = p.r.num_boxes, r_box_bytes = p.r.box_bytes, r_box_mn = p.r.box_mn;
+        const uint32_t c_boxes = p.c.num_boxes, c_box_bytes = p.c.box_bytes, c_box_mn = p.c.box_mn;
+        const bool r_mn_major = p.r.mn_major != 0, c_mn_major = p.c.mn_major != 0;
+        // Group strides of GEMM A / GEMM B (A is C when swapped)
+        const uint32_t rpg_a = kSwap ? p.rows_per_group_c : p.rows_per_group_r;
+        const uint32_t rpg_b = kSwap ? p.rows_per_group_r : p.rows_per_group_c;
+        const uint32_t kpg_a = kSwap ? p.k_rows_per_group_c : p.k_rows_per_group_r;
+        const uint32_t kpg_b = kSwap ? p.k_rows_per_group_r : p.k_rows_per_group_c;
+        const uint32_t sfg_a = kSwap ? p.sf_groups_c : p.sf_groups_r;
+        const uint32_t sfg_b = kSwap ? p.sf_groups_r : p.sf_groups_c;
+        for (uint32_t iter = 0; ok; ++iter) {
+            const uint32_t num_sub = walker.next(iter * p.num_units + unit, tiles);
+            if (num_sub == 0) break;
+            for (uint32_t sub = 0; sub < num_sub && ok; ++sub, ++acc_iter) {
+                const TileCoord& tc = tiles[sub];
                 // Operand coordinates of this tile (GEMM A / B, then mapped to R / C)
-                const uint32_t a_blk_rows = Cfg::kSwap ? BN : 128 * kCtas;
-                const uint32_t b_blk_rows = Cfg::kSwap ? 128 * kCtas : BN;
-                uint32_t a_mn = tc.m_blk * a_blk_rows, b_mn = tc.n_blk * b_blk_rows;
-                uint32_t a_k = tc.k_start, b_k = tc.k_start;
-                uint32_t sfa_k = tc.sfk_base, sfb_k = tc.sfk_base;
-                const OperandParams& pa = Cfg::kSwap ? p.c : p.r;
-                const OperandParams& pb = Cfg::kSwap ? p.r : p.c;
-                const uint32_t rpg_a = Cfg::kSwap ? p.rows_per_group_c : p.rows_per_group_r;
-                const uint32_t rpg_b = Cfg::kSwap ? p.rows_per_group_r : p.rows_per_group_c;
-                const uint32_t kpg_a = Cfg::kSwap ? p.k_rows_per_group_c : p.k_rows_per_group_r;
-                const uint32_t kpg_b = Cfg::kSwap ? p.k_rows_per_group_r : p.k_rows_per_group_c;
-                const uint32_t sfg_a = Cfg::kSwap ? p.sf_groups_c : p.sf_groups_r;
-                const uint32_t sfg_b = Cfg::kSwap ? p.sf_groups_r : p.sf_groups_c;
-                a_mn += tc.group * rpg_a, a_k += tc.group * kpg_a, sfa_k += tc.group * sfg_a;
-                b_mn += tc.group * rpg_b, b_k += tc.group * kpg_b, sfb_k += tc.group * sfg_b;
+                const uint32_t a_mn = tc.row0 + tc.group * rpg_a, b_mn = tc.n_blk * Cfg::UNIT_N + tc.group * rpg_b;
+                const uint32_t a_k = tc.k_start + tc.group * kpg_a, b_k = tc.k_start + tc.group * kpg_b;
+                const uint32_t sfa_k = tc.sfk_base + tc.group * sfg_a, sfb_k = tc.sfk_base + tc.group * sfg_b;
                 // SF rows are addressed inside the group (the group offset is on the packed-K axis)
-                const uint32_t sfa_mn = tc.m_blk * a_blk_rows, sfb_mn = tc.n_blk * b_blk_rows;
-
-                uint32_t r_mn = Cfg::kSwap ? b_mn : a_mn, c_mn = Cfg::kSwap ? a_mn : b_mn;
-                const uint32_t r_k = Cfg::kSwap ? b_k : a_k, c_k = Cfg::kSwap ? a_k : b_k;
-                uint32_t sfr_mn = Cfg::kSwap ? sfb_mn : sfa_mn;
-                const uint32_t sfc_mn = Cfg::kSwap ? sfa_mn : sfb_mn;
-                const uint32_t sfr_k = Cfg::kSwap ? sfb_k : sfa_k, sfc_k = Cfg::kSwap ? sfa_k : sfb_k;
-                // This CTA's share: its own 128 R rows, its half of the C rows
+                const uint32_t sfa_mn = tc.row0, sfb_mn = tc.n_blk * Cfg::UNIT_N;
+                uint32_t r_mn = kSwap ? b_mn : a_mn, c_mn = kSwap ? a_mn : b_mn;
+                const uint32_t r_k = kSwap ? b_k : a_k, c_k = kSwap ? a_k : b_k;
+                uint32_t sfr_mn = kSwap ? sfb_mn : sfa_mn;
+                const uint32_t sfc_mn = kSwap ? sfa_mn : sfb_mn;
+                const uint32_t sfr_k = kSwap ? sfb_k : sfa_k, sfc_k = kSwap ? sfa_k : sfb_k;
+                // This CTA's share: its own 128 R rows and its half of the C rows the UMMA reads
                 r_mn += cta_rank * 128, sfr_mn += cta_rank * 128;
-                c_mn += cta_rank * Cfg::C_ROWS_PER_CTA;
-                (void)pa, (void)pb;
+                c_mn += cta_rank * ((kSwap ? tc.rows : BN) / kCtas);
 
                 const uint32_t num_kb = max(1u, (tc.k_len + 127u) / 128u);
                 for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
                     DG_TRACE_AT(0, kb);
-                    ok = wait_barrier<false>(&bars->empty[stage], phase ^ 1, abort_flag, peer_abort, p,
-                                             kSiteProducerEmpty, iter, kb, stage);
+                    ok = wait_barrier(&bars->empty[stage], phase ^ 1, abort_flag, peer_abort, p, kSiteProducerEmpty,
+                                      acc_iter, kb, stage);
                     if (!ok) break;
                     DG_TRACE_AT(1, kb);
                     if (elect_one()) {
-                    // Scale factors first: the transposer works while the operand tiles are in flight
-                    uint32_t sf_bytes = 0;
-                    const uint32_t sf_bar = smem_u32(&bars->sf_full[stage]);
-                    if ((kb & sf_mask_r) == 0) {
-                        tma_load_2d<false>(smem_sfr + stage * Cfg::SFR_STAGE, &p.tm_sfr, sf_bar,
-                                           static_cast<int32_t>(sfr_mn),
-                                           static_cast<int32_t>(sfr_k + (kb >> sf_shift_r)));
-                        sf_bytes += Cfg::SFR_STAGE;
-                    }
-                    if ((kb & sf_mask_c) == 0) {
-                        tma_load_2d<false>(smem_sfc + stage * Cfg::SFC_STAGE, &p.tm_sfc, sf_bar,
-                                           static_cast<int32_t>(sfc_mn),
-                                           static_cast<int32_t>(sfc_k + (kb >> sf_shift_c)));
-                        sf_bytes += Cfg::SFC_STAGE;
-                    }
-                    mbar_arrive_expect_tx(&bars->sf_full[stage], sf_bytes);
-
-                    // Operand tiles land on the leader's barrier (both CTAs of a pair feed one UMMA)
-                    const uint32_t full_bar = full_bar0 + stage * 8;
-                    mbar_arrive_expect_tx_cluster(full_bar, stage_tx_bytes);
-                    const uint32_t kr = r_k + kb * 128, kc = c_k + kb * 128;
-                    for (uint32_t b = 0; b < r_boxes; ++b) {
-                        const uint32_t dst = smem_r + stage * Cfg::R_STAGE + b * r_box_bytes;
-                        const uint32_t mn = r_mn + b * r_box_mn;
-                        if (r_mn_major) tma_load_2d<kPair>(dst, &p.tm_r, full_bar, mn, kr);
-                        else              tma_load_2d<kPair>(dst, &p.tm_r, full_bar, kr, mn);
-                    }
-                    for (uint32_t b = 0; b < c_boxes; ++b) {
-                        const uint32_t dst = smem_c + stage * Cfg::C_STAGE + b * c_box_bytes;
-                        const uint32_t mn = c_mn + b * c_box_mn;
-                        if (c_mn_major) tma_load_2d<kPair>(dst, &p.tm_c, full_bar, mn, kc);
-                        else              tma_load_2d<kPair>(dst, &p.tm_c, full_bar, kc, mn);
-                    }
+                        // Scale factors first: the transposer works while the operand tiles are in flight
+                        uint32_t sf_bytes = 0;
+                        const uint32_t sf_bar = smem_u32(&bars->sf_full[stage]);
+                        if ((kb & sf_mask_r) == 0) {
+                            tma_load_2d<false>(smem_sfr + stage * Cfg::SFR_STAGE, &p.tm_sfr, sf_bar,
+                                               static_cast<int32_t>(sfr_mn),
+                                               static_cast<int32_t>(sfr_k + (kb >> sf_shift_r)));
+                            sf_bytes += Cfg::SFR_STAGE;
+                        }
+                        if ((kb & sf_mask_c) == 0) {
+                            tma_load_2d<false>(smem_sfc + stage * Cfg::SFC_STAGE, &p.tm_sfc, sf_bar,
+                                               static_cast<int32_t>(sfc_mn),
+                                               static_cast<int32_t>(sfc_k + (kb >> sf_shift_c)));
+                            sf_bytes += Cfg::SFC_STAGE;
+                        }
+                        mbar_arrive_expect_tx(&bars->sf_full[stage], sf_bytes);
+                        // Operand tiles land on the leader's barrier (both CTAs of a pair feed one UMMA)
+                        const uint32_t full_bar = full_bar0 + stage * 8;
+                        mbar_arrive_expect_tx_cluster(full_bar, stage_tx_bytes);
+                        const uint32_t kr = r_k + kb * 128, kc = c_k + kb * 128;
+                        for (uint32_t b = 0; b < r_boxes; ++b) {
+                            const uint32_t dst = smem_r + stage * Cfg::R_STAGE + b * r_box_bytes;
+                            const uint32_t mn = r_mn + b * r_box_mn;
+                            if (r_mn_major) tma_load_2d<kPair>(dst, &p.tm_r, full_bar, mn, kr);
+                            else            tma_load_2d<kPair>(dst, &p.tm_r, full_bar, kr, mn);
+                        }
+                        for (uint32_t b = 0; b < c_boxes; ++b) {
+                            const uint32_t dst = smem_c + stage * Cfg::C_STAGE + b * c_box_bytes;
+                            const uint32_t mn = c_mn + b * c_box_mn;
+                            if (c_mn_major) tma_load_2d<kPair>(dst, &p.tm_c, full_bar, mn, kc);
+                            else            tma_load_2d<kPair>(dst, &p.tm_c, full_bar, kc, mn);
+                        }
                     }
                     __syncwarp();
                 }
@@ -462,9 +497,6 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
         // Whole warp in the loop, one elected lane issues (always the same lane, so that
         // tcgen05.commit covers every UMMA issued before it).
         if (is_leader) {
-            TileWalker walker(p, Cfg::UNIT_M, Cfg::UNIT_N);
-            TileCoord tc;
-            bool ok = true;
             const uint32_t idesc_base = make_idesc_mxf8f6f4(p.r.fmt, p.c.fmt, p.r.mn_major != 0, p.c.mn_major != 0,
                                                             128 * kCtas, BN);
             const uint64_t sf_desc_hi = make_smem_desc(0, 0, 128, kSwizzleNone);
@@ -474,183 +506,210 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
             const uint32_t r_lo0 = static_cast<uint32_t>(make_smem_desc(smem_r, p.r.desc_lbo, p.r.desc_sbo, kSwizzle128B));
             const uint32_t c_lo0 = static_cast<uint32_t>(make_smem_desc(smem_c, p.c.desc_lbo, p.c.desc_sbo, kSwizzle128B));
             const uint32_t r_kstep = p.r.desc_kstep >> 4, c_kstep = p.c.desc_kstep >> 4;
-            const bool r_per32 = p.r.gran_k == 32, c_per32 = p.c.gran_k == 32;
-            for (uint32_t iter = 0; ok && walker.next(iter * p.num_units + unit, tc); ++iter) {
-                const uint32_t acc = iter % kAccStages;
-                const uint32_t acc_phase = (iter / kAccStages) & 1;
-                ok = wait_barrier<kPair>(&bars->tmem_empty[acc], acc_phase ^ 1, abort_flag, peer_abort, p,
-                                         kSiteMmaTmemEmpty, iter, 0, acc);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
-                const uint32_t num_kb = max(1u, (tc.k_len + 127u) / 128u);
-                for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
-                    DG_TRACE_AT(3, kb);
-                    ok = wait_barrier<kPair>(&bars->full[stage], phase, abort_flag, peer_abort, p, kSiteMmaFull, iter,
-                                             kb, stage);
+            // Scale byte selectors: per-32 scales pick byte ks of the word, per-128 scales byte (kb % 4)
+            const uint32_t r_per32 = p.r.gran_k == 32 ? 1u : 0u, c_per32 = p.c.gran_k == 32 ? 1u : 0u;
+            const uint32_t sfr_tmem = tmem_base + Cfg::kSfrCol, sfc_tmem = tmem_base + Cfg::kSfcCol;
+            for (uint32_t iter = 0; ok; ++iter) {
+                const uint32_t num_sub = walker.next(iter * p.num_units + unit, tiles);
+                if (num_sub == 0) break;
+                for (uint32_t sub = 0; sub < num_sub && ok; ++sub, ++acc_iter) {
+                    const TileCoord& tc = tiles[sub];
+                    const uint32_t acc = acc_iter & 1;
+                    const uint32_t acc_phase = (acc_iter >> 1) & 1;
+                    ok = wait_barrier(&bars->tmem_empty[acc], acc_phase ^ 1, abort_flag, peer_abort, p,
+                                      kSiteMmaTmemEmpty, acc_iter, 0, acc);
                     if (!ok) break;
-                    DG_TRACE_AT(4, kb);
+                    if (Cfg::kOverlap > 0 && acc_iter > 0) {
+                        // The previous tile's epilogue must have drained the columns both stages share
+                        const uint32_t prev = acc_iter - 1;
+                        ok = wait_barrier(&bars->overlap[prev & 1], (prev >> 1) & 1, abort_flag, peer_abort, p,
+                                          kSiteMmaOverlap, acc_iter, 0, acc);
+                        if (!ok) break;
+                    }
                     tc_fence_after();
-                    if (elect_one()) {
-                    // Fresh scale factors: shared memory (already in 32x4 order) -> TMEM
-                    if ((kb & sf_mask_r) == 0) {
-                        const uint32_t a = smem_sfr + stage * Cfg::SFR_STAGE;
-                        utccp_32x128b_warpx4<kCtas>(tmem_base + Cfg::kSfrCol, sf_desc_hi | ((a >> 4) & 0x3FFF));
-                    }
-                    if ((kb & sf_mask_c) == 0) {
+                    const uint32_t d_tmem = tmem_base + acc * Cfg::kAccStride;
+                    const uint32_t idesc_tile = kSwap ? idesc_with_n(idesc_base, tc.rows) : idesc_base;
+                    const uint32_t num_kb = max(1u, (tc.k_len + 127u) / 128u);
+                    for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
+                        DG_TRACE_AT(3, kb);
+                        ok = wait_barrier(&bars->full[stage], phase, abort_flag, peer_abort, p, kSiteMmaFull, acc_iter,
+                                          kb, stage);
+                        if (!ok) break;
+                        DG_TRACE_AT(4, kb);
+                        tc_fence_after();
+                        if (elect_one()) {
+                            // Fresh scale factors: shared memory (already in 32x4 order) -> TMEM
+                            if ((kb & sf_mask_r) == 0) {
+                                const uint32_t a = smem_sfr + stage * Cfg::SFR_STAGE;
+                                utccp_32x128b_warpx4<kCtas>(sfr_tmem, sf_desc_hi | (a >> 4));
+                            }
+                            if ((kb & sf_mask_c) == 0) {
 #pragma unroll
-                        for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i) {
-                            const uint32_t a = smem_sfc + stage * Cfg::SFC_STAGE + i * 512;
-                            utccp_32x128b_warpx4<kCtas>(tmem_base + Cfg::kSfcCol + i * 4,
-                                                        sf_desc_hi | ((a >> 4) & 0x3FFF));
+                                for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i) {
+                                    const uint32_t a = smem_sfc + stage * Cfg::SFC_STAGE + i * 512;
+                                    utccp_32x128b_warpx4<kCtas>(sfc_tmem + i * 4, sf_desc_hi | (a >> 4));
+                                }
+                            }
+                            const uint32_t r_lo = r_lo0 + stage * (Cfg::R_STAGE >> 4);
+                            const uint32_t c_lo = c_lo0 + stage * (Cfg::C_STAGE >> 4);
+                            const uint32_t id128 = kb & 3;
+                            const uint32_t idesc_kb = idesc_tile | ((c_per32 ? 0u : id128) << 4) |
+                                                      ((r_per32 ? 0u : id128) << 29);
+                            const uint32_t idesc_ks = (c_per32 << 4) | (r_per32 << 29);
+#pragma unroll
+                            for (uint32_t ks = 0; ks < 4; ++ks) {
+                                const uint64_t r_desc = (static_cast<uint64_t>(r_hi) << 32) | (r_lo + ks * r_kstep);
+                                const uint64_t c_desc = (static_cast<uint64_t>(c_hi) << 32) | (c_lo + ks * c_kstep);
+                                umma_mxf8f6f4<kCtas>(d_tmem, r_desc, c_desc, idesc_kb + ks * idesc_ks, sfr_tmem,
+                                                     sfc_tmem, (kb | ks) != 0);
+                            }
+                            umma_commit<kCtas>(&bars->empty[stage]);   // frees the stage (in both CTAs)
+                            if (kb + 1 == num_kb) umma_commit<kCtas>(&bars->tmem_full[acc]);
                         }
+                        __syncwarp();
+                        DG_TRACE_AT(5, kb);
                     }
-                    const uint32_t r_lo = r_lo0 + stage * (Cfg::R_STAGE >> 4);
-                    const uint32_t c_lo = c_lo0 + stage * (Cfg::C_STAGE >> 4);
-                    const uint32_t id128 = kb & 3;
-#pragma unroll
-                    for (uint32_t ks = 0; ks < 4; ++ks) {
-                        const uint32_t id_r = r_per32 ? ks : id128;
-                        const uint32_t id_c = c_per32 ? ks : id128;
-                        const uint64_t r_desc = (static_cast<uint64_t>(r_hi) << 32) | (r_lo + ks * r_kstep);
-                        const uint64_t c_desc = (static_cast<uint64_t>(c_hi) << 32) | (c_lo + ks * c_kstep);
-                        umma_mxf8f6f4<kCtas>(d_tmem, r_desc, c_desc, idesc_base | (id_c << 4) | (id_r << 29),
-                                             tmem_base + Cfg::kSfrCol, tmem_base + Cfg::kSfcCol, (kb | ks) != 0);
-                    }
-                    umma_commit<kCtas>(&bars->empty[stage]);   // frees the stage (in both CTAs)
-                    if (kb + 1 == num_kb) umma_commit<kCtas>(&bars->tmem_full[acc]);
-                    }
-                    __syncwarp();
-                    DG_TRACE_AT(5, kb);
                 }
             }
         }
     } else if (warp == 2) {
         // ============================================================ scale-factor transposer
         // tcgen05.cp 32x128b.warpx4 wants, per 128 rows, row i's word at position (i % 32) * 4 + i / 32.
-        TileWalker walker(p, Cfg::UNIT_M, Cfg::UNIT_N);
-        TileCoord tc;
-        bool ok = true;
         const uint32_t full_bar = leader_addr(&bars->full[0]);
-        for (uint32_t iter = 0; ok && walker.next(iter * p.num_units + unit, tc); ++iter) {
-            const uint32_t num_kb = max(1u, (tc.k_len + 127u) / 128u);
-            for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
-                ok = wait_barrier<false>(&bars->sf_full[stage], phase, abort_flag, peer_abort, p,
-                                         kSiteTransposerSfFull, iter, kb, stage);
-                if (!ok) break;
-                if (lane == 0) DG_TRACE_AT(2, kb);
-                auto transpose_128 = [&](uint32_t* w) {
-                    uint32_t v0 = w[lane], v1 = w[32 + lane], v2 = w[64 + lane], v3 = w[96 + lane];
-                    __syncwarp();
-                    reinterpret_cast<uint4*>(w)[lane] = make_uint4(v0, v1, v2, v3);
-                };
-                const bool new_r = (kb & sf_mask_r) == 0, new_c = (kb & sf_mask_c) == 0;
-                if (new_r) transpose_128(sf_words_r + stage * 128);
-                if (new_c) {
+        for (uint32_t iter = 0; ok; ++iter) {
+            const uint32_t num_sub = walker.next(iter * p.num_units + unit, tiles);
+            if (num_sub == 0) break;
+            for (uint32_t sub = 0; sub < num_sub && ok; ++sub, ++acc_iter) {
+                const uint32_t num_kb = max(1u, (tiles[sub].k_len + 127u) / 128u);
+                for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
+                    ok = wait_barrier(&bars->sf_full[stage], phase, abort_flag, peer_abort, p, kSiteTransposerSfFull,
+                                      acc_iter, kb, stage);
+                    if (!ok) break;
+                    DG_TRACE_AT(2, kb);
+                    auto transpose_128 = [&](uint32_t* w) {
+                        uint32_t v0 = w[lane], v1 = w[32 + lane], v2 = w[64 + lane], v3 = w[96 + lane];
+                        __syncwarp();
+                        reinterpret_cast<uint4*>(w)[lane] = make_uint4(v0, v1, v2, v3);
+                    };
+                    const bool new_r = (kb & sf_mask_r) == 0, new_c = (kb & sf_mask_c) == 0;
+                    if (new_r) transpose_128(sf_words_r + stage * 128);
+                    if (new_c) {
 #pragma unroll
-                    for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i)
-                        transpose_128(sf_words_c + stage * Cfg::SFC_ROWS + i * 128);
+                        for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i)
+                            transpose_128(sf_words_c + stage * Cfg::SFC_ROWS + i * 128);
+                    }
+                    if (new_r || new_c) {
+                        fence_proxy_async_smem();   // generic-proxy writes -> visible to tcgen05.cp
+                        __syncwarp();
+                    }
+                    if (lane == 0) mbar_arrive_cluster(full_bar + stage * 8);
                 }
-                if (new_r || new_c) {
-                    fence_proxy_async_smem();   // generic-proxy writes -> visible to tcgen05.cp
-                    __syncwarp();
-                }
-                if (lane == 0) mbar_arrive_cluster(full_bar + stage * 8);
             }
         }
     } else if (warp >= 4) {
         // ============================================================ epilogue
         const uint32_t q = warp - 4;   // TMEM lane quadrant == warp % 4
-        TileWalker walker(p, Cfg::UNIT_M, Cfg::UNIT_N);
-        TileCoord tc;
-        bool ok = true;
         const uint32_t tmem_empty_bar = leader_addr(&bars->tmem_empty[0]);
+        const uint32_t overlap_bar = leader_addr(&bars->overlap[0]);
         const uint32_t slab0 = smem_cd + q * Cfg::SLAB_BYTES;
         uint8_t* slab0_gen = smem_gen + (slab0 - smem_base);
         uint32_t buf = 0;
-        for (uint32_t iter = 0; ok && walker.next(iter * p.num_units + unit, tc); ++iter) {
-            const uint32_t acc = iter % kAccStages;
-            const uint32_t acc_phase = (iter / kAccStages) & 1;
-            ok = wait_barrier<false>(&bars->tmem_full[acc], acc_phase, abort_flag, peer_abort, p,
-                                     kSiteEpilogueTmemFull, iter, 0, acc);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t t_acc = tmem_base + acc * BN + ((q * 32) << 16);
-            // Where this warp's 32 lanes land in D
-            //   D tile  : rows m0 + q*32 .. +31, columns n0 + chunk
-            //   D^T tile: columns n0 + q*32 .. +31 (lanes), rows m0 + chunk (TMEM columns)
-            const uint32_t m0 = tc.m_blk * Cfg::UNIT_M + (Cfg::kSwap ? 0 : cta_rank * 128);
-            const uint32_t n0 = tc.n_blk * Cfg::UNIT_N + (Cfg::kSwap ? cta_rank * 128 : 0);
-            constexpr uint32_t kChunks = BN / Cfg::CHUNK_COLS;
+        for (uint32_t iter = 0; ok; ++iter) {
+            const uint32_t num_sub = walker.next(iter * p.num_units + unit, tiles);
+            if (num_sub == 0) break;
+            for (uint32_t sub = 0; sub < num_sub && ok; ++sub, ++acc_iter) {
+                const TileCoord& tc = tiles[sub];
+                const uint32_t acc = acc_iter & 1;
+                const uint32_t acc_phase = (acc_iter >> 1) & 1;
+                ok = wait_barrier(&bars->tmem_full[acc], acc_phase, abort_flag, peer_abort, p, kSiteEpilogueTmemFull,
+                                  acc_iter, 0, acc);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t t_acc = tmem_base + acc * Cfg::kAccStride + ((q * 32) << 16);
+                // Where this warp's 32 lanes land in D
+                //   D tile  : rows m0 + q*32 .. +31, columns n0 + chunk
+                //   D^T tile: columns n0 + q*32 .. +31 (lanes), rows m0 + chunk (TMEM columns)
+                const uint32_t m0 = tc.row0 + (kSwap ? 0 : cta_rank * 128);
+                const uint32_t n0 = tc.n_blk * Cfg::UNIT_N + (kSwap ? cta_rank * 128 : 0);
+                const uint32_t num_chunks = kSwap ? (tc.rows + Cfg::CHUNK_COLS - 1) / Cfg::CHUNK_COLS
+                                                  : BN / Cfg::CHUNK_COLS;
+                // Stage 0 shares its last columns, stage 1 its first: drain the shared ones first
+                const bool reverse = Cfg::kOverlap > 0 && acc == 0;
 #pragma unroll 1
-            for (uint32_t ch = 0; ch < kChunks; ++ch) {
-                uint32_t v[Cfg::CHUNK_COLS];
+                for (uint32_t i = 0; i < num_chunks; ++i) {
+                    const uint32_t ch = reverse ? num_chunks - 1 - i : i;
+                    uint32_t v[Cfg::CHUNK_COLS];
 #pragma unroll
-                for (uint32_t i = 0; i < Cfg::CHUNK_COLS / 32; ++i)
-                    tmem_ld_32x32b_x32(t_acc + ch * Cfg::CHUNK_COLS + i * 32, v + i * 32);
-                tmem_ld_wait();
-                if (ch + 1 == kChunks) {
-                    // Accumulator is in registers: hand the TMEM stage back to the UMMA issuer
-                    tc_fence_before();
+                    for (uint32_t j = 0; j < Cfg::CHUNK_COLS / 32; ++j)
+                        tmem_ld_32x32b_x32(t_acc + ch * Cfg::CHUNK_COLS + j * 32, v + j * 32);
+                    tmem_ld_wait();
+                    if (i == 0 || i + 1 == num_chunks) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            // First chunk read: the shared columns may be overwritten by the next tile.
+                            // Last chunk read: the whole stage goes back to the UMMA issuer.
+                            if (Cfg::kOverlap > 0 && i == 0) mbar_arrive_cluster(overlap_bar + acc * 8);
+                            if (i + 1 == num_chunks) mbar_arrive_cluster(tmem_empty_bar + acc * 8);
+                        }
+                    }
+                    // The slab we are about to overwrite must have been read by its previous store
+                    if (lane == 0) tma_store_wait_read<Cfg::kStoreBufs - 1>();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(tmem_empty_bar + acc * 8);
-                }
-                // The slab we are about to overwrite must have been read by its previous store
-                if (lane == 0) tma_store_wait_read<Cfg::kStoreBufs - 1>();
-                __syncwarp();
-                const uint32_t slab = slab0 + buf * 4 * Cfg::SLAB_BYTES;
-                uint8_t* slab_gen = slab0_gen + buf * 4 * Cfg::SLAB_BYTES;
-                if constexpr (!Cfg::kSwap) {
-                    // Row `lane` of the slab: 128 B, 16 B chunks XOR-swizzled by (row % 8)
-                    uint4* row = reinterpret_cast<uint4*>(slab_gen + lane * 128);
-                    if constexpr (Cfg::kCdF32) {
+                    const uint32_t slab = slab0 + buf * 4 * Cfg::SLAB_BYTES;
+                    uint8_t* slab_gen = slab0_gen + buf * 4 * Cfg::SLAB_BYTES;
+                    if constexpr (!kSwap) {
+                        // Row `lane` of the slab: 128 B, 16 B chunks XOR-swizzled by (row % 8)
+                        uint4* row = reinterpret_cast<uint4*>(slab_gen + lane * 128);
+                        if constexpr (Cfg::kCdF32) {
 #pragma unroll
-                        for (uint32_t c16 = 0; c16 < 8; ++c16) {
-                            float4 f;
-                            f.x = __uint_as_float(v[c16 * 4 + 0]) * p.alpha;
-                            f.y = __uint_as_float(v[c16 * 4 + 1]) * p.alpha;
-                            f.z = __uint_as_float(v[c16 * 4 + 2]) * p.alpha;
-                            f.w = __uint_as_float(v[c16 * 4 + 3]) * p.alpha;
-                            reinterpret_cast<float4*>(row)[c16 ^ (lane & 7)] = f;
-                        }
-                    } else {
-#pragma unroll
-                        for (uint32_t c16 = 0; c16 < 8; ++c16) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (uint32_t j = 0; j < 4; ++j) {
-                                const float lo = __uint_as_float(v[c16 * 8 + j * 2]) * p.alpha;
-                                const float hi = __uint_as_float(v[c16 * 8 + j * 2 + 1]) * p.alpha;
-                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
-                                w[j] = *reinterpret_cast<const uint32_t*>(&b2);
+                            for (uint32_t c16 = 0; c16 < 8; ++c16) {
+                                float4 f;
+                                f.x = __uint_as_float(v[c16 * 4 + 0]) * p.alpha;
+                                f.y = __uint_as_float(v[c16 * 4 + 1]) * p.alpha;
+                                f.z = __uint_as_float(v[c16 * 4 + 2]) * p.alpha;
+                                f.w = __uint_as_float(v[c16 * 4 + 3]) * p.alpha;
+                                reinterpret_cast<float4*>(row)[c16 ^ (lane & 7)] = f;
                             }
-                            row[c16 ^ (lane & 7)] = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
-                    }
-                } else {
-                    // D^T: lane holds column n0 + q*32 + lane for 32 tokens; slab is [token][32 n] BF16
-                    __nv_bfloat16* s = reinterpret_cast<__nv_bfloat16*>(slab_gen);
+                        } else {
 #pragma unroll
-                    for (uint32_t t = 0; t < 32; ++t)
-                        s[t * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[t]) * p.alpha);
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    int32_t cn, cm;
-                    if constexpr (!Cfg::kSwap) {
-                        cn = static_cast<int32_t>(n0 + ch * Cfg::CHUNK_COLS);
-                        cm = static_cast<int32_t>(m0 + q * 32);
+                            for (uint32_t c16 = 0; c16 < 8; ++c16) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (uint32_t j = 0; j < 4; ++j) {
+                                    const float lo = __uint_as_float(v[c16 * 8 + j * 2]) * p.alpha;
+                                    const float hi = __uint_as_float(v[c16 * 8 + j * 2 + 1]) * p.alpha;
+                                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+                                    w[j] = *reinterpret_cast<const uint32_t*>(&b2);
+                                }
+                                row[c16 ^ (lane & 7)] = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        }
                     } else {
-                        cn = static_cast<int32_t>(n0 + q * 32);
-                        cm = static_cast<int32_t>(m0 + ch * 32);
+                        // D^T: lane holds column n0 + q*32 + lane for 32 tokens; slab is [token][32 n] BF16
+                        __nv_bfloat16* s = reinterpret_cast<__nv_bfloat16*>(slab_gen);
+#pragma unroll
+                        for (uint32_t t = 0; t < 32; ++t)
+                            s[t * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[t]) * p.alpha);
                     }
-                    const int32_t cg = p.d_grouped ? static_cast<int32_t>(tc.group) : 0;
-                    if (p.accumulate) tma_reduce_add_3d(&p.tm_d, slab, cn, cm, cg);
-                    else              tma_store_3d(&p.tm_d, slab, cn, cm, cg);
-                    tma_store_commit();
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        int32_t cn, cm;
+                        if constexpr (!kSwap) {
+                            cn = static_cast<int32_t>(n0 + ch * Cfg::CHUNK_COLS);
+                            cm = static_cast<int32_t>(m0 + q * 32);
+                        } else {
+                            cn = static_cast<int32_t>(n0 + q * 32);
+                            cm = static_cast<int32_t>(m0 + ch * 32);
+                        }
+                        const int32_t cg = p.d_grouped ? static_cast<int32_t>(tc.group) : 0;
+                        if (p.accumulate) tma_reduce_add_3d(&p.tm_d, slab, cn, cm, cg);
+                        else              tma_store_3d(&p.tm_d, slab, cn, cm, cg);
+                        tma_store_commit();
+                    }
+                    buf = buf + 1 == Cfg::kStoreBufs ? 0 : buf + 1;
                 }
-                buf = buf + 1 == Cfg::kStoreBufs ? 0 : buf + 1;
             }
         }
         if (lane == 0) tma_store_wait<0>();

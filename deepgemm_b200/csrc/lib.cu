@@ -233,10 +233,16 @@ int choose_tile(const dg_gemm_args& a, int num_sms, TileChoice* t) {
     const bool k_grouped = a.gemm_type == DG_GEMM_K_GROUPED || a.gemm_type == DG_GEMM_K_GROUPED_PSUM;
     TileChoice c;
     if (m_grouped) {
-        // Tokens on the UMMA N axis: a CTA pair shares one token block of any expert.
+        // Tokens on the UMMA N axis: a CTA pair shares one token block of any expert.  256-token
+        // tiles halve the number of UMMAs per flop; short groups shrink the UMMA N at run time.
         c.swap = true;
-        c.bn = 128;
-        if (a.gemm_type == DG_GEMM_M_MASKED && a.expected_m > 0 && a.expected_m <= 64) c.bn = 64;
+        c.bn = 256;
+        if (a.gemm_type == DG_GEMM_M_MASKED && a.expected_m > 0 && a.expected_m <= 128) c.bn = a.expected_m <= 64 ? 64 : 128;
+        if (a.gemm_type == DG_GEMM_M_CONTIGUOUS) {
+            const int align = dg_get_mk_alignment_for_contiguous_layout();
+            if (align % 128 != 0) c.bn = align % 64 == 0 ? 64 : 128;   // odd alignments: one unit per tile
+            if (align % 256 != 0 && align % 128 == 0 && a.m < 256) c.bn = 128;
+        }
         c.ctas = (a.n % 256 == 0 && num_sms % 2 == 0) ? 2 : 1;
     } else if (k_grouped) {
         c.swap = false;
@@ -411,10 +417,21 @@ int dg_gemm_bs(const dg_gemm_args* args) {
 
     const uint32_t unit_m = t.swap ? t.bn : 128 * t.ctas;
     const uint32_t unit_n = t.swap ? 128 * t.ctas : t.bn;
-    if (a.gemm_type == DG_GEMM_M_CONTIGUOUS || a.gemm_type == DG_GEMM_M_PSUM) {
-        const int align = a.gemm_type == DG_GEMM_M_PSUM ? a.alignment : dg_get_mk_alignment_for_contiguous_layout();
-        DG_REQUIRE(align > 0 && align % unit_m == 0, "group alignment is a multiple of the token tile");
+    uint32_t split_blocks = 0;
+    if (a.gemm_type == DG_GEMM_M_CONTIGUOUS) {
+        // Tiles must not mix experts: a tile is one alignment unit, or two units that are split
+        // on the device where they belong to different experts.
+        const int align = dg_get_mk_alignment_for_contiguous_layout();
+        DG_REQUIRE(align > 0 && align % 32 == 0, "group alignment is a multiple of 32");
+        if (align % static_cast<int>(unit_m) != 0) {
+            DG_REQUIRE(t.swap && unit_m % 2 == 0 && align % static_cast<int>(unit_m / 2) == 0,
+                       "group alignment is a multiple of half the token tile");
+            split_blocks = 1;
+        }
     }
+    if (a.gemm_type == DG_GEMM_M_PSUM) DG_REQUIRE(a.alignment > 0 && a.alignment % 32 == 0, "psum alignment");
+    if (a.gemm_type == DG_GEMM_M_PSUM || a.gemm_type == DG_GEMM_M_MASKED)
+        DG_REQUIRE(t.swap, "psum / masked layouts run with swapped operands");
     if (k_grouped) DG_REQUIRE(a.alignment > 0 && a.alignment % 128 == 0, "k alignment");
 
     // Operand roles
@@ -445,6 +462,7 @@ int dg_gemm_bs(const dg_gemm_args* args) {
     p.alpha = a.alpha;
     p.accumulate = a.accumulate ? 1 : 0;
     p.d_grouped = (a.gemm_type == DG_GEMM_M_MASKED || k_grouped) ? 1 : 0;
+    p.split_blocks = split_blocks;
     {
         std::lock_guard<std::mutex> lk(g_knobs.mu);
         p.timeout_ms = g_knobs.timeout_ms;
@@ -498,6 +516,7 @@ int dg_gemm_bs(const dg_gemm_args* args) {
     DG_TRY(2, 64, true, false)
     DG_TRY(2, 128, true, false)
     DG_TRY(2, 256, true, false)
+    DG_TRY(1, 256, true, false)
 #undef DG_TRY
     return fail(DG_ERR_INVALID, "no kernel built for cta_group %d, block_n %d, swap %d, f32 %d", t.ctas, t.bn,
                 static_cast<int>(t.swap), static_cast<int>(a.d_dtype == DG_F32));

@@ -250,9 +250,9 @@ def test_empty_and_k_zero():
 # --------------------------------------------------------------------------- M-grouped
 @pytest.mark.parametrize("use_psum", [False, True])
 @pytest.mark.parametrize("b_kind,tol", [("fp8_block", FP8_TOL), ("fp4", FP4_TOL)])
-@pytest.mark.parametrize("tile", [None, T(1, 128, 2), T(2, 128, 2), T(1, 64, 2)])
+@pytest.mark.parametrize("tile", [None, T(1, 128, 2), T(2, 128, 2), T(1, 64, 2), T(2, 256, 2), T(1, 256, 2)])
 def test_m_grouped_contiguous(use_psum, b_kind, tol, tile):
-    case = H.make_m_grouped_contiguous(4, 300, 512, 1024, use_psum=use_psum, b_kind=b_kind,
+    case = H.make_m_grouped_contiguous(5, 300, 512, 1024, use_psum=use_psum, b_kind=b_kind,
                                        scale_b=0.02 if b_kind == "fp4" else 1.0, seed=21)
     ga, gmb, gb = case["grans"]
     d = torch.full((case["m"], 512), float("nan"), dtype=torch.bfloat16, device="cuda")
@@ -283,13 +283,15 @@ def test_m_grouped_contiguous_nn_alias():
 
 @pytest.mark.parametrize("b_kind,tol", [("fp8_block", FP8_TOL), ("fp4", FP4_TOL)])
 @pytest.mark.parametrize("groups,max_m,expected", [(4, 512, 150), (6, 256, 20), (3, 1024, 700)])
-def test_m_grouped_masked(b_kind, tol, groups, max_m, expected):
+@pytest.mark.parametrize("tile", [None, T(2, 256, 2), T(2, 128, 2), T(1, 64, 2)])
+def test_m_grouped_masked(b_kind, tol, groups, max_m, expected, tile):
     case = H.make_masked(groups, max_m, expected, 512, 1024, b_kind=b_kind, scale_b=0.02 if b_kind == "fp4" else 1.0,
                          seed=groups)
     ga, gmb, gb = case["grans"]
     d = torch.full((groups, max_m, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
-    dg.m_grouped_fp8_fp4_gemm_nt_masked(case["a"], case["b"], d, case["masked"], expected, recipe_a=(1, ga),
-                                        recipe_b=(gmb, gb))
+    with H.force_tile(**(tile or {})):
+        dg.m_grouped_fp8_fp4_gemm_nt_masked(case["a"], case["b"], d, case["masked"], expected, recipe_a=(1, ga),
+                                            recipe_b=(gmb, gb))
     ref = OG.m_grouped_masked(case["ref_a"], case["ref_b"], case["masked_cpu"])
     dn = H.to_np(d)
     for g in range(groups):
