@@ -24,6 +24,12 @@ from .ops import (  # noqa: F401
     m_grouped_fp8_fp4_gemm_nt_masked, k_grouped_fp8_gemm_tn_contiguous,
 )
 
+from . import mega  # noqa: F401,E402
+from .mega import (  # noqa: F401,E402
+    SymmBuffer, get_symm_buffer_for_mega_moe, transform_weights_for_mega_moe, fp8_fp4_mega_moe,
+    get_token_alignment_for_mega_moe, get_block_m_for_mega_moe,
+)
+
 __version__ = "0.1.0"
 
 # Aliases (csrc/apis/gemm.hpp:927-936 of the reference)

@@ -18,6 +18,7 @@ EXPORTS = (
     "dg_set_tc_util", "dg_get_tc_util", "dg_set_mk_alignment_for_contiguous_layout",
     "dg_get_mk_alignment_for_contiguous_layout", "dg_get_theoretical_mk_alignment_for_contiguous_layout",
     "dg_set_wait_timeout_ms", "dg_check_status", "dg_last_error", "dg_version",
+    "dg_mega_moe_buffer_layout", "dg_get_token_alignment_for_mega_moe", "dg_mega_moe_forward",
 )
 
 
@@ -35,6 +36,25 @@ class GemmArgs(C.Structure):
                 ("grouped_layout", C.c_void_p), ("stream", C.c_void_p),
                 ("force_cta_group", C.c_int32), ("force_block_n", C.c_int32), ("force_swap", C.c_int32),
                 ("reserved", C.c_int32)]
+
+
+class MoeConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("num_ranks", "num_experts", "num_max_tokens_per_rank", "num_topk", "hidden",
+                                          "intermediate_hidden")]
+
+
+class MoeLayout(C.Structure):
+    _fields_ = [(n, C.c_int64) for n in ("num_bytes", "pool_rows", "off_x", "off_x_sf", "off_topk_idx",
+                                          "off_topk_weights", "off_l1_acts", "off_l1_acts_sf", "off_l2_acts",
+                                          "off_l2_acts_sf", "off_token_src_metadata", "off_combine")]
+
+
+class MoeArgs(C.Structure):
+    _fields_ = [("cfg", MoeConfig), ("buffer_ptrs", C.POINTER(C.c_void_p)), ("rank", C.c_int32),
+                ("num_tokens", C.c_int32), ("y", C.c_void_p), ("ldy", C.c_int64),
+                ("l1_w", C.c_void_p), ("l1_sf", C.c_void_p), ("l2_w", C.c_void_p), ("l2_sf", C.c_void_p),
+                ("l1_sf_ld", C.c_int64), ("l2_sf_ld", C.c_int64), ("stats", C.c_void_p),
+                ("activation_clamp", C.c_float), ("fast_math", C.c_int32), ("stream", C.c_void_p)]
 
 
 _lib = None
@@ -58,6 +78,8 @@ def lib() -> C.CDLL:
                                                  C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                                  C.c_void_p]
         l.dg_check_status.argtypes = [C.POINTER(C.c_uint32)]
+        l.dg_mega_moe_buffer_layout.argtypes = [C.POINTER(MoeConfig), C.POINTER(MoeLayout)]
+        l.dg_mega_moe_forward.argtypes = [C.POINTER(MoeArgs)]
         for name in ("dg_set_num_sms", "dg_set_tc_util", "dg_set_mk_alignment_for_contiguous_layout",
                      "dg_get_theoretical_mk_alignment_for_contiguous_layout", "dg_set_wait_timeout_ms"):
             getattr(l, name).argtypes = [C.c_int32]

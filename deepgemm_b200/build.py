@@ -15,7 +15,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_DIR = os.path.join(PKG_DIR, "lib")
 LIB_PATH = os.environ.get("DEEPGEMM_B200_LIB") or os.path.join(LIB_DIR, "libdeepgemm_b200.so")
 SOURCES = ["lib.cu"]
-HEADERS = ["ptx.cuh", "gemm_bs.cuh", "sf_pack.cuh", os.path.join("..", "..", "include", "deepgemm_b200.h")]
+HEADERS = ["ptx.cuh", "gemm_bs.cuh", "sf_pack.cuh", "mega_moe.cuh", os.path.join("..", "..", "include", "deepgemm_b200.h")]
 
 
 def nvcc_path() -> str:

@@ -22,6 +22,9 @@
 // loops, outstanding copies are given time to land, TMEM is freed and the kernel returns.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
 #include "ptx.cuh"
 
 namespace dg {
@@ -46,6 +49,7 @@ enum WaitSite : uint32_t {
     kSiteMmaFull = 4,
     kSiteEpilogueTmemFull = 5,
     kSiteMmaOverlap = 6,
+    kSiteEpilogueSync = 7,
 };
 
 // One UMMA operand as the kernel sees it (all values computed on the host).
@@ -60,6 +64,22 @@ struct OperandParams {
     uint32_t desc_kstep;  // descriptor start-address advance per UMMA_K (32 elements), bytes
     uint32_t gran_k;      // 32 or 128 K elements per scale
     uint32_t fmt;         // kFmtE4M3 / kFmtE2M1
+};
+
+// Arguments of the fused Mega MoE epilogues.
+//   kEpi == 1 (first expert GEMM): BF16-round gate / up, gate * sigmoid(gate) * up * route weight,
+//             per-32 UE8M0 E4M3 requantisation, written as the second GEMM's A operand.
+//   kEpi == 2 (second expert GEMM): BF16 rows stored into the source rank's combine buffer.
+struct MoeEpilogueParams {
+    uint8_t* l2_acts;          // e4m3 [pool_rows, inter]
+    uint8_t* l2_sf;            // UE8M0 bytes: word (kw, row) at (kw * pool_rows + row) * 4, byte k % 4
+    const float* pool_w;       // route weight per pool row
+    const int32_t* pool_meta;  // (source rank, token, slot) per pool row; rank < 0: no token
+    uint8_t* peer_base[16];    // every rank's buffer base
+    uint64_t off_combine;
+    uint32_t pool_rows, inter, hidden, t_max;
+    float clamp;               // activation clamp; +inf = none
+    uint32_t fast_math;
 };
 
 struct GemmParams {
@@ -80,6 +100,8 @@ struct GemmParams {
     uint32_t accumulate;        // D += result (TMA reduce-add) instead of D = result
     uint32_t d_grouped;         // D has a group axis (masked / K-grouped): third store coordinate = group
     uint32_t split_blocks;      // contiguous layout: a schedule slot spans two alignment units (may straddle experts)
+    uint32_t r_sf_pretransposed;  // R's scale words already sit in the 32x4 order tcgen05.cp reads (Mega MoE weights)
+    MoeEpilogueParams moe;      // fused Mega MoE epilogues (GemmConfig::kEpi != 0)
     uint32_t timeout_ms;
     uint32_t* status;           // 16 words: [0] code, [1] site, [2] block, [3] tile iter, [4] k block, [5] stage
     unsigned long long* trace;  // optional clock samples of block 0's first tile (builds with DG_TRACE only)
@@ -230,8 +252,10 @@ struct TileWalker {
     }
 };
 
-template <int kCtas_, int BN_, bool kSwap_, bool kCdF32_>
+template <int kCtas_, int BN_, bool kSwap_, bool kCdF32_, int kEpi_ = 0>
 struct GemmConfig {
+    static constexpr int kEpi = kEpi_;   // 0: store D; 1 / 2: fused Mega MoE epilogues (swapped tiles only)
+    static_assert(kEpi_ == 0 || kSwap_, "the fused epilogues work on D^T tiles");
     static constexpr int kCtas = kCtas_;
     static constexpr int BN = BN_;
     static constexpr bool kSwap = kSwap_;
@@ -256,7 +280,10 @@ struct GemmConfig {
     static constexpr uint32_t CHUNK_COLS = kSwap ? 32 : (kCdF32 ? 32 : 64);
     static constexpr uint32_t SLAB_BYTES = kSwap ? 32 * 64 : 32 * 128;
     static constexpr uint32_t kStoreBufs = (kCtas == 1 && BN == 256) ? 1 : 2;
-    static constexpr uint32_t CD_BYTES = kStoreBufs * 4 * SLAB_BYTES;
+    // Fused epilogues stage 32 tokens x 128 rows of BF16 per buffer (row pitch padded for kEpi == 1)
+    static constexpr uint32_t MOE_PITCH = kEpi == 1 ? 272 : 256;
+    static constexpr uint32_t CD_BYTES = kEpi == 0 ? kStoreBufs * 4 * SLAB_BYTES
+                                                   : (2 * 32 * MOE_PITCH + 1023) / 1024 * 1024;
 
     static constexpr uint32_t kSmemLimit = 232448;
     static constexpr uint32_t kBarrierBytes = 1024;
@@ -293,6 +320,7 @@ struct alignas(8) GemmBarriers {
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint64_t overlap[2];
+    uint64_t epi_sync[2];   // fused epilogues: the four epilogue warps meet here once per chunk
     uint32_t tmem_base;
     uint32_t abort;
 };
@@ -377,6 +405,7 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
             mbar_init(&bars->tmem_full[i], 1);            // UMMA commit
             mbar_init(&bars->tmem_empty[i], kCtas * 4);   // one lane per epilogue warp
             mbar_init(&bars->overlap[i], kCtas * 4);
+            mbar_init(&bars->epi_sync[i], 4);
         }
         bars->abort = 0;
         fence_mbar_init();
@@ -592,7 +621,7 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                         reinterpret_cast<uint4*>(w)[lane] = make_uint4(v0, v1, v2, v3);
                     };
                     const bool new_r = (kb & sf_mask_r) == 0, new_c = (kb & sf_mask_c) == 0;
-                    if (new_r) transpose_128(sf_words_r + stage * 128);
+                    if (new_r && !p.r_sf_pretransposed) transpose_128(sf_words_r + stage * 128);
                     if (new_c) {
 #pragma unroll
                         for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i)
@@ -613,7 +642,8 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
         const uint32_t overlap_bar = leader_addr(&bars->overlap[0]);
         const uint32_t slab0 = smem_cd + q * Cfg::SLAB_BYTES;
         uint8_t* slab0_gen = smem_gen + (slab0 - smem_base);
-        uint32_t buf = 0;
+        uint32_t buf = 0, moe_buf = 0, moe_chunks = 0;
+        (void)buf, (void)moe_buf, (void)moe_chunks;
         for (uint32_t iter = 0; ok; ++iter) {
             const uint32_t num_sub = walker.next(iter * p.num_units + unit, tiles);
             if (num_sub == 0) break;
@@ -653,6 +683,7 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                             if (i + 1 == num_chunks) mbar_arrive_cluster(tmem_empty_bar + acc * 8);
                         }
                     }
+                    if constexpr (Cfg::kEpi == 0) {
                     // The slab we are about to overwrite must have been read by its previous store
                     if (lane == 0) tma_store_wait_read<Cfg::kStoreBufs - 1>();
                     __syncwarp();
@@ -709,10 +740,106 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                         tma_store_commit();
                     }
                     buf = buf + 1 == Cfg::kStoreBufs ? 0 : buf + 1;
+                    } else {
+                        // Fused Mega MoE epilogues: the four warps stage this chunk's 32 tokens x 128 rows as
+                        // BF16 [token][row] in shared memory (two buffers, one named barrier per chunk: a
+                        // buffer is rewritten two chunks later, after its readers passed the next barrier).
+                        uint8_t* stage_gen = smem_gen + (smem_cd - smem_base) + moe_buf * 32 * Cfg::MOE_PITCH;
+#pragma unroll
+                        for (uint32_t t = 0; t < 32; ++t)
+                            *reinterpret_cast<__nv_bfloat16*>(stage_gen + t * Cfg::MOE_PITCH + (q * 32 + lane) * 2) =
+                                __float2bfloat16_rn(__uint_as_float(v[t]));
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bars->epi_sync[moe_buf]);
+                        ok = wait_barrier(&bars->epi_sync[moe_buf], (moe_chunks >> 1) & 1, abort_flag, peer_abort, p,
+                                          kSiteEpilogueSync, acc_iter, ch, moe_buf);
+                        ++moe_chunks;
+                        if (!ok) break;
+                        const uint32_t et = q * 32 + lane;           // epilogue thread 0..127
+                        const uint32_t chunk_rows = min(32u, tc.rows - ch * 32);
+                        if constexpr (Cfg::kEpi == 1) {
+                            // Thread (token t, group g): 32 intermediate outputs = 64 interleaved rows
+                            // laid out as 4 x [8 gate | 8 up] (weights interleaved in blocks of 8 rows).
+                            const uint32_t t = et & 31, g = et >> 5;
+                            if (g < 2 && t < chunk_rows) {
+                                const uint32_t row = m0 + ch * 32 + t;
+                                const float w = p.moe.pool_w[row];
+                                const uint4* src = reinterpret_cast<const uint4*>(stage_gen + t * Cfg::MOE_PITCH + g * 128);
+                                float act[32];
+                                float amax = 0.f;
+#pragma unroll
+                                for (uint32_t blk = 0; blk < 4; ++blk) {
+                                    const uint4 gv = src[2 * blk], uv = src[2 * blk + 1];
+                                    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+                                    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+#pragma unroll
+                                    for (uint32_t j = 0; j < 4; ++j) {
+                                        float2 gf = __bfloat1622float2(g2[j]), uf = __bfloat1622float2(u2[j]);
+                                        gf.x = fminf(gf.x, p.moe.clamp), gf.y = fminf(gf.y, p.moe.clamp);
+                                        uf.x = fminf(fmaxf(uf.x, -p.moe.clamp), p.moe.clamp);
+                                        uf.y = fminf(fmaxf(uf.y, -p.moe.clamp), p.moe.clamp);
+                                        float sx, sy;
+                                        if (p.moe.fast_math) {
+                                            sx = gf.x * __frcp_rn(1.0f + __expf(-gf.x));
+                                            sy = gf.y * __frcp_rn(1.0f + __expf(-gf.y));
+                                        } else {
+                                            sx = gf.x / (1.0f + expf(-gf.x));
+                                            sy = gf.y / (1.0f + expf(-gf.y));
+                                        }
+                                        const float ax = (sx * uf.x) * w, ay = (sy * uf.y) * w;
+                                        act[blk * 8 + j * 2] = ax, act[blk * 8 + j * 2 + 1] = ay;
+                                        amax = fmaxf(amax, fmaxf(fabsf(ax), fabsf(ay)));
+                                    }
+                                }
+                                // Power-of-two scale 2^e >= amax / 448, floor 2^-22 (amax clamp 1e-4): the add
+                                // carries into the exponent iff the mantissa exceeds that of 448 = 1.75 * 2^8
+                                uint32_t e = (__float_as_uint(amax) + 0x1FFFFFu) >> 23;
+                                e = max(e, 113u) - 8u;
+                                const float inv = __uint_as_float((254u - e) << 23);
+                                uint32_t packed[8];
+#pragma unroll
+                                for (uint32_t j = 0; j < 8; ++j) {
+                                    const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
+                                        make_float2(act[4 * j] * inv, act[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+                                    const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
+                                        make_float2(act[4 * j + 2] * inv, act[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+                                    packed[j] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+                                }
+                                const uint32_t inter0 = n0 / 2 + g * 32;   // n0: first interleaved row of this CTA
+                                uint4* dst = reinterpret_cast<uint4*>(p.moe.l2_acts +
+                                                                      static_cast<uint64_t>(row) * p.moe.inter + inter0);
+                                dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                                dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                                const uint32_t kgroup = inter0 / 32;
+                                p.moe.l2_sf[(static_cast<uint64_t>(kgroup / 4) * p.moe.pool_rows + row) * 4 + (kgroup & 3)] =
+                                    static_cast<uint8_t>(e);
+                            }
+                        } else {
+                            // 32 tokens x 256 B: 16 lanes move one token's 256 B segment to its source rank
+#pragma unroll
+                            for (uint32_t i = 0; i < 4; ++i) {
+                                const uint32_t piece = i * 128 + et, t = piece >> 4, part = piece & 15;
+                                if (t < chunk_rows) {
+                                    const uint32_t row = m0 + ch * 32 + t;
+                                    const int32_t src_rank = p.moe.pool_meta[row * 3];
+                                    if (src_rank >= 0) {
+                                        const uint32_t token = static_cast<uint32_t>(p.moe.pool_meta[row * 3 + 1]);
+                                        const uint32_t slot = static_cast<uint32_t>(p.moe.pool_meta[row * 3 + 2]);
+                                        const uint4 val = *reinterpret_cast<const uint4*>(stage_gen + t * Cfg::MOE_PITCH + part * 16);
+                                        uint8_t* dst = p.moe.peer_base[src_rank] + p.moe.off_combine +
+                                                       ((static_cast<uint64_t>(slot) * p.moe.t_max + token) * p.moe.hidden + n0) * 2 +
+                                                       part * 16;
+                                        *reinterpret_cast<uint4*>(dst) = val;
+                                    }
+                                }
+                            }
+                        }
+                        moe_buf ^= 1;
+                    }
                 }
             }
         }
-        if (lane == 0) tma_store_wait<0>();
+        if (Cfg::kEpi == 0 && lane == 0) tma_store_wait<0>();
     }
 
     // ---------------------------------------------------------------- tear-down

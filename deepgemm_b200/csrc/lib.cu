@@ -13,6 +13,7 @@
 #include "../../include/deepgemm_b200.h"
 #include "gemm_bs.cuh"
 #include "sf_pack.cuh"
+#include "mega_moe.cuh"
 
 namespace {
 
@@ -28,9 +29,10 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
-#define DG_REQUIRE(cond, ...)                                                          \
-    do {                                                                               \
-        if (!(cond)) return fail(DG_ERR_INVALID, "Assertion failed: " #cond " (" __VA_ARGS__ ")"); \
+// The condition text may contain '%': it is passed as an argument, never as the format.
+#define DG_REQUIRE(cond, ...)                                                                 \
+    do {                                                                                      \
+        if (!(cond)) return fail(DG_ERR_INVALID, "%s", "Assertion failed: " #cond " (" __VA_ARGS__ ")"); \
     } while (0)
 
 #define DG_CUDA(call)                                                                                   \
@@ -382,14 +384,13 @@ int dg_sf_pack_ue8m0_k_grouped(const float* sf, int32_t* out, const int32_t* gro
     return DG_OK;
 }
 
-int dg_gemm_bs(const dg_gemm_args* args) {
-    DG_REQUIRE(args != nullptr, "args");
-    const dg_gemm_args& a = *args;
+// Shared by dg_gemm_bs (epi == 0) and the two expert GEMMs of dg_mega_moe_forward (epi == 1, 2).
+static int run_gemm(const dg_gemm_args& a, int epi, const dg::MoeEpilogueParams* moe) {
     DG_REQUIRE(a.gemm_type >= DG_GEMM_NORMAL && a.gemm_type <= DG_GEMM_K_GROUPED_PSUM, "gemm_type");
     DG_REQUIRE(a.m >= 0 && a.n >= 0 && a.k >= 0, "shape");
     if (a.m == 0 || a.n == 0) return DG_OK;
     DG_REQUIRE(a.k > 0, "k == 0 is handled by the caller");
-    DG_REQUIRE(a.a.data && a.b.data && a.a.sf && a.b.sf && a.d, "null tensor");
+    DG_REQUIRE(a.a.data && a.b.data && a.a.sf && a.b.sf && (a.d || epi != 0), "null tensor");
     DG_REQUIRE(a.a.dtype == DG_E4M3 || a.a.dtype == DG_E2M1_PACKED, "a dtype");
     DG_REQUIRE(a.b.dtype == DG_E4M3 || a.b.dtype == DG_E2M1_PACKED, "b dtype");
     DG_REQUIRE(!(a.a.dtype == DG_E2M1_PACKED && a.b.dtype == DG_E2M1_PACKED),
@@ -411,6 +412,7 @@ int dg_gemm_bs(const dg_gemm_args* args) {
     DG_REQUIRE(num_sms > 0, "num_sms");
     TileChoice t;
     choose_tile(a, num_sms, &t);
+    if (epi != 0) t.swap = true, t.bn = a.force_block_n ? a.force_block_n : 256;
     DG_REQUIRE(t.ctas == 1 || t.ctas == 2, "cta group");
     DG_REQUIRE(!(t.swap && a.d_dtype == DG_F32), "swapped tiles write BF16 only");
     DG_REQUIRE(!(t.swap && a.accumulate), "swapped tiles do not accumulate");
@@ -472,8 +474,12 @@ int dg_gemm_bs(const dg_gemm_args* args) {
     p.status = static_cast<uint32_t*>(status_ptr);
     p.trace = g_trace;
 
+    if (epi != 0) {
+        p.moe = *moe;
+        p.r_sf_pretransposed = 1;
+    }
     // D: [groups, m, n] row-major
-    {
+    if (epi == 0) {
         const uint32_t es = a.d_dtype == DG_F32 ? 4 : 2;
         const uint64_t d_groups = p.d_grouped ? a.num_groups : 1;
         const uint64_t dims[3] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.m), d_groups};
@@ -500,6 +506,19 @@ int dg_gemm_bs(const dg_gemm_args* args) {
     p.num_units = units;
     p.raster = choose_raster(p.num_m_blocks, unit_m, unit_n, units);
 
+#define DG_TRY_MOE(CT, BNV, EPI)                                                           \
+    if (epi == EPI && t.ctas == CT && t.bn == BNV)                                         \
+        return launch_gemm<dg::GemmConfig<CT, BNV, true, false, EPI>>(p, a, units);
+    DG_TRY_MOE(2, 256, 1)
+    DG_TRY_MOE(2, 128, 1)
+    DG_TRY_MOE(1, 256, 1)
+    DG_TRY_MOE(1, 128, 1)
+    DG_TRY_MOE(2, 256, 2)
+    DG_TRY_MOE(2, 128, 2)
+    DG_TRY_MOE(1, 256, 2)
+    DG_TRY_MOE(1, 128, 2)
+#undef DG_TRY_MOE
+    if (epi != 0) return fail(DG_ERR_INVALID, "no fused-epilogue kernel for cta_group %d, block_n %d", t.ctas, t.bn);
 #define DG_TRY(CT, BNV, SW, F32)                                                           \
     if (t.ctas == CT && t.bn == BNV && t.swap == SW && (a.d_dtype == DG_F32) == F32)       \
         return launch_gemm<dg::GemmConfig<CT, BNV, SW, F32>>(p, a, units);
@@ -520,6 +539,117 @@ int dg_gemm_bs(const dg_gemm_args* args) {
 #undef DG_TRY
     return fail(DG_ERR_INVALID, "no kernel built for cta_group %d, block_n %d, swap %d, f32 %d", t.ctas, t.bn,
                 static_cast<int>(t.swap), static_cast<int>(a.d_dtype == DG_F32));
+}
+
+
+int dg_gemm_bs(const dg_gemm_args* args) {
+    DG_REQUIRE(args != nullptr, "args");
+    return run_gemm(*args, 0, nullptr);
+}
+
+// --------------------------------------------------------------------------- Mega MoE
+static int check_moe_config(const dg_moe_config& c) {
+    DG_REQUIRE(c.num_ranks > 0 && c.num_ranks <= static_cast<int>(dg::kMoeMaxRanks), "num_ranks");
+    DG_REQUIRE(c.num_experts > 0 && c.num_experts % c.num_ranks == 0, "num_experts % num_ranks == 0");
+    DG_REQUIRE(c.num_topk > 0 && c.num_topk <= c.num_experts, "num_topk");
+    DG_REQUIRE(c.num_max_tokens_per_rank > 0, "num_max_tokens_per_rank");
+    DG_REQUIRE(c.hidden > 0 && c.hidden % 128 == 0 && c.intermediate_hidden > 0 && c.intermediate_hidden % 128 == 0,
+               "hidden % 128 == 0 and intermediate_hidden % 128 == 0");
+    return DG_OK;
+}
+
+int dg_get_token_alignment_for_mega_moe(void) { return 128; }
+
+int dg_mega_moe_buffer_layout(const dg_moe_config* cfg, dg_moe_layout* out) {
+    DG_REQUIRE(cfg != nullptr && out != nullptr, "null argument");
+    int rc = check_moe_config(*cfg);
+    if (rc != DG_OK) return rc;
+    DG_REQUIRE(cfg->num_max_tokens_per_rank % dg_get_token_alignment_for_mega_moe() == 0, "token alignment");
+    const dg::MoeLayout L = dg::make_moe_layout(cfg->num_ranks, cfg->num_experts, cfg->num_max_tokens_per_rank,
+                                                cfg->num_topk, cfg->hidden, cfg->intermediate_hidden);
+    out->num_bytes = static_cast<int64_t>(L.total_bytes);
+    out->pool_rows = static_cast<int64_t>(L.pool_rows);
+    out->off_x = L.off_x, out->off_x_sf = L.off_x_sf, out->off_topk_idx = L.off_topk_idx;
+    out->off_topk_weights = L.off_topk_w, out->off_l1_acts = L.off_l1_acts, out->off_l1_acts_sf = L.off_l1_sf;
+    out->off_l2_acts = L.off_l2_acts, out->off_l2_acts_sf = L.off_l2_sf, out->off_token_src_metadata = L.off_pool_meta;
+    out->off_combine = L.off_combine;
+    return DG_OK;
+}
+
+int dg_mega_moe_forward(const dg_moe_args* args) {
+    DG_REQUIRE(args != nullptr, "args");
+    const dg_moe_args& m = *args;
+    int rc = check_moe_config(m.cfg);
+    if (rc != DG_OK) return rc;
+    DG_REQUIRE(m.rank >= 0 && m.rank < m.cfg.num_ranks, "rank");
+    DG_REQUIRE(m.num_tokens >= 0 && m.num_tokens <= m.cfg.num_max_tokens_per_rank, "num_tokens <= num_max_tokens_per_rank");
+    DG_REQUIRE(m.buffer_ptrs != nullptr && m.y != nullptr, "null argument");
+    DG_REQUIRE(m.l1_w && m.l1_sf && m.l2_w && m.l2_sf, "null weights");
+    const dg::MoeLayout L = dg::make_moe_layout(m.cfg.num_ranks, m.cfg.num_experts, m.cfg.num_max_tokens_per_rank,
+                                                m.cfg.num_topk, m.cfg.hidden, m.cfg.intermediate_hidden);
+    dg::MoeArgs a;
+    memset(&a, 0, sizeof(a));
+    a.L = L;
+    for (int r = 0; r < m.cfg.num_ranks; ++r) {
+        DG_REQUIRE(m.buffer_ptrs[r] != nullptr, "buffer_ptrs[r]");
+        a.base[r] = static_cast<uint8_t*>(m.buffer_ptrs[r]);
+    }
+    a.rank = m.rank, a.num_tokens = m.num_tokens;
+    {
+        std::lock_guard<std::mutex> lk(g_knobs.mu);
+        a.timeout_ms = g_knobs.timeout_ms;
+    }
+    void* status_ptr = nullptr;
+    DG_CUDA(cudaGetSymbolAddress(&status_ptr, g_status));
+    a.status = static_cast<uint32_t*>(status_ptr);
+    a.stats = m.stats;
+    cudaStream_t stream = static_cast<cudaStream_t>(m.stream);
+    uint8_t* mine = a.base[m.rank];
+
+    // 1. count + index scatter, 2. count exchange + barrier + pool layout, 3. pull
+    const uint32_t pairs = static_cast<uint32_t>(m.num_tokens) * L.topk;
+    if (pairs > 0) dg::moe_scatter_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(a);
+    dg::moe_exchange_kernel<<<1, 256, 0, stream>>>(a);
+    int num_sms = dg_get_num_sms();
+    DG_REQUIRE(num_sms > 0, "num_sms");
+    const uint32_t seg_smem = (L.experts_local * L.ranks + 1) * 4;
+    dg::moe_pull_kernel<<<num_sms * 4, 256, seg_smem, stream>>>(a);
+    DG_CUDA(cudaGetLastError());
+
+    // 4. first expert GEMM (+ SwiGLU, route weight, FP8 requantisation), 5. second (+ combine push)
+    dg::MoeEpilogueParams e;
+    memset(&e, 0, sizeof(e));
+    e.l2_acts = mine + L.off_l2_acts, e.l2_sf = mine + L.off_l2_sf;
+    e.pool_w = reinterpret_cast<const float*>(mine + L.off_pool_w);
+    e.pool_meta = reinterpret_cast<const int32_t*>(mine + L.off_pool_meta);
+    for (uint32_t r = 0; r < L.ranks; ++r) e.peer_base[r] = a.base[r];
+    e.off_combine = L.off_combine, e.pool_rows = L.pool_rows, e.inter = L.inter, e.hidden = L.hidden, e.t_max = L.t_max;
+    e.clamp = m.activation_clamp, e.fast_math = m.fast_math ? 1 : 0;
+    const int32_t* psum = reinterpret_cast<const int32_t*>(mine + L.off_work) + dg::MoeWork::psum_end(L.experts);
+
+    dg_gemm_args g;
+    memset(&g, 0, sizeof(g));
+    g.gemm_type = DG_GEMM_M_PSUM, g.num_groups = L.experts_local, g.alignment = dg::kMoePoolAlign;
+    g.grouped_layout = psum, g.stream = m.stream, g.alpha = 1.0f, g.d_dtype = DG_BF16;
+    g.m = L.pool_rows, g.n = 2 * L.inter, g.k = L.hidden;
+    g.a.data = mine + L.off_l1_acts, g.a.sf = reinterpret_cast<const int32_t*>(mine + L.off_l1_sf);
+    g.a.ld = L.hidden, g.a.sf_ld = L.pool_rows, g.a.dtype = DG_E4M3, g.a.gran_k = 32;
+    g.b.data = m.l1_w, g.b.sf = m.l1_sf, g.b.ld = L.hidden / 2, g.b.sf_ld = m.l1_sf_ld, g.b.dtype = DG_E2M1_PACKED;
+    g.b.gran_k = 32;
+    rc = run_gemm(g, 1, &e);
+    if (rc != DG_OK) return rc;
+    g.n = L.hidden, g.k = L.inter;
+    g.a.data = mine + L.off_l2_acts, g.a.sf = reinterpret_cast<const int32_t*>(mine + L.off_l2_sf), g.a.ld = L.inter;
+    g.b.data = m.l2_w, g.b.sf = m.l2_sf, g.b.ld = L.inter / 2, g.b.sf_ld = m.l2_sf_ld;
+    rc = run_gemm(g, 2, &e);
+    if (rc != DG_OK) return rc;
+
+    // 6. every rank has pushed its results, 7. local top-k reduction
+    dg::moe_barrier_kernel<<<1, 32, 0, stream>>>(a);
+    if (m.num_tokens > 0)
+        dg::moe_reduce_kernel<<<m.num_tokens, 128, 0, stream>>>(a, static_cast<__nv_bfloat16*>(m.y), m.ldy);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
 }
 
 }  // extern "C"

@@ -1,0 +1,269 @@
+// Mega MoE forward: buffer layout and the CUDA-core kernels around the two grouped GEMMs
+// (expert counting and index scatter, count exchange + cross-rank barrier, token pull into the
+// expert-sorted pool, top-k reduction).  Peer memory is reached through plain loads / stores on
+// the symmetric buffer's per-rank base addresses (NVLink), never through multicast loads.
+//
+// Takes the role of the dispatch / combine halves of the reference's sm100_fp8_fp4_mega_moe_impl
+// (deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh:360-729, 1588-1743) and of its
+// NVLink barrier (deep_gemm/include/deep_gemm/comm/barrier.cuh:53-92), with bounded waits.
+#pragma once
+
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace dg {
+
+constexpr uint32_t kMoeMaxRanks = 16;
+constexpr uint32_t kMoePoolAlign = 128;   // rows: every expert's pool segment starts on this boundary
+
+// Byte offsets inside one rank's symmetric buffer (identical on every rank).
+struct MoeLayout {
+    uint32_t ranks, experts, experts_local, t_max, topk, hidden, inter;
+    uint32_t pool_rows;      // capacity of the expert-sorted pool (multiple of 256)
+    uint64_t off_signals;    // u32 [2][kMoeMaxRanks]: barrier flags written by peers
+    uint64_t off_recv_count; // u32 [ranks][experts_local]: rows each source rank sends to each local expert
+    uint64_t off_src_idx;    // u32 [experts_local][ranks][t_max]: token * topk + slot, written by the source rank
+    uint64_t off_x, off_x_sf, off_topk_idx, off_topk_w;   // inputs the caller fills
+    uint64_t off_l1_acts, off_l1_sf, off_pool_w, off_pool_meta, off_l2_acts, off_l2_sf;
+    uint64_t off_combine;    // bf16 [topk][t_max][hidden]: written by the experts' ranks
+    uint64_t off_work;       // local scratch, see MoeWork
+    uint64_t total_bytes;
+};
+
+// Local scratch at off_work (u32 words)
+struct MoeWork {
+    static constexpr uint32_t kCall = 0;        // calls made so far (epoch of the barrier flags)
+    static constexpr uint32_t kTotalRows = 1;   // pool rows in use, aligned
+    static constexpr uint32_t kSendCount = 16;  // [experts]
+    __host__ __device__ static uint32_t psum_end(uint32_t experts) { return kSendCount + experts; }   // [experts_local]
+    __host__ __device__ static uint32_t seg_off(uint32_t experts, uint32_t el) { return psum_end(experts) + el; }
+    // [experts_local * ranks]: first pool row of each (expert, source) segment
+    __host__ __device__ static uint32_t seg_prefix(uint32_t experts, uint32_t el, uint32_t ranks) {
+        return seg_off(experts, el) + el * ranks;
+    }   // [experts_local * ranks + 1]: rows before each segment, unaligned (the pull kernel's work list)
+    __host__ __device__ static uint32_t words(uint32_t experts, uint32_t el, uint32_t ranks) {
+        return seg_prefix(experts, el, ranks) + el * ranks + 1;
+    }
+};
+
+inline uint64_t moe_align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
+
+inline MoeLayout make_moe_layout(uint32_t ranks, uint32_t experts, uint32_t t_max, uint32_t topk, uint32_t hidden,
+                                 uint32_t inter) {
+    MoeLayout L{};
+    L.ranks = ranks, L.experts = experts, L.experts_local = experts / ranks, L.t_max = t_max, L.topk = topk;
+    L.hidden = hidden, L.inter = inter;
+    const uint64_t active_topk = topk < L.experts_local ? topk : L.experts_local;
+    L.pool_rows = static_cast<uint32_t>(moe_align_up(static_cast<uint64_t>(t_max) * ranks * active_topk +
+                                                     static_cast<uint64_t>(L.experts_local) * kMoePoolAlign, 256));
+    uint64_t off = 0;
+    auto take = [&](uint64_t bytes) {
+        const uint64_t o = off;
+        off = moe_align_up(off + bytes, 1024);
+        return o;
+    };
+    L.off_signals = take(2 * kMoeMaxRanks * 4);
+    L.off_recv_count = take(static_cast<uint64_t>(ranks) * L.experts_local * 4);
+    L.off_src_idx = take(static_cast<uint64_t>(L.experts_local) * ranks * t_max * 4);
+    L.off_x = take(static_cast<uint64_t>(t_max) * hidden);
+    L.off_x_sf = take(static_cast<uint64_t>(t_max) * (hidden / 128) * 4);
+    L.off_topk_idx = take(static_cast<uint64_t>(t_max) * topk * 8);
+    L.off_topk_w = take(static_cast<uint64_t>(t_max) * topk * 4);
+    L.off_l1_acts = take(static_cast<uint64_t>(L.pool_rows) * hidden);
+    L.off_l1_sf = take(static_cast<uint64_t>(L.pool_rows) * (hidden / 128) * 4);
+    L.off_pool_w = take(static_cast<uint64_t>(L.pool_rows) * 4);
+    L.off_pool_meta = take(static_cast<uint64_t>(L.pool_rows) * 12);
+    L.off_l2_acts = take(static_cast<uint64_t>(L.pool_rows) * inter);
+    L.off_l2_sf = take(static_cast<uint64_t>(L.pool_rows) * (inter / 128) * 4);
+    L.off_combine = take(static_cast<uint64_t>(topk) * t_max * hidden * 2);
+    L.off_work = take(static_cast<uint64_t>(MoeWork::words(experts, L.experts_local, ranks)) * 4);
+    L.total_bytes = off;
+    return L;
+}
+
+struct MoeArgs {
+    MoeLayout L;
+    uint8_t* base[kMoeMaxRanks];   // base address of every rank's buffer as mapped into this process
+    uint32_t rank, num_tokens, timeout_ms;
+    uint32_t* status;              // status block shared with the GEMM kernels
+    int32_t* stats;                // cumulative_local_expert_recv_stats [experts_local] or null
+};
+
+enum : uint32_t { kStatusPeerTimeout = 2 };
+
+DG_DEVICE void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+DG_DEVICE uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Signal every peer with `value` in slot `which`, then wait (bounded) until every peer has signalled
+// at least `value`.  Called by threads 0..ranks-1 of one CTA; returns false on timeout.
+DG_DEVICE bool moe_cross_rank_barrier(const MoeArgs& a, uint32_t which, uint32_t value, uint32_t peer) {
+    __threadfence_system();
+    uint32_t* remote = reinterpret_cast<uint32_t*>(a.base[peer] + a.L.off_signals) + which * kMoeMaxRanks + a.rank;
+    st_release_sys(remote, value);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(a.base[a.rank] + a.L.off_signals) + which * kMoeMaxRanks + peer;
+    const uint64_t t0 = global_timer_ns();
+    const uint64_t budget = static_cast<uint64_t>(a.timeout_ms) * 1000000ull;
+    while (static_cast<int32_t>(ld_acquire_sys(mine) - value) < 0) {
+        __nanosleep(200);
+        if (global_timer_ns() - t0 > budget) {
+            if (atomicCAS(a.status, 0u, kStatusPeerTimeout) == 0u) {
+                a.status[1] = 100 + which, a.status[2] = peer, a.status[3] = value;
+                __threadfence_system();
+            }
+            return false;
+        }
+    }
+    return true;
+}
+
+// ---- step 1: count (token, slot) pairs per expert and tell the expert's rank which pairs to pull.
+// grid: ceil(num_tokens * topk / 256), block 256
+__global__ void __launch_bounds__(256) moe_scatter_kernel(const MoeArgs a) {
+    const uint32_t i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= a.num_tokens * a.L.topk) return;
+    const long long e = reinterpret_cast<const long long*>(a.base[a.rank] + a.L.off_topk_idx)[i];
+    if (e < 0 || e >= static_cast<long long>(a.L.experts)) return;
+    uint32_t* work = reinterpret_cast<uint32_t*>(a.base[a.rank] + a.L.off_work);
+    const uint32_t j = atomicAdd(work + MoeWork::kSendCount + static_cast<uint32_t>(e), 1u);
+    const uint32_t dest = static_cast<uint32_t>(e) / a.L.experts_local, el = static_cast<uint32_t>(e) % a.L.experts_local;
+    uint32_t* idx = reinterpret_cast<uint32_t*>(a.base[dest] + a.L.off_src_idx);
+    idx[(static_cast<uint64_t>(el) * a.L.ranks + a.rank) * a.L.t_max + j] = i;
+}
+
+// ---- step 2: publish the counts, cross-rank barrier, then lay out the pool.  One CTA of 256 threads.
+__global__ void __launch_bounds__(256) moe_exchange_kernel(const MoeArgs a) {
+    const MoeLayout& L = a.L;
+    uint32_t* work = reinterpret_cast<uint32_t*>(a.base[a.rank] + L.off_work);
+    __shared__ uint32_t s_call, s_ok;
+    if (threadIdx.x == 0) {
+        s_call = ++work[MoeWork::kCall];
+        s_ok = 1;
+    }
+    for (uint32_t e = threadIdx.x; e < L.experts; e += 256) {
+        const uint32_t cnt = work[MoeWork::kSendCount + e];
+        work[MoeWork::kSendCount + e] = 0;   // ready for the next call
+        const uint32_t dest = e / L.experts_local, el = e % L.experts_local;
+        reinterpret_cast<uint32_t*>(a.base[dest] + L.off_recv_count)[a.rank * L.experts_local + el] = cnt;
+    }
+    __syncthreads();
+    if (threadIdx.x < L.ranks)
+        if (!moe_cross_rank_barrier(a, 0, 2 * s_call - 1, threadIdx.x)) s_ok = 0;
+    __syncthreads();
+    if (!s_ok) return;
+    // Pool layout: expert el owns rows [align(prev_end), end); inside, sources in rank order.
+    const uint32_t* recv = reinterpret_cast<const uint32_t*>(a.base[a.rank] + L.off_recv_count);
+    int32_t* meta = reinterpret_cast<int32_t*>(a.base[a.rank] + L.off_pool_meta);
+    if (threadIdx.x == 0) {
+        uint32_t prev_end = 0, flat = 0;
+        for (uint32_t el = 0; el < L.experts_local; ++el) {
+            const uint32_t start = (prev_end + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
+            uint32_t row = start;
+            for (uint32_t src = 0; src < L.ranks; ++src) {
+                const uint32_t cnt = recv[src * L.experts_local + el];
+                work[MoeWork::seg_off(L.experts, L.experts_local) + el * L.ranks + src] = row;
+                work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + el * L.ranks + src] = flat;
+                row += cnt, flat += cnt;
+            }
+            work[MoeWork::psum_end(L.experts) + el] = row;
+            if (a.stats != nullptr) a.stats[el] += static_cast<int32_t>(row - start);
+            prev_end = row;
+        }
+        work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + L.experts_local * L.ranks] = flat;
+        work[MoeWork::kTotalRows] = (prev_end + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
+    }
+    __syncthreads();
+    // Rows between an expert's end and the next boundary carry no token: mark them
+    for (uint32_t el = 0; el < L.experts_local; ++el) {
+        const uint32_t end = work[MoeWork::psum_end(L.experts) + el];
+        const uint32_t stop = (end + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
+        for (uint32_t r = end + threadIdx.x; r < stop; r += 256) meta[r * 3] = -1;
+    }
+}
+
+// ---- step 3: pull every routed token (row, packed scales, route weight) into the pool.  One warp per row.
+__global__ void __launch_bounds__(256) moe_pull_kernel(const MoeArgs a) {
+    const MoeLayout& L = a.L;
+    const uint32_t* work = reinterpret_cast<const uint32_t*>(a.base[a.rank] + L.off_work);
+    extern __shared__ uint32_t s_prefix[];   // [segments + 1]
+    const uint32_t segments = L.experts_local * L.ranks;
+    for (uint32_t i = threadIdx.x; i <= segments; i += 256)
+        s_prefix[i] = work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + i];
+    __syncthreads();
+    const uint32_t total = s_prefix[segments];
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warps = gridDim.x * 8;
+    const uint32_t* src_idx = reinterpret_cast<const uint32_t*>(a.base[a.rank] + L.off_src_idx);
+    uint8_t* l1 = a.base[a.rank] + L.off_l1_acts;
+    uint32_t* l1_sf = reinterpret_cast<uint32_t*>(a.base[a.rank] + L.off_l1_sf);
+    float* pool_w = reinterpret_cast<float*>(a.base[a.rank] + L.off_pool_w);
+    int32_t* meta = reinterpret_cast<int32_t*>(a.base[a.rank] + L.off_pool_meta);
+    const uint32_t sf_words = L.hidden / 128;
+    for (uint32_t r = blockIdx.x * 8 + threadIdx.x / 32; r < total; r += warps) {
+        // segment holding flat row r: last i with prefix[i] <= r
+        uint32_t lo = 0, hi = segments;
+        while (hi - lo > 1) {
+            const uint32_t mid = (lo + hi) / 2;
+            if (s_prefix[mid] <= r) lo = mid; else hi = mid;
+        }
+        const uint32_t el = lo / L.ranks, src = lo % L.ranks, j = r - s_prefix[lo];
+        const uint32_t pair = src_idx[(static_cast<uint64_t>(el) * L.ranks + src) * L.t_max + j];
+        const uint32_t token = pair / L.topk, slot = pair % L.topk;
+        const uint32_t dst = work[MoeWork::seg_off(L.experts, L.experts_local) + lo] + j;
+        const uint8_t* peer = a.base[src];
+        const uint4* from = reinterpret_cast<const uint4*>(peer + L.off_x + static_cast<uint64_t>(token) * L.hidden);
+        uint4* to = reinterpret_cast<uint4*>(l1 + static_cast<uint64_t>(dst) * L.hidden);
+        for (uint32_t c = lane; c < L.hidden / 16; c += 32) to[c] = from[c];
+        const uint32_t* sf_from = reinterpret_cast<const uint32_t*>(peer + L.off_x_sf) + static_cast<uint64_t>(token) * sf_words;
+        for (uint32_t c = lane; c < sf_words; c += 32) l1_sf[static_cast<uint64_t>(c) * L.pool_rows + dst] = sf_from[c];
+        if (lane == 0) {
+            pool_w[dst] = reinterpret_cast<const float*>(peer + L.off_topk_w)[pair];
+            meta[dst * 3 + 0] = static_cast<int32_t>(src);
+            meta[dst * 3 + 1] = static_cast<int32_t>(token);
+            meta[dst * 3 + 2] = static_cast<int32_t>(slot);
+        }
+    }
+}
+
+// ---- cross-rank barrier on its own (after the experts' ranks have pushed their results).  One CTA.
+__global__ void __launch_bounds__(32) moe_barrier_kernel(const MoeArgs a) {
+    const uint32_t* work = reinterpret_cast<const uint32_t*>(a.base[a.rank] + a.L.off_work);
+    if (threadIdx.x < a.L.ranks) moe_cross_rank_barrier(a, 1, 2 * work[MoeWork::kCall], threadIdx.x);
+}
+
+// ---- last step: y[t] = bf16(sum over the token's valid slots, in slot order, of its combine rows).
+// grid: num_tokens, block: 128; each thread owns 8 consecutive columns per pass.
+__global__ void __launch_bounds__(128) moe_reduce_kernel(const MoeArgs a, __nv_bfloat16* y, int64_t ldy) {
+    const MoeLayout& L = a.L;
+    const uint32_t t = blockIdx.x;
+    const long long* idx = reinterpret_cast<const long long*>(a.base[a.rank] + L.off_topk_idx) + static_cast<uint64_t>(t) * L.topk;
+    const uint8_t* combine = a.base[a.rank] + L.off_combine;
+    for (uint32_t c = threadIdx.x * 8; c < L.hidden; c += 128 * 8) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (uint32_t s = 0; s < L.topk; ++s) {
+            const long long e = idx[s];
+            if (e < 0 || e >= static_cast<long long>(L.experts)) continue;
+            const uint4 v = *reinterpret_cast<const uint4*>(
+                combine + ((static_cast<uint64_t>(s) * L.t_max + t) * L.hidden + c) * 2);
+            const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(b[i]);
+                acc[2 * i] += f.x, acc[2 * i + 1] += f.y;
+            }
+        }
+        uint4 out;
+        __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(y) + (static_cast<uint64_t>(t) * ldy + c) * 2) = out;
+    }
+}
+
+}  // namespace dg

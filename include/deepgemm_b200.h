@@ -114,6 +114,60 @@ int dg_sf_pack_ue8m0_k_grouped(const float* sf, int32_t* out, const int32_t* gro
                                int32_t mn, int32_t sf_k_rows, int32_t packed_rows, int32_t gran_k,
                                int32_t k_alignment, int32_t use_psum, void* stream);
 
+
+/* ---- Mega MoE forward (expert parallel over the GPUs of one node) ------------------------------------
+ * One symmetric buffer per rank (same layout everywhere) holds the caller's inputs, the exchange tables,
+ * the expert-sorted token pool and the combine planes; `buffer_ptrs[r]` is rank r's buffer as mapped into
+ * the calling process (peer access over NVLink; with one rank, the buffer itself). */
+typedef struct dg_moe_config {
+    int32_t num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden;
+} dg_moe_config;
+
+/* Byte offsets of the views inside one rank's buffer (shapes as in csrc/apis/mega_moe.hpp:137-226 of the
+ * reference): x e4m3 [T, H]; x_sf int32 [T, H/128]; topk_idx int64 [T, K]; topk_weights f32 [T, K];
+ * l1_acts e4m3 [P, H]; l1_acts_sf int32 [P, H/128] with strides (1, P); l2_acts e4m3 [P, I];
+ * l2_acts_sf int32 [P, I/128] with strides (1, P); token_src_metadata int32 [P, 3];
+ * combine bf16 [K, T, H].  P = pool_rows. */
+typedef struct dg_moe_layout {
+    int64_t num_bytes, pool_rows;
+    int64_t off_x, off_x_sf, off_topk_idx, off_topk_weights;
+    int64_t off_l1_acts, off_l1_acts_sf, off_l2_acts, off_l2_acts_sf, off_token_src_metadata, off_combine;
+} dg_moe_layout;
+
+/* Size and view offsets of the symmetric buffer.  Takes the role of get_symm_buffer_size_for_mega_moe_v3
+ * (csrc/apis/mega_moe.hpp:73-229); the byte layout is this library's own. */
+int dg_mega_moe_buffer_layout(const dg_moe_config* cfg, dg_moe_layout* out);
+
+/* Row granularity of num_max_tokens_per_rank (csrc/apis/mega_moe.hpp:34-36). */
+int dg_get_token_alignment_for_mega_moe(void);
+
+typedef struct dg_moe_args {
+    dg_moe_config cfg;
+    void* const* buffer_ptrs;   /* host array [num_ranks] of device addresses */
+    int32_t rank;
+    int32_t num_tokens;         /* rows of y and of the inputs in use on this rank */
+    void* y;                    /* bf16 [num_tokens, hidden] */
+    int64_t ldy;                /* elements between rows of y */
+    /* Expert weights of this rank as produced by transform_weights_for_mega_moe
+     * (deep_gemm/mega/__init__.py:201-220): MXFP4 codes [E_local, 2I, H/2] with gate / up rows interleaved in
+     * blocks of 8 and [E_local, H, I/2]; packed UE8M0 scales MN-major, rows permuted per 128 for tcgen05.cp. */
+    const void* l1_w;
+    const int32_t* l1_sf;
+    const void* l2_w;
+    const int32_t* l2_sf;
+    int64_t l1_sf_ld, l2_sf_ld; /* words between packed-K columns of the scale tensors */
+    int32_t* stats;             /* optional int32 [E_local]: += rows received per local expert */
+    float activation_clamp;     /* +inf: none */
+    int32_t fast_math;
+    void* stream;
+} dg_moe_args;
+
+/* y[t] = bf16( sum over slots of bf16( Q32( SwiGLU(bf16(x_t W13_e^T)) * w_{t,slot} ) W2_e^T ) ) with the tokens
+ * dispatched to the experts' ranks and the results combined back over NVLink peer memory.  Takes the role of
+ * fp8_fp4_mega_moe (csrc/apis/mega_moe.hpp:321-519, impls/sm100_fp8_fp4_mega_moe.cuh).  Every rank of the
+ * group must make the call; calls on one buffer must not overlap. */
+int dg_mega_moe_forward(const dg_moe_args* args);
+
 /* Process-wide knobs (csrc/apis/config.hpp:8-48, csrc/apis/layout.hpp:138-146 of the reference). */
 int dg_set_num_sms(int32_t num_sms);
 int dg_get_num_sms(void);           /* device SM count unless overridden */

@@ -1,0 +1,137 @@
+"""GPU parity of the Mega MoE forward against the CPU oracle (oracle/mega_moe.py).
+
+Bit-exact: dispatched token rows / scales, routing metadata (as sets per local expert), received-row
+statistics.  Floating point: calc_diff <= 2e-4 against the dequantised reference, the bound the
+reference's own test uses (tests/test_mega_moe.py:540-549).
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+import deepgemm_b200 as dg
+import helpers as H
+from oracle import mega_moe as OM
+from oracle import quant as OQ
+
+MOE_TOL = 2e-4
+
+
+def make_weights(num_experts, hidden, inter, seed=1234, device="cuda"):
+    """All experts from one seed (tests/test_mega_moe.py:490-511): MXFP4 1x32, dequantised copies for the oracle."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    l1 = (torch.randn((num_experts, 2 * inter, hidden), generator=g) * (2 / hidden ** 0.5)).to(torch.bfloat16)
+    l2 = (torch.randn((num_experts, hidden, inter), generator=g) * (1 / inter ** 0.5)).to(torch.bfloat16)
+
+    def cast(w):
+        q, sf = [], []
+        for i in range(w.shape[0]):
+            a, b = dg.utils.per_token_cast_to_fp4(w[i].to(device), use_ue8m0=True, gran_k=32)
+            q.append(a), sf.append(b)
+        q, sf = torch.stack(q), torch.stack(sf)
+        deq = np.stack([OQ.cast_back_from_fp4(H.to_np(q[i]), H.to_np(sf[i]), 32) for i in range(w.shape[0])])
+        return q, sf, deq
+
+    return cast(l1), cast(l2)
+
+
+def make_inputs(num_tokens, hidden, num_experts, topk, seed, device="cuda", drop=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = torch.randn((num_tokens, hidden), generator=g).to(torch.bfloat16).to(device)
+    scores = torch.randn((num_tokens, num_experts), generator=g).to(device)
+    w, idx = torch.topk(scores.softmax(dim=-1), topk, dim=-1, sorted=False)
+    w = w / w.sum(dim=-1, keepdim=True)
+    if drop:
+        idx[::drop, 0] = -1                                    # masked slots are skipped
+    x_fp8, x_sf = dg.utils.per_token_cast_to_fp8(x, use_ue8m0=True, gran_k=32, use_packed_ue8m0=True)
+    x_deq = OQ.cast_back_from_fp8(H.to_np(x_fp8), H.to_np(x_sf), 32, use_packed_ue8m0=True)
+    return x_fp8, x_sf, idx, w.float(), x_deq
+
+
+def run_rank(group, rank, ranks, cfg, results=None):
+    hidden, inter, experts, topk, tokens, clamp, drop = cfg
+    el = experts // ranks
+    (q1, sf1, deq1), (q2, sf2, deq2) = make_weights(experts, hidden, inter)
+    lo = rank * el
+    l1 = (q1[lo:lo + el].contiguous(),
+          dg.transform_sf_into_required_layout(sf1[lo:lo + el].contiguous(), 2 * inter, hidden, (1, 32), el))
+    l2 = (q2[lo:lo + el].contiguous(),
+          dg.transform_sf_into_required_layout(sf2[lo:lo + el].contiguous(), hidden, inter, (1, 32), el))
+    l1, l2 = dg.transform_weights_for_mega_moe(l1, l2)
+    x_fp8, x_sf, idx, w, x_deq = make_inputs(tokens, hidden, experts, topk, 100 + rank, drop=drop)
+    buf = dg.get_symm_buffer_for_mega_moe(group, experts, tokens, topk, hidden, inter)
+    stats = torch.zeros(el, dtype=torch.int32, device="cuda")
+    y = None
+    for it in range(2):                                        # twice: the buffer's epochs and counters must reset
+        buf.x[:tokens].copy_(x_fp8)
+        buf.x_sf[:tokens].copy_(x_sf)
+        buf.topk_idx[:tokens].copy_(idx)
+        buf.topk_weights[:tokens].copy_(w)
+        y_it = torch.full((tokens, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+        dg.fp8_fp4_mega_moe(y_it, l1, l2, buf, cumulative_local_expert_recv_stats=stats, activation_clamp=clamp)
+        torch.cuda.synchronize()
+        dg.check_status()
+        if group is not None:
+            group.barrier()
+        if y is not None:
+            assert torch.equal(y, y_it), "second call differs"
+        y = y_it
+    ref, counts = OM.mega_moe_reference(x_deq, idx.cpu().numpy(), w.cpu().numpy(), deq1, deq2, clamp)
+    diff = H.calc_diff(H.to_np(y), ref)
+    assert not np.isnan(H.to_np(y)).any()
+    assert diff < MOE_TOL, f"rank {rank}: calc_diff {diff}"
+    # Integer-exact side: rows received per local expert (over all ranks' tokens) and the pool's routing metadata
+    all_idx = [make_inputs(tokens, hidden, experts, topk, 100 + r, drop=drop)[2].cpu().numpy() for r in range(ranks)]
+    expect = np.array([sum(int((a == lo + e).sum()) for a in all_idx) for e in range(el)])
+    assert np.array_equal(stats.cpu().numpy(), 2 * expect)
+    meta = buf.token_src_metadata.cpu().numpy()
+    l1_acts = buf.l1_acts.view(torch.uint8)
+    start = 0
+    for e in range(el):
+        rows = meta[start:start + expect[e]]
+        got = {tuple(r) for r in rows}
+        want = {(r, int(t), int(s)) for r in range(ranks) for t, s in zip(*np.nonzero(all_idx[r] == lo + e))}
+        assert got == want, f"expert {e}"
+        mine = [(i, t) for i, (r, t, s) in enumerate(rows) if r == rank][:8]
+        for i, t in mine:                                      # dispatched rows are byte copies of the source rows
+            assert torch.equal(l1_acts[start + i], x_fp8.view(torch.uint8)[t])
+        start = (start + expect[e] + 127) // 128 * 128
+    buf.destroy()
+    if results is not None:
+        results[rank] = diff
+    return diff
+
+
+@pytest.mark.parametrize("cfg", [
+    (1024, 512, 8, 4, 96, None, 0),          # hidden, inter, experts, topk, tokens, clamp, drop
+    (2048, 1024, 16, 4, 700, 10.0, 5),
+    (4096, 1536, 16, 4, 96, None, 0),        # the reference's own activation-test shape
+    (7168, 2048, 8, 8, 1000, None, 0),       # production hidden / intermediate, few experts
+])
+def test_mega_moe_single_rank(cfg):
+    run_rank(None, 0, 1, cfg)
+
+
+def _worker(local_rank, ranks, cfg, port, results):
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", world_size=ranks, rank=local_rank)
+    try:
+        run_rank(dist.group.WORLD, local_rank, ranks, cfg, results)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("ranks", [2, 4, 8])
+def test_mega_moe_expert_parallel(ranks):
+    if torch.cuda.device_count() < ranks:
+        pytest.skip(f"needs {ranks} GPUs")
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import torch.multiprocessing as mp
+    results = mp.get_context("spawn").Manager().dict()
+    cfg = (2048, 1024, 8 * ranks, 4, 300, None, 7)
+    mp.spawn(_worker, args=(ranks, cfg, 29531 + ranks, results), nprocs=ranks, join=True)
+    assert len(results) == ranks and all(v < MOE_TOL for v in results.values())

@@ -106,3 +106,33 @@ def test_sf_layout_validation_messages():
         dg.transform_sf_into_required_layout(bad, 64, 1024, (1, 128))
     with pytest.raises(RuntimeError, match="is_sfa"):
         dg.transform_sf_into_required_layout(good, 64, 1024, (1, 1, 128))
+
+
+def test_mega_moe_weight_transform_matches_oracle_permutations():
+    from oracle import layout as OL
+    g, n, h = 2, 256, 512
+    w = torch.randint(-128, 127, (g, n, h // 2), dtype=torch.int8)
+    sf_store = torch.randint(0, 2 ** 31 - 1, (g, h // 128, n), dtype=torch.int32)
+    sf = sf_store.transpose(1, 2)                              # [g, n, pk] with MN-major strides
+    w2 = torch.randint(-128, 127, (g, h, n // 4), dtype=torch.int8)
+    sf2 = torch.randint(0, 2 ** 31 - 1, (g, (n // 2) // 128, h), dtype=torch.int32).transpose(1, 2)
+    (t1, tsf1), (t2, tsf2) = dg.transform_weights_for_mega_moe((w, sf), (w2, sf2))
+    assert np.array_equal(t1.numpy(), OL.interleave_gate_up(w.numpy()))
+    assert np.array_equal(tsf1.numpy(), OL.transpose_sf_for_utccp(OL.interleave_gate_up(sf.numpy())))
+    assert np.array_equal(tsf2.numpy(), OL.transpose_sf_for_utccp(sf2.numpy()))
+    assert t2.data_ptr() == w2.data_ptr()
+    assert tsf1.stride() == sf.stride() and tsf2.stride() == sf2.stride()      # still MN-major
+
+
+def test_mega_moe_buffer_layout_and_checks():
+    cfg = _lib.MoeConfig(8, 256, 4096, 8, 7168, 2048)
+    lay = _lib.MoeLayout()
+    assert _lib.lib().dg_mega_moe_buffer_layout(ctypes.byref(cfg), ctypes.byref(lay)) == 0
+    offs = [lay.off_x, lay.off_x_sf, lay.off_topk_idx, lay.off_topk_weights, lay.off_l1_acts, lay.off_l1_acts_sf,
+            lay.off_l2_acts, lay.off_l2_acts_sf, lay.off_combine]
+    assert all(o % 1024 == 0 for o in offs) and len(set(offs)) == len(offs) and lay.num_bytes > max(offs)
+    assert lay.pool_rows >= 4096 * 8 * 8 and lay.pool_rows % 256 == 0
+    bad = _lib.MoeConfig(3, 256, 4096, 8, 7168, 2048)
+    assert _lib.lib().dg_mega_moe_buffer_layout(ctypes.byref(bad), ctypes.byref(lay)) != 0
+    assert b"num_experts" in _lib.lib().dg_last_error()
+    assert dg.get_token_alignment_for_mega_moe() == 128
