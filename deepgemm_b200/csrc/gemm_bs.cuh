@@ -283,7 +283,8 @@ struct GemmConfig {
     // Fused epilogues stage 32 tokens x 128 rows of BF16 per buffer (row pitch padded for kEpi == 1)
     static constexpr uint32_t MOE_PITCH = kEpi == 1 ? 272 : 256;
     static constexpr uint32_t CD_BYTES = kEpi == 0 ? kStoreBufs * 4 * SLAB_BYTES
-                                                   : (2 * 32 * MOE_PITCH + 1023) / 1024 * 1024;
+                                                   : (2 * 32 * MOE_PITCH + 2 * 256 * 8 + 1023) / 1024 * 1024;
+    static constexpr uint32_t MOE_TABLE_OFF = 2 * 32 * MOE_PITCH;   // per-tile token tables, two copies
 
     static constexpr uint32_t kSmemLimit = 232448;
     static constexpr uint32_t kBarrierBytes = 1024;
@@ -651,6 +652,28 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                 const TileCoord& tc = tiles[sub];
                 const uint32_t acc = acc_iter & 1;
                 const uint32_t acc_phase = (acc_iter >> 1) & 1;
+                if constexpr (Cfg::kEpi != 0) {
+                    // Per-token data of this tile, fetched while the UMMAs still run: route weights (kEpi 1) or
+                    // destination addresses in the source ranks' combine planes (kEpi 2; 0 = row carries no token)
+                    uint64_t* table = reinterpret_cast<uint64_t*>(smem_gen + (smem_cd - smem_base) + Cfg::MOE_TABLE_OFF) +
+                                      acc * 256;
+                    for (uint32_t tok = q * 32 + lane; tok < tc.rows; tok += 128) {
+                        const uint32_t row = tc.row0 + tok;
+                        if constexpr (Cfg::kEpi == 1) {
+                            reinterpret_cast<float*>(table)[tok] = p.moe.pool_w[row];
+                        } else {
+                            const int32_t src_rank = p.moe.pool_meta[row * 3];
+                            uint64_t dst = 0;
+                            if (src_rank >= 0) {
+                                const uint64_t token = static_cast<uint32_t>(p.moe.pool_meta[row * 3 + 1]);
+                                const uint64_t slot = static_cast<uint32_t>(p.moe.pool_meta[row * 3 + 2]);
+                                dst = reinterpret_cast<uint64_t>(p.moe.peer_base[src_rank]) + p.moe.off_combine +
+                                      (slot * p.moe.t_max + token) * p.moe.hidden * 2;
+                            }
+                            table[tok] = dst;
+                        }
+                    }
+                }
                 ok = wait_barrier(&bars->tmem_full[acc], acc_phase, abort_flag, peer_abort, p, kSiteEpilogueTmemFull,
                                   acc_iter, 0, acc);
                 if (!ok) break;
@@ -758,79 +781,76 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                         const uint32_t et = q * 32 + lane;           // epilogue thread 0..127
                         const uint32_t chunk_rows = min(32u, tc.rows - ch * 32);
                         if constexpr (Cfg::kEpi == 1) {
-                            // Thread (token t, group g): 32 intermediate outputs = 64 interleaved rows
-                            // laid out as 4 x [8 gate | 8 up] (weights interleaved in blocks of 8 rows).
-                            const uint32_t t = et & 31, g = et >> 5;
-                            if (g < 2 && t < chunk_rows) {
-                                const uint32_t row = m0 + ch * 32 + t;
-                                const float w = p.moe.pool_w[row];
-                                const uint4* src = reinterpret_cast<const uint4*>(stage_gen + t * Cfg::MOE_PITCH + g * 128);
-                                float act[32];
-                                float amax = 0.f;
+                            // A warp takes 8 tokens; lane = (token, 32-output group g, half): 16 outputs per
+                            // thread = 32 interleaved rows laid out as 2 x [8 gate | 8 up] (the weights come
+                            // interleaved in blocks of 8 rows); the two halves of a group share their amax.
+                            const uint32_t t = q * 8 + (lane >> 2), g = (lane >> 1) & 1, half = lane & 1;
+                            const float* wtab = reinterpret_cast<const float*>(
+                                reinterpret_cast<const uint64_t*>(smem_gen + (smem_cd - smem_base) + Cfg::MOE_TABLE_OFF) + acc * 256);
+                            const float w = wtab[min(ch * 32 + t, 255u)];
+                            const uint4* src = reinterpret_cast<const uint4*>(stage_gen + t * Cfg::MOE_PITCH + g * 128 + half * 64);
+                            float act[16];
+                            float amax = 0.f;
 #pragma unroll
-                                for (uint32_t blk = 0; blk < 4; ++blk) {
-                                    const uint4 gv = src[2 * blk], uv = src[2 * blk + 1];
-                                    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
-                                    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+                            for (uint32_t blk = 0; blk < 2; ++blk) {
+                                const uint4 gv = src[2 * blk], uv = src[2 * blk + 1];
+                                const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+                                const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
 #pragma unroll
-                                    for (uint32_t j = 0; j < 4; ++j) {
-                                        float2 gf = __bfloat1622float2(g2[j]), uf = __bfloat1622float2(u2[j]);
-                                        gf.x = fminf(gf.x, p.moe.clamp), gf.y = fminf(gf.y, p.moe.clamp);
-                                        uf.x = fminf(fmaxf(uf.x, -p.moe.clamp), p.moe.clamp);
-                                        uf.y = fminf(fmaxf(uf.y, -p.moe.clamp), p.moe.clamp);
-                                        float sx, sy;
-                                        if (p.moe.fast_math) {
-                                            sx = gf.x * __frcp_rn(1.0f + __expf(-gf.x));
-                                            sy = gf.y * __frcp_rn(1.0f + __expf(-gf.y));
-                                        } else {
-                                            sx = gf.x / (1.0f + expf(-gf.x));
-                                            sy = gf.y / (1.0f + expf(-gf.y));
-                                        }
-                                        const float ax = (sx * uf.x) * w, ay = (sy * uf.y) * w;
-                                        act[blk * 8 + j * 2] = ax, act[blk * 8 + j * 2 + 1] = ay;
-                                        amax = fmaxf(amax, fmaxf(fabsf(ax), fabsf(ay)));
+                                for (uint32_t j = 0; j < 4; ++j) {
+                                    float2 gf = __bfloat1622float2(g2[j]), uf = __bfloat1622float2(u2[j]);
+                                    gf.x = fminf(gf.x, p.moe.clamp), gf.y = fminf(gf.y, p.moe.clamp);
+                                    uf.x = fminf(fmaxf(uf.x, -p.moe.clamp), p.moe.clamp);
+                                    uf.y = fminf(fmaxf(uf.y, -p.moe.clamp), p.moe.clamp);
+                                    float sx, sy;
+                                    if (p.moe.fast_math) {
+                                        sx = gf.x * __frcp_rn(1.0f + __expf(-gf.x));
+                                        sy = gf.y * __frcp_rn(1.0f + __expf(-gf.y));
+                                    } else {
+                                        sx = gf.x / (1.0f + expf(-gf.x));
+                                        sy = gf.y / (1.0f + expf(-gf.y));
                                     }
+                                    const float ax = (sx * uf.x) * w, ay = (sy * uf.y) * w;
+                                    act[blk * 8 + j * 2] = ax, act[blk * 8 + j * 2 + 1] = ay;
+                                    amax = fmaxf(amax, fmaxf(fabsf(ax), fabsf(ay)));
                                 }
-                                // Power-of-two scale 2^e >= amax / 448, floor 2^-22 (amax clamp 1e-4): the add
-                                // carries into the exponent iff the mantissa exceeds that of 448 = 1.75 * 2^8
-                                uint32_t e = (__float_as_uint(amax) + 0x1FFFFFu) >> 23;
-                                e = max(e, 113u) - 8u;
-                                const float inv = __uint_as_float((254u - e) << 23);
-                                uint32_t packed[8];
+                            }
+                            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                            // Power-of-two scale 2^e >= amax / 448, floor 2^-22 (amax clamp 1e-4): the add
+                            // carries into the exponent iff the mantissa exceeds that of 448 = 1.75 * 2^8
+                            uint32_t e = (__float_as_uint(amax) + 0x1FFFFFu) >> 23;
+                            e = max(e, 113u) - 8u;
+                            const float inv = __uint_as_float((254u - e) << 23);
+                            uint32_t packed[4];
 #pragma unroll
-                                for (uint32_t j = 0; j < 8; ++j) {
-                                    const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
-                                        make_float2(act[4 * j] * inv, act[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
-                                    const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
-                                        make_float2(act[4 * j + 2] * inv, act[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
-                                    packed[j] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-                                }
+                            for (uint32_t j = 0; j < 4; ++j) {
+                                const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
+                                    make_float2(act[4 * j] * inv, act[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+                                const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
+                                    make_float2(act[4 * j + 2] * inv, act[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+                                packed[j] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+                            }
+                            if (t < chunk_rows) {
+                                const uint32_t row = m0 + ch * 32 + t;
                                 const uint32_t inter0 = n0 / 2 + g * 32;   // n0: first interleaved row of this CTA
-                                uint4* dst = reinterpret_cast<uint4*>(p.moe.l2_acts +
-                                                                      static_cast<uint64_t>(row) * p.moe.inter + inter0);
-                                dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                                dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                                *reinterpret_cast<uint4*>(p.moe.l2_acts + static_cast<uint64_t>(row) * p.moe.inter + inter0 +
+                                                          half * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                                 const uint32_t kgroup = inter0 / 32;
-                                p.moe.l2_sf[(static_cast<uint64_t>(kgroup / 4) * p.moe.pool_rows + row) * 4 + (kgroup & 3)] =
-                                    static_cast<uint8_t>(e);
+                                if (half == 0)
+                                    p.moe.l2_sf[(static_cast<uint64_t>(kgroup / 4) * p.moe.pool_rows + row) * 4 + (kgroup & 3)] =
+                                        static_cast<uint8_t>(e);
                             }
                         } else {
                             // 32 tokens x 256 B: 16 lanes move one token's 256 B segment to its source rank
 #pragma unroll
                             for (uint32_t i = 0; i < 4; ++i) {
                                 const uint32_t piece = i * 128 + et, t = piece >> 4, part = piece & 15;
-                                if (t < chunk_rows) {
-                                    const uint32_t row = m0 + ch * 32 + t;
-                                    const int32_t src_rank = p.moe.pool_meta[row * 3];
-                                    if (src_rank >= 0) {
-                                        const uint32_t token = static_cast<uint32_t>(p.moe.pool_meta[row * 3 + 1]);
-                                        const uint32_t slot = static_cast<uint32_t>(p.moe.pool_meta[row * 3 + 2]);
-                                        const uint4 val = *reinterpret_cast<const uint4*>(stage_gen + t * Cfg::MOE_PITCH + part * 16);
-                                        uint8_t* dst = p.moe.peer_base[src_rank] + p.moe.off_combine +
-                                                       ((static_cast<uint64_t>(slot) * p.moe.t_max + token) * p.moe.hidden + n0) * 2 +
-                                                       part * 16;
-                                        *reinterpret_cast<uint4*>(dst) = val;
-                                    }
+                                const uint64_t* dtab = reinterpret_cast<const uint64_t*>(smem_gen + (smem_cd - smem_base) +
+                                                                                         Cfg::MOE_TABLE_OFF) + acc * 256;
+                                const uint64_t base = t < chunk_rows ? dtab[ch * 32 + t] : 0;
+                                if (base != 0) {
+                                    const uint4 val = *reinterpret_cast<const uint4*>(stage_gen + t * Cfg::MOE_PITCH + part * 16);
+                                    *reinterpret_cast<uint4*>(base + static_cast<uint64_t>(n0) * 2 + part * 16) = val;
                                 }
                             }
                         }
