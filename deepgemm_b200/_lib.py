@@ -18,7 +18,7 @@ EXPORTS = (
     "dg_set_tc_util", "dg_get_tc_util", "dg_set_mk_alignment_for_contiguous_layout",
     "dg_get_mk_alignment_for_contiguous_layout", "dg_get_theoretical_mk_alignment_for_contiguous_layout",
     "dg_set_wait_timeout_ms", "dg_check_status", "dg_last_error", "dg_version",
-    "dg_mega_moe_buffer_layout", "dg_get_token_alignment_for_mega_moe", "dg_mega_moe_forward",
+    "dg_mega_moe_buffer_layout", "dg_get_token_alignment_for_mega_moe", "dg_mega_moe_forward", "dg_gemm_fp8_fp32sf_noalloc", "dg_noalloc_scratch_bytes",
 )
 
 
@@ -57,6 +57,13 @@ class MoeArgs(C.Structure):
                 ("activation_clamp", C.c_float), ("fast_math", C.c_int32), ("stream", C.c_void_p)]
 
 
+class GemmNoAllocArgs(C.Structure):
+    _fields_ = [("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("gran_k", C.c_int32),
+                ("gran_mn_b", C.c_int32), ("d_dtype", C.c_int32),
+                ("a", C.c_void_p), ("sfa", C.c_void_p), ("b", C.c_void_p), ("sfb", C.c_void_p), ("d", C.c_void_p),
+                ("lda", C.c_int64), ("ldb", C.c_int64), ("ldd", C.c_int64), ("stream", C.c_void_p)]
+
+
 _lib = None
 
 
@@ -80,6 +87,7 @@ def lib() -> C.CDLL:
         l.dg_check_status.argtypes = [C.POINTER(C.c_uint32)]
         l.dg_mega_moe_buffer_layout.argtypes = [C.POINTER(MoeConfig), C.POINTER(MoeLayout)]
         l.dg_mega_moe_forward.argtypes = [C.POINTER(MoeArgs)]
+        l.dg_gemm_fp8_fp32sf_noalloc.argtypes = [C.POINTER(GemmNoAllocArgs)]
         for name in ("dg_set_num_sms", "dg_set_tc_util", "dg_set_mk_alignment_for_contiguous_layout",
                      "dg_get_theoretical_mk_alignment_for_contiguous_layout", "dg_set_wait_timeout_ms"):
             getattr(l, name).argtypes = [C.c_int32]

@@ -652,4 +652,70 @@ int dg_mega_moe_forward(const dg_moe_args* args) {
     return DG_OK;
 }
 
+
+// --------------------------------------------------------------------------- no-allocation entry point
+// Scratch for dg_gemm_fp8_fp32sf_noalloc: the packed UE8M0 scale tensors of both operands live here instead
+// of in caller-allocated memory.  One copy per GPU that loads the library, held until the process exits.
+constexpr size_t kNoAllocScratchBytes = 4u << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+// `g_noalloc_scratch` is a host-side stand-in in host code, not a device address: the address the kernels
+// get comes from cudaGetSymbolAddress, asked once per device with that device current.
+static int noalloc_scratch_address(unsigned char** out) {
+    static std::mutex mu;
+    static unsigned char* cached[64] = {nullptr};
+    int dev = 0;
+    DG_CUDA(cudaGetDevice(&dev));
+    DG_REQUIRE(dev >= 0 && dev < 64, "device index");
+    std::lock_guard<std::mutex> lk(mu);
+    if (cached[dev] == nullptr) {
+        void* ptr = nullptr;
+        DG_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        cached[dev] = static_cast<unsigned char*>(ptr);
+    }
+    *out = cached[dev];
+    return DG_OK;
+}
+
+int dg_noalloc_scratch_bytes(void) { return static_cast<int>(kNoAllocScratchBytes); }
+
+int dg_gemm_fp8_fp32sf_noalloc(const dg_gemm_noalloc_args* args) {
+    DG_REQUIRE(args != nullptr, "args");
+    const dg_gemm_noalloc_args& a = *args;
+    DG_REQUIRE(a.m >= 0 && a.n >= 0 && a.k > 0, "shape");
+    if (a.m == 0 || a.n == 0) return DG_OK;
+    DG_REQUIRE(a.a && a.sfa && a.b && a.sfb && a.d, "null tensor");
+    DG_REQUIRE(a.gran_k == 32 || a.gran_k == 128, "gran_k");
+    DG_REQUIRE(a.gran_mn_b == 1 || a.gran_mn_b == 128, "gran_mn_b");
+    DG_REQUIRE(a.d_dtype == DG_BF16 || a.d_dtype == DG_F32, "d dtype");
+    const int64_t sf_k = (static_cast<int64_t>(a.k) + a.gran_k - 1) / a.gran_k;
+    const int64_t packed_k = (sf_k + 3) / 4;
+    const int64_t amn_a = (static_cast<int64_t>(a.m) + 3) / 4 * 4, amn_b = (static_cast<int64_t>(a.n) + 3) / 4 * 4;
+    // Both packed scale tensors, each starting on a 256-byte boundary
+    const int64_t bytes_a = (packed_k * amn_a * 4 + 255) / 256 * 256, bytes_b = packed_k * amn_b * 4;
+    if (bytes_a + bytes_b > static_cast<int64_t>(kNoAllocScratchBytes))
+        return fail(DG_ERR_INVALID,
+                    "dg_gemm_fp8_fp32sf_noalloc: the packed scales of m=%d n=%d k=%d need %lld bytes, the built-in "
+                    "scratch holds %zu; use dg_sf_pack_ue8m0 + dg_gemm_bs with caller-owned memory",
+                    a.m, a.n, a.k, static_cast<long long>(bytes_a + bytes_b), kNoAllocScratchBytes);
+    unsigned char* scratch = nullptr;
+    int rc = noalloc_scratch_address(&scratch);
+    if (rc != DG_OK) return rc;
+    int32_t* sfa_packed = reinterpret_cast<int32_t*>(scratch);
+    int32_t* sfb_packed = reinterpret_cast<int32_t*>(scratch + bytes_a);
+    // Every word the GEMM reads is rewritten by the two pack launches: nothing relies on the array's old contents
+    rc = dg_sf_pack_ue8m0(a.sfa, sfa_packed, 1, a.m, static_cast<int32_t>(sf_k), 1, 0, sf_k, 1, nullptr, 0, 0, a.stream);
+    if (rc != DG_OK) return rc;
+    rc = dg_sf_pack_ue8m0(a.sfb, sfb_packed, 1, a.n, static_cast<int32_t>(sf_k), a.gran_mn_b, 0, sf_k, 1, nullptr, 0, 0,
+                          a.stream);
+    if (rc != DG_OK) return rc;
+    dg_gemm_args g;
+    memset(&g, 0, sizeof(g));
+    g.gemm_type = DG_GEMM_NORMAL, g.m = a.m, g.n = a.n, g.k = a.k, g.num_groups = 1;
+    g.a.data = a.a, g.a.sf = sfa_packed, g.a.ld = a.lda, g.a.sf_ld = amn_a, g.a.dtype = DG_E4M3, g.a.gran_k = a.gran_k;
+    g.b.data = a.b, g.b.sf = sfb_packed, g.b.ld = a.ldb, g.b.sf_ld = amn_b, g.b.dtype = DG_E4M3, g.b.gran_k = a.gran_k;
+    g.d = a.d, g.ldd = a.ldd, g.d_dtype = a.d_dtype, g.alpha = 1.0f, g.stream = a.stream;
+    return run_gemm(g, 0, nullptr);
+}
+
 }  // extern "C"

@@ -168,6 +168,41 @@ typedef struct dg_moe_args {
  * group must make the call; calls on one buffer must not overlap. */
 int dg_mega_moe_forward(const dg_moe_args* args);
 
+/* ---- Dense FP8 GEMM that allocates nothing ------------------------------------------------------------
+ * No counterpart in the reference.  For callers that must not call cudaMalloc (or any allocating library
+ * routine) around the GEMM - a plugin running inside another runtime's memory plan, a real-time loop, code
+ * between the nodes of a captured region's set-up - and therefore cannot provide the temporary packed scale
+ * tensors that dg_sf_pack_ue8m0 + dg_gemm_bs need.  This entry point takes the FP32 power-of-two scales
+ * directly and packs them into a scratch array built into the library image (4 MiB per GPU that loads the
+ * library, held until the process exits), then runs the same GEMM kernel as dg_gemm_bs.
+ *
+ *   a : E4M3 [m, k], K contiguous, lda bytes between rows;  sfa : float32 [m, ceil(k / gran_k)] contiguous
+ *   b : E4M3 [n, k], K contiguous, ldb bytes between rows;  sfb : float32 [ceil(n / gran_mn_b), ceil(k / gran_k)]
+ *   d : BF16 or FP32 [m, n], ldd bytes between rows
+ *
+ * Limits and rules:
+ *   - (align(m,4) + align(n,4)) * ceil(k / (4 * gran_k)) * 4 bytes must fit dg_noalloc_scratch_bytes();
+ *     larger problems are rejected with DG_ERR_INVALID and a message naming the sizes.
+ *   - The first call on a device looks up the scratch array's device address (no allocation); make that
+ *     first call before starting any stream capture.
+ *   - All calls on one GPU share the one array, which keeps the last call's contents: each call rewrites
+ *     every word it later reads, but two calls whose kernels overlap on the GPU (different streams) race. */
+typedef struct dg_gemm_noalloc_args {
+    int32_t m, n, k;
+    int32_t gran_k;        /* 32 or 128 */
+    int32_t gran_mn_b;     /* 1: per-row scales of b; 128: 128 x 128 block scales */
+    int32_t d_dtype;       /* DG_BF16 or DG_F32 */
+    const void* a;
+    const float* sfa;
+    const void* b;
+    const float* sfb;
+    void* d;
+    int64_t lda, ldb, ldd;
+    void* stream;
+} dg_gemm_noalloc_args;
+int dg_gemm_fp8_fp32sf_noalloc(const dg_gemm_noalloc_args* args);
+int dg_noalloc_scratch_bytes(void);
+
 /* Process-wide knobs (csrc/apis/config.hpp:8-48, csrc/apis/layout.hpp:138-146 of the reference). */
 int dg_set_num_sms(int32_t num_sms);
 int dg_get_num_sms(void);           /* device SM count unless overridden */
