@@ -82,6 +82,12 @@ struct MoeEpilogueParams {
     uint32_t fast_math;
 };
 
+// Position of pool row `row` inside its 128-row group in the order tcgen05.cp.32x128b.warpx4 copies to TMEM.
+__host__ __device__ inline uint32_t moe_sf_row(uint32_t row) {
+    const uint32_t i = row & 127u;
+    return (row & ~127u) + (i & 31u) * 4u + (i >> 5);
+}
+
 struct GemmParams {
     CUtensorMap tm_r, tm_c, tm_sfr, tm_sfc, tm_d;
     OperandParams r, c;
@@ -101,6 +107,7 @@ struct GemmParams {
     uint32_t d_grouped;         // D has a group axis (masked / K-grouped): third store coordinate = group
     uint32_t split_blocks;      // contiguous layout: a schedule slot spans two alignment units (may straddle experts)
     uint32_t r_sf_pretransposed;  // R's scale words already sit in the 32x4 order tcgen05.cp reads (Mega MoE weights)
+    uint32_t c_sf_pretransposed;  // same for C (Mega MoE activations: the pool is written in that order)
     MoeEpilogueParams moe;      // fused Mega MoE epilogues (GemmConfig::kEpi != 0)
     uint32_t timeout_ms;
     uint32_t* status;           // 16 words: [0] code, [1] site, [2] block, [3] tile iter, [4] k block, [5] stage
@@ -356,6 +363,87 @@ DG_DEVICE bool wait_barrier(uint64_t* bar, uint32_t parity, volatile uint32_t* a
                 if (peer_abort_addr) st_cluster_u32(peer_abort_addr, 1);
                 return false;
             }
+        }
+    }
+}
+
+// One 32-token chunk of the first expert GEMM's epilogue, after the chunk was staged as BF16 [token][128 rows]:
+// SwiGLU on the BF16-rounded gate / up pairs, times the route weight, per-32 UE8M0 E4M3 requantisation, stored
+// as rows of the second GEMM's A operand.  m0: first pool row of the tile; n0: first interleaved weight row of
+// this CTA; wtab: the tile's route weights.
+DG_DEVICE void moe_l1_chunk(const MoeEpilogueParams& m, const uint8_t* stage, uint32_t pitch, const float* wtab,
+                            uint32_t q, uint32_t lane, uint32_t ch, uint32_t chunk_rows, uint32_t m0, uint32_t n0) {
+    // A warp takes 8 tokens; lane = (token, 32-output group g, half): 16 outputs per
+    // thread = 32 interleaved rows laid out as 2 x [8 gate | 8 up] (the weights come
+    // interleaved in blocks of 8 rows); the two halves of a group share their amax.
+    const uint32_t t = q * 8 + (lane >> 2), g = (lane >> 1) & 1, half = lane & 1;
+    const float w = wtab[min(ch * 32 + t, 255u)];
+    const uint4* src = reinterpret_cast<const uint4*>(stage + t * pitch + g * 128 + half * 64);
+    float act[16];
+    float amax = 0.f;
+#pragma unroll
+    for (uint32_t blk = 0; blk < 2; ++blk) {
+        const uint4 gv = src[2 * blk], uv = src[2 * blk + 1];
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+            float2 gf = __bfloat1622float2(g2[j]), uf = __bfloat1622float2(u2[j]);
+            gf.x = fminf(gf.x, m.clamp), gf.y = fminf(gf.y, m.clamp);
+            uf.x = fminf(fmaxf(uf.x, -m.clamp), m.clamp);
+            uf.y = fminf(fmaxf(uf.y, -m.clamp), m.clamp);
+            float sx, sy;
+            if (m.fast_math) {
+                sx = gf.x * __frcp_rn(1.0f + __expf(-gf.x));
+                sy = gf.y * __frcp_rn(1.0f + __expf(-gf.y));
+            } else {
+                sx = gf.x / (1.0f + expf(-gf.x));
+                sy = gf.y / (1.0f + expf(-gf.y));
+            }
+            const float ax = (sx * uf.x) * w, ay = (sy * uf.y) * w;
+            act[blk * 8 + j * 2] = ax, act[blk * 8 + j * 2 + 1] = ay;
+            amax = fmaxf(amax, fmaxf(fabsf(ax), fabsf(ay)));
+        }
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    // Power-of-two scale 2^e >= amax / 448, floor 2^-22 (amax clamp 1e-4): the add
+    // carries into the exponent iff the mantissa exceeds that of 448 = 1.75 * 2^8
+    uint32_t e = (__float_as_uint(amax) + 0x1FFFFFu) >> 23;
+    e = max(e, 113u) - 8u;
+    const float inv = __uint_as_float((254u - e) << 23);
+    uint32_t packed[4];
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j) {
+        const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
+            make_float2(act[4 * j] * inv, act[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+        const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
+            make_float2(act[4 * j + 2] * inv, act[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+        packed[j] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+    }
+    if (t < chunk_rows) {
+        const uint32_t row = m0 + ch * 32 + t;
+        const uint32_t inter0 = n0 / 2 + g * 32;   // n0: first interleaved row of this CTA
+        *reinterpret_cast<uint4*>(m.l2_acts + static_cast<uint64_t>(row) * m.inter + inter0 +
+                                  half * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        const uint32_t kgroup = inter0 / 32;
+        if (half == 0)
+            m.l2_sf[(static_cast<uint64_t>(kgroup / 4) * m.pool_rows + moe_sf_row(row)) * 4 + (kgroup & 3)] =
+                static_cast<uint8_t>(e);
+    }
+}
+
+// One 32-token chunk of the second expert GEMM's epilogue: 16 lanes move one token's 256 B segment of BF16
+// results to that token's slot plane in its source rank's buffer (dtab: per-token destination row address, 0 = none).
+DG_DEVICE void moe_l2_chunk(const uint8_t* stage, uint32_t pitch, const uint64_t* dtab, uint32_t et, uint32_t ch,
+                            uint32_t chunk_rows, uint32_t n0) {
+    // 32 tokens x 256 B: 16 lanes move one token's 256 B segment to its source rank
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) {
+        const uint32_t piece = i * 128 + et, t = piece >> 4, part = piece & 15;
+        const uint64_t base = t < chunk_rows ? dtab[ch * 32 + t] : 0;
+        if (base != 0) {
+            const uint4 val = *reinterpret_cast<const uint4*>(stage + t * pitch + part * 16);
+            *reinterpret_cast<uint4*>(base + static_cast<uint64_t>(n0) * 2 + part * 16) = val;
         }
     }
 }
@@ -623,12 +711,12 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                     };
                     const bool new_r = (kb & sf_mask_r) == 0, new_c = (kb & sf_mask_c) == 0;
                     if (new_r && !p.r_sf_pretransposed) transpose_128(sf_words_r + stage * 128);
-                    if (new_c) {
+                    if (new_c && !p.c_sf_pretransposed) {
 #pragma unroll
                         for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i)
                             transpose_128(sf_words_c + stage * Cfg::SFC_ROWS + i * 128);
                     }
-                    if (new_r || new_c) {
+                    if ((new_r && !p.r_sf_pretransposed) || (new_c && !p.c_sf_pretransposed)) {
                         fence_proxy_async_smem();   // generic-proxy writes -> visible to tcgen05.cp
                         __syncwarp();
                     }
@@ -778,82 +866,14 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                                           kSiteEpilogueSync, acc_iter, ch, moe_buf);
                         ++moe_chunks;
                         if (!ok) break;
-                        const uint32_t et = q * 32 + lane;           // epilogue thread 0..127
                         const uint32_t chunk_rows = min(32u, tc.rows - ch * 32);
-                        if constexpr (Cfg::kEpi == 1) {
-                            // A warp takes 8 tokens; lane = (token, 32-output group g, half): 16 outputs per
-                            // thread = 32 interleaved rows laid out as 2 x [8 gate | 8 up] (the weights come
-                            // interleaved in blocks of 8 rows); the two halves of a group share their amax.
-                            const uint32_t t = q * 8 + (lane >> 2), g = (lane >> 1) & 1, half = lane & 1;
-                            const float* wtab = reinterpret_cast<const float*>(
-                                reinterpret_cast<const uint64_t*>(smem_gen + (smem_cd - smem_base) + Cfg::MOE_TABLE_OFF) + acc * 256);
-                            const float w = wtab[min(ch * 32 + t, 255u)];
-                            const uint4* src = reinterpret_cast<const uint4*>(stage_gen + t * Cfg::MOE_PITCH + g * 128 + half * 64);
-                            float act[16];
-                            float amax = 0.f;
-#pragma unroll
-                            for (uint32_t blk = 0; blk < 2; ++blk) {
-                                const uint4 gv = src[2 * blk], uv = src[2 * blk + 1];
-                                const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
-                                const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
-#pragma unroll
-                                for (uint32_t j = 0; j < 4; ++j) {
-                                    float2 gf = __bfloat1622float2(g2[j]), uf = __bfloat1622float2(u2[j]);
-                                    gf.x = fminf(gf.x, p.moe.clamp), gf.y = fminf(gf.y, p.moe.clamp);
-                                    uf.x = fminf(fmaxf(uf.x, -p.moe.clamp), p.moe.clamp);
-                                    uf.y = fminf(fmaxf(uf.y, -p.moe.clamp), p.moe.clamp);
-                                    float sx, sy;
-                                    if (p.moe.fast_math) {
-                                        sx = gf.x * __frcp_rn(1.0f + __expf(-gf.x));
-                                        sy = gf.y * __frcp_rn(1.0f + __expf(-gf.y));
-                                    } else {
-                                        sx = gf.x / (1.0f + expf(-gf.x));
-                                        sy = gf.y / (1.0f + expf(-gf.y));
-                                    }
-                                    const float ax = (sx * uf.x) * w, ay = (sy * uf.y) * w;
-                                    act[blk * 8 + j * 2] = ax, act[blk * 8 + j * 2 + 1] = ay;
-                                    amax = fmaxf(amax, fmaxf(fabsf(ax), fabsf(ay)));
-                                }
-                            }
-                            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-                            // Power-of-two scale 2^e >= amax / 448, floor 2^-22 (amax clamp 1e-4): the add
-                            // carries into the exponent iff the mantissa exceeds that of 448 = 1.75 * 2^8
-                            uint32_t e = (__float_as_uint(amax) + 0x1FFFFFu) >> 23;
-                            e = max(e, 113u) - 8u;
-                            const float inv = __uint_as_float((254u - e) << 23);
-                            uint32_t packed[4];
-#pragma unroll
-                            for (uint32_t j = 0; j < 4; ++j) {
-                                const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
-                                    make_float2(act[4 * j] * inv, act[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
-                                const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
-                                    make_float2(act[4 * j + 2] * inv, act[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
-                                packed[j] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-                            }
-                            if (t < chunk_rows) {
-                                const uint32_t row = m0 + ch * 32 + t;
-                                const uint32_t inter0 = n0 / 2 + g * 32;   // n0: first interleaved row of this CTA
-                                *reinterpret_cast<uint4*>(p.moe.l2_acts + static_cast<uint64_t>(row) * p.moe.inter + inter0 +
-                                                          half * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                                const uint32_t kgroup = inter0 / 32;
-                                if (half == 0)
-                                    p.moe.l2_sf[(static_cast<uint64_t>(kgroup / 4) * p.moe.pool_rows + row) * 4 + (kgroup & 3)] =
-                                        static_cast<uint8_t>(e);
-                            }
-                        } else {
-                            // 32 tokens x 256 B: 16 lanes move one token's 256 B segment to its source rank
-#pragma unroll
-                            for (uint32_t i = 0; i < 4; ++i) {
-                                const uint32_t piece = i * 128 + et, t = piece >> 4, part = piece & 15;
-                                const uint64_t* dtab = reinterpret_cast<const uint64_t*>(smem_gen + (smem_cd - smem_base) +
-                                                                                         Cfg::MOE_TABLE_OFF) + acc * 256;
-                                const uint64_t base = t < chunk_rows ? dtab[ch * 32 + t] : 0;
-                                if (base != 0) {
-                                    const uint4 val = *reinterpret_cast<const uint4*>(stage_gen + t * Cfg::MOE_PITCH + part * 16);
-                                    *reinterpret_cast<uint4*>(base + static_cast<uint64_t>(n0) * 2 + part * 16) = val;
-                                }
-                            }
-                        }
+                        const uint64_t* table = reinterpret_cast<const uint64_t*>(smem_gen + (smem_cd - smem_base) +
+                                                                                  Cfg::MOE_TABLE_OFF) + acc * 256;
+                        if constexpr (Cfg::kEpi == 1)
+                            moe_l1_chunk(p.moe, stage_gen, Cfg::MOE_PITCH, reinterpret_cast<const float*>(table), q, lane, ch,
+                                         chunk_rows, m0, n0);
+                        else
+                            moe_l2_chunk(stage_gen, Cfg::MOE_PITCH, table, q * 32 + lane, ch, chunk_rows, n0);
                         moe_buf ^= 1;
                     }
                 }

@@ -2,6 +2,7 @@
 // launches behind the C ABI declared in include/deepgemm_b200.h.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -14,6 +15,7 @@
 #include "gemm_bs.cuh"
 #include "sf_pack.cuh"
 #include "mega_moe.cuh"
+#include "mega_moe_fused.cuh"
 
 namespace {
 
@@ -52,6 +54,7 @@ struct Knobs {
     int tc_util = 100;
     int mk_alignment = 128;
     int timeout_ms = 2000;
+    int moe_fused = 1;     // Mega MoE: one persistent kernel (1) or the kernel-per-phase path (0)
 } g_knobs;
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -477,6 +480,7 @@ static int run_gemm(const dg_gemm_args& a, int epi, const dg::MoeEpilogueParams*
     if (epi != 0) {
         p.moe = *moe;
         p.r_sf_pretransposed = 1;
+        p.c_sf_pretransposed = 1;
     }
     // D: [groups, m, n] row-major
     if (epi == 0) {
@@ -558,6 +562,79 @@ static int check_moe_config(const dg_moe_config& c) {
     return DG_OK;
 }
 
+
+// Epilogue arguments and the two expert GEMMs' descriptions, shared by both Mega MoE paths.
+static void fill_moe_gemm_args(const dg_moe_args& m, const dg::MoeArgs& a, dg::MoeEpilogueParams* e, dg_gemm_args* g1,
+                               dg_gemm_args* g2) {
+    const dg::MoeLayout& L = a.L;
+    uint8_t* mine = a.base[m.rank];
+    memset(e, 0, sizeof(*e));
+    e->l2_acts = mine + L.off_l2_acts, e->l2_sf = mine + L.off_l2_sf;
+    e->pool_w = reinterpret_cast<const float*>(mine + L.off_pool_w);
+    e->pool_meta = reinterpret_cast<const int32_t*>(mine + L.off_pool_meta);
+    for (uint32_t r = 0; r < L.ranks; ++r) e->peer_base[r] = a.base[r];
+    e->off_combine = L.off_combine, e->pool_rows = L.pool_rows, e->inter = L.inter, e->hidden = L.hidden, e->t_max = L.t_max;
+    e->clamp = m.activation_clamp, e->fast_math = m.fast_math ? 1 : 0;
+    dg_gemm_args g;
+    memset(&g, 0, sizeof(g));
+    g.gemm_type = DG_GEMM_M_PSUM, g.num_groups = L.experts_local, g.alignment = dg::kMoePoolAlign;
+    g.grouped_layout = reinterpret_cast<const int32_t*>(mine + L.off_work) + dg::MoeWork::psum_end(L.experts);
+    g.stream = m.stream, g.alpha = 1.0f, g.d_dtype = DG_BF16;
+    g.m = L.pool_rows, g.n = 2 * L.inter, g.k = L.hidden;
+    g.a.data = mine + L.off_l1_acts, g.a.sf = reinterpret_cast<const int32_t*>(mine + L.off_l1_sf);
+    g.a.ld = L.hidden, g.a.sf_ld = L.pool_rows, g.a.dtype = DG_E4M3, g.a.gran_k = 32;
+    g.b.data = m.l1_w, g.b.sf = m.l1_sf, g.b.ld = L.hidden / 2, g.b.sf_ld = m.l1_sf_ld, g.b.dtype = DG_E2M1_PACKED;
+    g.b.gran_k = 32;
+    *g1 = g;
+    g.n = L.hidden, g.k = L.inter;
+    g.a.data = mine + L.off_l2_acts, g.a.sf = reinterpret_cast<const int32_t*>(mine + L.off_l2_sf), g.a.ld = L.inter;
+    g.b.data = m.l2_w, g.b.sf = m.l2_sf, g.b.ld = L.inter / 2, g.b.sf_ld = m.l2_sf_ld;
+    *g2 = g;
+}
+
+static int launch_moe_fused(const dg_moe_args& m, const dg::MoeArgs& a, int num_sms) {
+    dg::MoeFusedParams p;
+    memset(&p, 0, sizeof(p));
+    p.a = a;
+    dg_gemm_args g[2];
+    fill_moe_gemm_args(m, a, &p.e, &g[0], &g[1]);
+    for (int i = 0; i < 2; ++i) {
+        // weights are the UMMA row operand (128 rows per CTA), tokens the column operand (half of 256 per CTA)
+        OperandPlan w, act;
+        int rc = plan_operand(g[i], g[i].b, /*is_a=*/false, 128, 128, &w);
+        if (rc != DG_OK) return rc;
+        rc = plan_operand(g[i], g[i].a, /*is_a=*/true, 128, 256, &act);
+        if (rc != DG_OK) return rc;
+        p.tm_w[i] = w.tm, p.tm_wsf[i] = w.tm_sf, p.tm_act[i] = act.tm, p.tm_actsf[i] = act.tm_sf;
+    }
+    p.y = static_cast<__nv_bfloat16*>(m.y), p.ldy = m.ldy;
+    p.num_ctas = static_cast<uint32_t>(num_sms) / 2 * 2;
+    p.trace = g_trace;
+    {
+        const char* env = getenv("DG_MEGA_MOE_LAG");   // tuning aid
+        p.lag = env != nullptr ? static_cast<uint32_t>(atoi(env)) : 4;
+        if (p.lag < 1) p.lag = 1;
+    }
+    DG_CUDA(cudaFuncSetAttribute(dg::mega_moe_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(dg::FusedCfg::kSmemBytes)));
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(p.num_ctas, 1, 1), cfg.blockDim = dim3(dg::kFusedThreads, 1, 1);
+    cfg.dynamicSmemBytes = dg::FusedCfg::kSmemBytes, cfg.stream = static_cast<cudaStream_t>(m.stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    DG_CUDA(cudaLaunchKernelEx(&cfg, dg::mega_moe_fused_kernel, p));
+    return DG_OK;
+}
+
+int dg_set_mega_moe_fused(int32_t enable) {
+    std::lock_guard<std::mutex> lk(g_knobs.mu);
+    g_knobs.moe_fused = enable ? 1 : 0;
+    return DG_OK;
+}
+
 int dg_get_token_alignment_for_mega_moe(void) { return 128; }
 
 int dg_mega_moe_buffer_layout(const dg_moe_config* cfg, dg_moe_layout* out) {
@@ -604,44 +681,32 @@ int dg_mega_moe_forward(const dg_moe_args* args) {
     a.status = static_cast<uint32_t*>(status_ptr);
     a.stats = m.stats;
     cudaStream_t stream = static_cast<cudaStream_t>(m.stream);
-    uint8_t* mine = a.base[m.rank];
+    int num_sms = dg_get_num_sms();
+    DG_REQUIRE(num_sms > 0, "num_sms");
+    bool fused;
+    {
+        std::lock_guard<std::mutex> lk(g_knobs.mu);
+        fused = g_knobs.moe_fused != 0;
+    }
+    fused = fused && L.hidden % 256 == 0 && L.inter % 128 == 0 && L.experts_local * L.ranks <= dg::FusedCfg::kMaxSegments &&
+            num_sms >= 2;
+    if (fused) return launch_moe_fused(m, a, num_sms);
 
     // 1. count + index scatter, 2. count exchange + barrier + pool layout, 3. pull
     const uint32_t pairs = static_cast<uint32_t>(m.num_tokens) * L.topk;
     if (pairs > 0) dg::moe_scatter_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(a);
     dg::moe_exchange_kernel<<<1, 256, 0, stream>>>(a);
-    int num_sms = dg_get_num_sms();
-    DG_REQUIRE(num_sms > 0, "num_sms");
     const uint32_t seg_smem = (L.experts_local * L.ranks + 1) * 4;
     dg::moe_pull_kernel<<<num_sms * 4, 256, seg_smem, stream>>>(a);
     DG_CUDA(cudaGetLastError());
 
     // 4. first expert GEMM (+ SwiGLU, route weight, FP8 requantisation), 5. second (+ combine push)
     dg::MoeEpilogueParams e;
-    memset(&e, 0, sizeof(e));
-    e.l2_acts = mine + L.off_l2_acts, e.l2_sf = mine + L.off_l2_sf;
-    e.pool_w = reinterpret_cast<const float*>(mine + L.off_pool_w);
-    e.pool_meta = reinterpret_cast<const int32_t*>(mine + L.off_pool_meta);
-    for (uint32_t r = 0; r < L.ranks; ++r) e.peer_base[r] = a.base[r];
-    e.off_combine = L.off_combine, e.pool_rows = L.pool_rows, e.inter = L.inter, e.hidden = L.hidden, e.t_max = L.t_max;
-    e.clamp = m.activation_clamp, e.fast_math = m.fast_math ? 1 : 0;
-    const int32_t* psum = reinterpret_cast<const int32_t*>(mine + L.off_work) + dg::MoeWork::psum_end(L.experts);
-
-    dg_gemm_args g;
-    memset(&g, 0, sizeof(g));
-    g.gemm_type = DG_GEMM_M_PSUM, g.num_groups = L.experts_local, g.alignment = dg::kMoePoolAlign;
-    g.grouped_layout = psum, g.stream = m.stream, g.alpha = 1.0f, g.d_dtype = DG_BF16;
-    g.m = L.pool_rows, g.n = 2 * L.inter, g.k = L.hidden;
-    g.a.data = mine + L.off_l1_acts, g.a.sf = reinterpret_cast<const int32_t*>(mine + L.off_l1_sf);
-    g.a.ld = L.hidden, g.a.sf_ld = L.pool_rows, g.a.dtype = DG_E4M3, g.a.gran_k = 32;
-    g.b.data = m.l1_w, g.b.sf = m.l1_sf, g.b.ld = L.hidden / 2, g.b.sf_ld = m.l1_sf_ld, g.b.dtype = DG_E2M1_PACKED;
-    g.b.gran_k = 32;
-    rc = run_gemm(g, 1, &e);
+    dg_gemm_args g1, g2;
+    fill_moe_gemm_args(m, a, &e, &g1, &g2);
+    rc = run_gemm(g1, 1, &e);
     if (rc != DG_OK) return rc;
-    g.n = L.hidden, g.k = L.inter;
-    g.a.data = mine + L.off_l2_acts, g.a.sf = reinterpret_cast<const int32_t*>(mine + L.off_l2_sf), g.a.ld = L.inter;
-    g.b.data = m.l2_w, g.b.sf = m.l2_sf, g.b.ld = L.inter / 2, g.b.sf_ld = m.l2_sf_ld;
-    rc = run_gemm(g, 2, &e);
+    rc = run_gemm(g2, 2, &e);
     if (rc != DG_OK) return rc;
 
     // 6. every rank has pushed its results, 7. local top-k reduction

@@ -12,6 +12,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include "gemm_bs.cuh"   // ptx helpers, moe_sf_row
+
 namespace dg {
 
 constexpr uint32_t kMoeMaxRanks = 16;
@@ -47,6 +49,17 @@ struct MoeWork {
     }
 };
 
+// Work-area words used only by the fused kernel (after the tables of MoeWork)
+struct MoeFusedWork {
+    static constexpr uint32_t kGridSync = 2, kLayoutReady = 3, kNumTiles = 4, kCombineReady = 5, kFusedCalls = 6;
+    __host__ __device__ static uint32_t max_tiles(const MoeLayout& L) { return L.pool_rows / 256 + L.experts_local; }
+    __host__ __device__ static uint32_t tile_table(const MoeLayout& L) { return MoeWork::words(L.experts, L.experts_local, L.ranks); }
+    // per tile: row0, rows (UMMA N), expert, valid rows in its first 128-row block, valid rows in its second
+    __host__ __device__ static uint32_t pulled(const MoeLayout& L) { return tile_table(L) + max_tiles(L) * 8; }   // [pool_rows / 128]
+    __host__ __device__ static uint32_t l1_done(const MoeLayout& L) { return pulled(L) + L.pool_rows / 128; }      // [max_tiles]
+    __host__ __device__ static uint32_t words(const MoeLayout& L) { return l1_done(L) + max_tiles(L); }
+};
+
 inline uint64_t moe_align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 
 inline MoeLayout make_moe_layout(uint32_t ranks, uint32_t experts, uint32_t t_max, uint32_t topk, uint32_t hidden,
@@ -77,7 +90,7 @@ inline MoeLayout make_moe_layout(uint32_t ranks, uint32_t experts, uint32_t t_ma
     L.off_l2_acts = take(static_cast<uint64_t>(L.pool_rows) * inter);
     L.off_l2_sf = take(static_cast<uint64_t>(L.pool_rows) * (inter / 128) * 4);
     L.off_combine = take(static_cast<uint64_t>(topk) * t_max * hidden * 2);
-    L.off_work = take(static_cast<uint64_t>(MoeWork::words(experts, L.experts_local, ranks)) * 4);
+    L.off_work = take(static_cast<uint64_t>(MoeFusedWork::words(L)) * 4);
     L.total_bytes = off;
     return L;
 }
@@ -125,9 +138,7 @@ DG_DEVICE bool moe_cross_rank_barrier(const MoeArgs& a, uint32_t which, uint32_t
 
 // ---- step 1: count (token, slot) pairs per expert and tell the expert's rank which pairs to pull.
 // grid: ceil(num_tokens * topk / 256), block 256
-__global__ void __launch_bounds__(256) moe_scatter_kernel(const MoeArgs a) {
-    const uint32_t i = blockIdx.x * 256 + threadIdx.x;
-    if (i >= a.num_tokens * a.L.topk) return;
+DG_DEVICE void moe_scatter_pair(const MoeArgs& a, uint32_t i) {
     const long long e = reinterpret_cast<const long long*>(a.base[a.rank] + a.L.off_topk_idx)[i];
     if (e < 0 || e >= static_cast<long long>(a.L.experts)) return;
     uint32_t* work = reinterpret_cast<uint32_t*>(a.base[a.rank] + a.L.off_work);
@@ -136,32 +147,41 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const MoeArgs a) {
     uint32_t* idx = reinterpret_cast<uint32_t*>(a.base[dest] + a.L.off_src_idx);
     idx[(static_cast<uint64_t>(el) * a.L.ranks + a.rank) * a.L.t_max + j] = i;
 }
+__global__ void __launch_bounds__(256) moe_scatter_kernel(const MoeArgs a) {
+    const uint32_t i = blockIdx.x * 256 + threadIdx.x;
+    if (i < a.num_tokens * a.L.topk) moe_scatter_pair(a, i);
+}
 
-// ---- step 2: publish the counts, cross-rank barrier, then lay out the pool.  One CTA of 256 threads.
-__global__ void __launch_bounds__(256) moe_exchange_kernel(const MoeArgs a) {
+// ---- step 2: publish the counts, cross-rank barrier, then lay out the pool.  Run by ALL threads of one CTA
+// (`nthreads` of them).  With `fused` != nullptr it also writes the fused kernel's tile table, clears its
+// progress counters and finally publishes `layout_ready`.  Returns false if the barrier timed out.
+struct MoeFusedHooks {
+    uint32_t tile_table, pulled, l1_done, num_tiles_word, layout_ready_word;   // word offsets in the work area
+};
+DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthreads, const MoeFusedHooks* fused) {
     const MoeLayout& L = a.L;
     uint32_t* work = reinterpret_cast<uint32_t*>(a.base[a.rank] + L.off_work);
-    __shared__ uint32_t s_call, s_ok;
-    if (threadIdx.x == 0) {
+    __shared__ uint32_t s_call, s_ok, s_tiles, s_rows;
+    if (tid == 0) {
         s_call = ++work[MoeWork::kCall];
         s_ok = 1;
     }
-    for (uint32_t e = threadIdx.x; e < L.experts; e += 256) {
+    for (uint32_t e = tid; e < L.experts; e += nthreads) {
         const uint32_t cnt = work[MoeWork::kSendCount + e];
         work[MoeWork::kSendCount + e] = 0;   // ready for the next call
         const uint32_t dest = e / L.experts_local, el = e % L.experts_local;
         reinterpret_cast<uint32_t*>(a.base[dest] + L.off_recv_count)[a.rank * L.experts_local + el] = cnt;
     }
     __syncthreads();
-    if (threadIdx.x < L.ranks)
-        if (!moe_cross_rank_barrier(a, 0, 2 * s_call - 1, threadIdx.x)) s_ok = 0;
+    if (tid < L.ranks)
+        if (!moe_cross_rank_barrier(a, 0, 2 * s_call - 1, tid)) s_ok = 0;
     __syncthreads();
-    if (!s_ok) return;
+    if (!s_ok) return false;
     // Pool layout: expert el owns rows [align(prev_end), end); inside, sources in rank order.
     const uint32_t* recv = reinterpret_cast<const uint32_t*>(a.base[a.rank] + L.off_recv_count);
     int32_t* meta = reinterpret_cast<int32_t*>(a.base[a.rank] + L.off_pool_meta);
-    if (threadIdx.x == 0) {
-        uint32_t prev_end = 0, flat = 0;
+    if (tid == 0) {
+        uint32_t prev_end = 0, flat = 0, tiles = 0;
         for (uint32_t el = 0; el < L.experts_local; ++el) {
             const uint32_t start = (prev_end + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
             uint32_t row = start;
@@ -173,39 +193,61 @@ __global__ void __launch_bounds__(256) moe_exchange_kernel(const MoeArgs a) {
             }
             work[MoeWork::psum_end(L.experts) + el] = row;
             if (a.stats != nullptr) a.stats[el] += static_cast<int32_t>(row - start);
+            if (fused != nullptr) {
+                // 256-token tiles over the expert's aligned extent
+                const uint32_t total = row - start;
+                const uint32_t aligned = (total + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
+                for (uint32_t off = 0; off < aligned; off += 256, ++tiles) {
+                    uint32_t* t = work + fused->tile_table + tiles * 8;
+                    t[0] = start + off, t[1] = min(256u, aligned - off), t[2] = el;
+                    t[3] = total > off ? min(128u, total - off) : 0;
+                    t[4] = total > off + 128 ? min(128u, total - off - 128) : 0;
+                }
+            }
             prev_end = row;
         }
         work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + L.experts_local * L.ranks] = flat;
-        work[MoeWork::kTotalRows] = (prev_end + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
+        s_rows = (prev_end + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
+        work[MoeWork::kTotalRows] = s_rows;
+        s_tiles = tiles;
+        if (fused != nullptr) work[fused->num_tiles_word] = tiles;
     }
     __syncthreads();
     // Rows between an expert's end and the next boundary carry no token: mark them
     for (uint32_t el = 0; el < L.experts_local; ++el) {
         const uint32_t end = work[MoeWork::psum_end(L.experts) + el];
         const uint32_t stop = (end + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
-        for (uint32_t r = end + threadIdx.x; r < stop; r += 256) meta[r * 3] = -1;
+        for (uint32_t r = end + tid; r < stop; r += nthreads) meta[r * 3] = -1;
     }
+    if (fused != nullptr) {
+        for (uint32_t i = tid; i < s_rows / 128; i += nthreads) work[fused->pulled + i] = 0;
+        for (uint32_t i = tid; i < s_tiles; i += nthreads) work[fused->l1_done + i] = 0;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(work + fused->layout_ready_word), "r"(s_call) : "memory");
+    }
+    return true;
 }
 
-// ---- step 3: pull every routed token (row, packed scales, route weight) into the pool.  One warp per row.
-__global__ void __launch_bounds__(256) moe_pull_kernel(const MoeArgs a) {
+__global__ void __launch_bounds__(256) moe_exchange_kernel(const MoeArgs a) {
+    moe_exchange_body(a, threadIdx.x, 256, nullptr);
+}
+
+// ---- step 3: pull every routed token (row, packed scales, route weight) into the pool.  One warp per row:
+// flat rows first, first + stride, ...; `pulled` (optional) counts finished rows per 128-row pool block.
+DG_DEVICE void moe_pull_rows(const MoeArgs& a, const uint32_t* s_prefix, uint32_t first, uint32_t stride, uint32_t lane,
+                             uint32_t* pulled) {
     const MoeLayout& L = a.L;
     const uint32_t* work = reinterpret_cast<const uint32_t*>(a.base[a.rank] + L.off_work);
-    extern __shared__ uint32_t s_prefix[];   // [segments + 1]
     const uint32_t segments = L.experts_local * L.ranks;
-    for (uint32_t i = threadIdx.x; i <= segments; i += 256)
-        s_prefix[i] = work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + i];
-    __syncthreads();
     const uint32_t total = s_prefix[segments];
-    const uint32_t lane = threadIdx.x & 31;
-    const uint32_t warps = gridDim.x * 8;
     const uint32_t* src_idx = reinterpret_cast<const uint32_t*>(a.base[a.rank] + L.off_src_idx);
     uint8_t* l1 = a.base[a.rank] + L.off_l1_acts;
     uint32_t* l1_sf = reinterpret_cast<uint32_t*>(a.base[a.rank] + L.off_l1_sf);
     float* pool_w = reinterpret_cast<float*>(a.base[a.rank] + L.off_pool_w);
     int32_t* meta = reinterpret_cast<int32_t*>(a.base[a.rank] + L.off_pool_meta);
     const uint32_t sf_words = L.hidden / 128;
-    for (uint32_t r = blockIdx.x * 8 + threadIdx.x / 32; r < total; r += warps) {
+    for (uint32_t r = first; r < total; r += stride) {
         // segment holding flat row r: last i with prefix[i] <= r
         uint32_t lo = 0, hi = segments;
         while (hi - lo > 1) {
@@ -219,16 +261,50 @@ __global__ void __launch_bounds__(256) moe_pull_kernel(const MoeArgs a) {
         const uint8_t* peer = a.base[src];
         const uint4* from = reinterpret_cast<const uint4*>(peer + L.off_x + static_cast<uint64_t>(token) * L.hidden);
         uint4* to = reinterpret_cast<uint4*>(l1 + static_cast<uint64_t>(dst) * L.hidden);
-        for (uint32_t c = lane; c < L.hidden / 16; c += 32) to[c] = from[c];
+        // 8 independent 16-byte loads in flight per lane before the stores (peer loads have NVLink latency)
+        const uint32_t vecs = L.hidden / 16;
+        for (uint32_t c0 = 0; c0 < vecs; c0 += 256) {
+            uint4 tmp[8];
+#pragma unroll
+            for (uint32_t u = 0; u < 8; ++u) {
+                const uint32_t c = c0 + u * 32 + lane;
+                if (c < vecs) tmp[u] = from[c];
+            }
+#pragma unroll
+            for (uint32_t u = 0; u < 8; ++u) {
+                const uint32_t c = c0 + u * 32 + lane;
+                if (c < vecs) to[c] = tmp[u];
+            }
+        }
         const uint32_t* sf_from = reinterpret_cast<const uint32_t*>(peer + L.off_x_sf) + static_cast<uint64_t>(token) * sf_words;
-        for (uint32_t c = lane; c < sf_words; c += 32) l1_sf[static_cast<uint64_t>(c) * L.pool_rows + dst] = sf_from[c];
+        // scale words go straight into the per-128-row order tcgen05.cp reads (no transposition in the GEMM)
+        const uint32_t sf_dst = moe_sf_row(dst);
+        for (uint32_t c = lane; c < sf_words; c += 32) l1_sf[static_cast<uint64_t>(c) * L.pool_rows + sf_dst] = sf_from[c];
         if (lane == 0) {
             pool_w[dst] = reinterpret_cast<const float*>(peer + L.off_topk_w)[pair];
             meta[dst * 3 + 0] = static_cast<int32_t>(src);
             meta[dst * 3 + 1] = static_cast<int32_t>(token);
             meta[dst * 3 + 2] = static_cast<int32_t>(slot);
         }
+        if (pulled != nullptr) {
+            // the row is read by TMA (async proxy) in another CTA once the block's count is complete
+            asm volatile("fence.proxy.async;" ::: "memory");
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) atomicAdd(pulled + dst / 128, 1u);
+        }
     }
+}
+
+__global__ void __launch_bounds__(256) moe_pull_kernel(const MoeArgs a) {
+    const MoeLayout& L = a.L;
+    const uint32_t* work = reinterpret_cast<const uint32_t*>(a.base[a.rank] + L.off_work);
+    extern __shared__ uint32_t s_prefix[];   // [segments + 1]
+    const uint32_t segments = L.experts_local * L.ranks;
+    for (uint32_t i = threadIdx.x; i <= segments; i += 256)
+        s_prefix[i] = work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + i];
+    __syncthreads();
+    moe_pull_rows(a, s_prefix, blockIdx.x * 8 + threadIdx.x / 32, gridDim.x * 8, threadIdx.x & 31, nullptr);
 }
 
 // ---- cross-rank barrier on its own (after the experts' ranks have pushed their results).  One CTA.
@@ -238,32 +314,68 @@ __global__ void __launch_bounds__(32) moe_barrier_kernel(const MoeArgs a) {
 }
 
 // ---- last step: y[t] = bf16(sum over the token's valid slots, in slot order, of its combine rows).
-// grid: num_tokens, block: 128; each thread owns 8 consecutive columns per pass.
-__global__ void __launch_bounds__(128) moe_reduce_kernel(const MoeArgs a, __nv_bfloat16* y, int64_t ldy) {
+// `nthreads` threads of one CTA own 8 consecutive columns each per pass.
+// Columns [c, c + 8) and, if second, [c2, c2 + 8) of token t: every slot load of both column groups is issued before
+// any is used, so a thread keeps up to 16 16-byte loads in flight (the fused kernel has few threads per SM).
+template <bool kTwo>
+DG_DEVICE void moe_reduce_cols(const MoeArgs& a, __nv_bfloat16* y, int64_t ldy, uint32_t t, uint32_t c, uint32_t c2) {
     const MoeLayout& L = a.L;
-    const uint32_t t = blockIdx.x;
     const long long* idx = reinterpret_cast<const long long*>(a.base[a.rank] + L.off_topk_idx) + static_cast<uint64_t>(t) * L.topk;
-    const uint8_t* combine = a.base[a.rank] + L.off_combine;
-    for (uint32_t c = threadIdx.x * 8; c < L.hidden; c += 128 * 8) {
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (uint32_t s = 0; s < L.topk; ++s) {
-            const long long e = idx[s];
-            if (e < 0 || e >= static_cast<long long>(L.experts)) continue;
-            const uint4 v = *reinterpret_cast<const uint4*>(
-                combine + ((static_cast<uint64_t>(s) * L.t_max + t) * L.hidden + c) * 2);
-            const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+    const uint8_t* col = a.base[a.rank] + L.off_combine + (static_cast<uint64_t>(t) * L.hidden + c) * 2;
+    const int64_t delta = (static_cast<int64_t>(c2) - static_cast<int64_t>(c)) * 2;
+    const uint64_t plane = static_cast<uint64_t>(L.t_max) * L.hidden * 2;
+    float acc0[8] = {0, 0, 0, 0, 0, 0, 0, 0}, acc1[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (uint32_t s0 = 0; s0 < L.topk; s0 += 8) {
+        uint4 v0[8], v1[8];
+        uint32_t mask = 0;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(b[i]);
-                acc[2 * i] += f.x, acc[2 * i + 1] += f.y;
+        for (uint32_t u = 0; u < 8; ++u) {
+            const uint32_t s = s0 + u;
+            v0[u] = make_uint4(0, 0, 0, 0), v1[u] = make_uint4(0, 0, 0, 0);
+            if (s < L.topk) {
+                const long long e = idx[s];
+                if (e >= 0 && e < static_cast<long long>(L.experts)) {
+                    mask |= 1u << u;
+                    v0[u] = *reinterpret_cast<const uint4*>(col + s * plane);
+                    if (kTwo) v1[u] = *reinterpret_cast<const uint4*>(col + s * plane + delta);
+                }
             }
         }
-        uint4 out;
-        __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
+        // masked slots hold +0.0 and leave the sums unchanged, so the order of the valid ones is the slot order
 #pragma unroll
-        for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(y) + (static_cast<uint64_t>(t) * ldy + c) * 2) = out;
+        for (uint32_t u = 0; u < 8; ++u) {
+            const __nv_bfloat162* b0 = reinterpret_cast<const __nv_bfloat162*>(&v0[u]);
+            const __nv_bfloat162* b1 = reinterpret_cast<const __nv_bfloat162*>(&v1[u]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f0 = __bfloat1622float2(b0[i]);
+                acc0[2 * i] += f0.x, acc0[2 * i + 1] += f0.y;
+                if (kTwo) {
+                    const float2 f1 = __bfloat1622float2(b1[i]);
+                    acc1[2 * i] += f1.x, acc1[2 * i + 1] += f1.y;
+                }
+            }
+        }
+        (void)mask;
     }
+    uint4 out;
+    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(acc0[2 * i], acc0[2 * i + 1]);
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(y) + (static_cast<uint64_t>(t) * ldy + c) * 2) = out;
+    if (kTwo) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(acc1[2 * i], acc1[2 * i + 1]);
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(y) + (static_cast<uint64_t>(t) * ldy + c2) * 2) = out;
+    }
+}
+DG_DEVICE void moe_reduce_token(const MoeArgs& a, __nv_bfloat16* y, int64_t ldy, uint32_t t, uint32_t tid, uint32_t nthreads) {
+    for (uint32_t c = tid * 8; c < a.L.hidden; c += nthreads * 8) moe_reduce_cols<false>(a, y, ldy, t, c, c);
+}
+
+// grid: num_tokens, block: 128
+__global__ void __launch_bounds__(128) moe_reduce_kernel(const MoeArgs a, __nv_bfloat16* y, int64_t ldy) {
+    moe_reduce_token(a, y, ldy, blockIdx.x, threadIdx.x, 128);
 }
 
 }  // namespace dg

@@ -1,0 +1,439 @@
+// Mega MoE forward as ONE persistent kernel: dispatch (count, index scatter, count exchange, token pull over
+// NVLink peer loads), the two expert GEMMs (tcgen05 block-scaled UMMA, 2-CTA pairs, 256-token tiles) with the
+// SwiGLU / requantisation and combine-push epilogues, and the top-k reduction.
+//
+// Dataflow inside the launch: pull warps fill the expert-sorted pool in pool order and count rows per 128-row
+// block; the TMA producer starts a first-GEMM tile as soon as its rows are there; second-GEMM tiles of token
+// tile j - lag are interleaved after the first-GEMM tiles of tile j and wait (rarely) on a per-tile counter
+// that the first GEMM's epilogue bumps; the combine push therefore spreads over the whole kernel.  Two
+// grid-wide barriers (after the scatter, before the reduction) and two cross-rank barriers per call.
+// Every wait is bounded and reports through the status block.
+//
+// Takes the role of sm100_fp8_fp4_mega_moe_impl
+// (deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh:64-94) and its scheduler
+// (deep_gemm/include/deep_gemm/scheduler/mega_moe.cuh:372-476).
+#pragma once
+
+#include "mega_moe.cuh"
+
+namespace dg {
+
+constexpr uint32_t kFusedThreads = 384;
+
+struct MoeFusedParams {
+    CUtensorMap tm_w[2], tm_wsf[2], tm_act[2], tm_actsf[2];   // [0]: first GEMM (W13, pool tokens), [1]: second (W2, activations)
+    MoeArgs a;
+    MoeEpilogueParams e;
+    __nv_bfloat16* y;
+    int64_t ldy;
+    uint32_t num_ctas;
+    unsigned long long* trace;   // optional per-CTA time stamps (builds with DG_TRACE only)
+    uint32_t lag;   // token tiles between a tile's first-GEMM slots and its second-GEMM slots in the schedule
+};
+
+struct FusedCfg {
+    static constexpr uint32_t BN = 256, R_STAGE = 128 * 128, C_STAGE = 128 * 128, SFR_STAGE = 512, SFC_STAGE = 1024;
+    static constexpr uint32_t STAGE_BYTES = R_STAGE + C_STAGE + SFR_STAGE + SFC_STAGE;
+    static constexpr uint32_t PITCH = 272;
+    static constexpr uint32_t TABLE_OFF = 2 * 32 * PITCH;
+    static constexpr uint32_t PREFIX_OFF = TABLE_OFF + 2 * 256 * 8;   // (expert, source) segment prefix, <= 512 words
+    static constexpr uint32_t kMaxSegments = 511;
+    static constexpr uint32_t CD_BYTES = (PREFIX_OFF + 512 * 4 + 1023) / 1024 * 1024;
+    static constexpr uint32_t kStages = (232448 - 1024 - CD_BYTES - 1024) / STAGE_BYTES;
+    static constexpr uint32_t kSmemBytes = 1024 + kStages * STAGE_BYTES + CD_BYTES + 1024;
+    static constexpr uint32_t kOverlap = 16, kAccStride = BN - kOverlap, kSfrCol = 2 * BN - kOverlap, kSfcCol = kSfrCol + 4;
+    static constexpr uint32_t kTmemCols = 512;
+    // bytes one CTA's loads add to the stage barrier: FP4 weights count packed bytes
+    static constexpr uint32_t kTxBytes = R_STAGE / 2 + C_STAGE + SFR_STAGE + SFC_STAGE;
+};
+static_assert(FusedCfg::kStages >= 4 && FusedCfg::kStages <= 10, "stage count");
+
+struct FusedTile {
+    uint32_t kind;   // 0: first GEMM, 1: second GEMM
+    uint32_t tile, row0, rows, group, n_blk, valid0, valid1;
+};
+
+// Bounded spin on a device-scope counter; false on timeout / abort.
+DG_DEVICE bool fused_wait_counter(const uint32_t* counter, uint32_t target, volatile uint32_t* abort_flag,
+                                  const MoeArgs& a, uint32_t site, uint32_t info) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+    if (static_cast<int32_t>(v - target) >= 0) return true;
+    const uint64_t t0 = global_timer_ns();
+    const uint64_t budget = static_cast<uint64_t>(a.timeout_ms) * 1000000ull;
+    while (true) {
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        if (static_cast<int32_t>(v - target) >= 0) return true;
+        __nanosleep(100);
+        if (*abort_flag) return false;
+        if (global_timer_ns() - t0 > budget) {
+            if (atomicCAS(a.status, 0u, static_cast<uint32_t>(kStatusTimeout)) == 0u) {
+                a.status[1] = site, a.status[2] = blockIdx.x, a.status[3] = info, a.status[4] = v, a.status[5] = target;
+                __threadfence_system();
+            }
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
+
+// Schedule slot -> tile.  Slots come in rounds of (n1 + n2): round j holds the first GEMM's n1 tiles of token
+// tile j and the second GEMM's n2 tiles of token tile j - lag.  Returns false for an empty slot.
+DG_DEVICE bool fused_slot_to_tile(const uint32_t* table, uint32_t num_tiles, uint32_t n1, uint32_t n2, uint32_t lag,
+                                  uint32_t slot, FusedTile& t) {
+    const uint32_t round = slot / (n1 + n2), r = slot % (n1 + n2);
+    if (r < n1) {
+        if (round >= num_tiles) return false;
+        t.kind = 0, t.tile = round, t.n_blk = r;
+    } else {
+        if (round < lag || round - lag >= num_tiles) return false;
+        t.kind = 1, t.tile = round - lag, t.n_blk = r - n1;
+    }
+    const uint32_t* e = table + t.tile * 8;
+    t.row0 = e[0], t.rows = e[1], t.group = e[2], t.valid0 = e[3], t.valid1 = e[4];
+    return true;
+}
+
+// Grid-wide barrier on a monotonic counter (all CTAs co-resident: one per SM).  Whole CTA calls it.
+DG_DEVICE bool fused_grid_barrier(uint32_t* counter, uint32_t target, volatile uint32_t* abort_flag, const MoeArgs& a,
+                                  uint32_t site) {
+    __shared__ uint32_t s_ok;
+    __threadfence_system();   // also covers this CTA's stores to peer buffers
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        atomicAdd(counter, 1u);
+        s_ok = fused_wait_counter(counter, target, abort_flag, a, site, target) ? 1u : 0u;
+    }
+    __syncthreads();
+    return s_ok != 0;
+}
+
+#ifdef DG_TRACE
+#define DG_FUSED_STAMP(slot_) do { if (p.trace != nullptr && lane == 0) p.trace[(blockIdx.x * 16 + warp) * 8 + (slot_)] = global_timer_ns(); } while (0)
+#else
+#define DG_FUSED_STAMP(slot_) do { } while (0)
+#endif
+
+__global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const __grid_constant__ MoeFusedParams p) {
+    using Cfg = FusedCfg;
+    constexpr uint32_t kStages = Cfg::kStages, BN = Cfg::BN;
+    const MoeLayout& L = p.a.L;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t smem_r = smem_base;
+    const uint32_t smem_c = smem_r + kStages * Cfg::R_STAGE;
+    const uint32_t smem_cd = smem_c + kStages * Cfg::C_STAGE;
+    const uint32_t smem_sfr = smem_cd + Cfg::CD_BYTES;
+    const uint32_t smem_sfc = smem_sfr + kStages * Cfg::SFR_STAGE;
+    GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(smem_gen + (smem_sfc + kStages * Cfg::SFC_STAGE - smem_base));
+    uint32_t* s_prefix = reinterpret_cast<uint32_t*>(smem_gen + (smem_cd - smem_base) + Cfg::PREFIX_OFF);   // [segments + 1]
+
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t cta_rank = cluster_ctarank();
+    const bool is_leader = cta_rank == 0;
+    const uint32_t unit = blockIdx.x / 2, num_units = p.num_ctas / 2;
+    volatile uint32_t* abort_flag = &bars->abort;
+    const uint32_t peer_abort = map_to_cta(smem_u32(&bars->abort), cta_rank ^ 1);
+    uint32_t* work = reinterpret_cast<uint32_t*>(p.a.base[p.a.rank] + L.off_work);
+    GemmParams wp;   // only the fields wait_barrier reports through
+    wp.timeout_ms = p.a.timeout_ms, wp.status = p.a.status;
+
+    // ---------------------------------------------------------------- set-up
+    if (warp == 0 && lane == 0) {
+        for (uint32_t i = 0; i < 2; ++i) {
+            prefetch_tmap(&p.tm_w[i]), prefetch_tmap(&p.tm_wsf[i]), prefetch_tmap(&p.tm_act[i]), prefetch_tmap(&p.tm_actsf[i]);
+        }
+        for (uint32_t i = 0; i < kStages; ++i) {
+            mbar_init(&bars->full[i], 2);    // both CTAs' producers; every copy of the stage lands here
+            mbar_init(&bars->empty[i], 1);   // UMMA commit
+        }
+        for (uint32_t i = 0; i < 2; ++i) {
+            mbar_init(&bars->tmem_full[i], 1);
+            mbar_init(&bars->tmem_empty[i], 2 * 4);
+            mbar_init(&bars->overlap[i], 2 * 4);
+            mbar_init(&bars->epi_sync[i], 4);
+        }
+        bars->abort = 0;
+        fence_mbar_init();
+    }
+    cluster_sync();
+    if (warp == 1) {
+        tmem_alloc<2>(&bars->tmem_base, Cfg::kTmemCols);
+        tmem_relinquish<2>();
+    }
+    tc_fence_before();
+    cluster_sync();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+    DG_FUSED_STAMP(0);
+    // ---------------------------------------------------------------- dispatch, step 1: count and scatter indices
+    const uint32_t call_old = *reinterpret_cast<volatile uint32_t*>(work + MoeWork::kCall);
+    const uint32_t call_new = call_old + 1;
+    // the grid barrier's counter only advances in launches of this kernel: its targets follow their own count
+    const uint32_t fused_calls = *reinterpret_cast<volatile uint32_t*>(work + MoeFusedWork::kFusedCalls);
+    for (uint32_t i = blockIdx.x * kFusedThreads + threadIdx.x; i < p.a.num_tokens * L.topk; i += p.num_ctas * kFusedThreads)
+        moe_scatter_pair(p.a, i);
+    bool ok = fused_grid_barrier(work + MoeFusedWork::kGridSync, (2 * fused_calls + 1) * p.num_ctas, abort_flag, p.a, 201);
+    // step 2 (CTA 0): publish counts, cross-rank barrier, pool layout, tile table, counters, layout_ready
+    if (ok && blockIdx.x == 0) {
+        if (threadIdx.x == 0) work[MoeFusedWork::kFusedCalls] = fused_calls + 1;   // every CTA has read it before the barrier
+        MoeFusedHooks hooks;
+        hooks.tile_table = MoeFusedWork::tile_table(L), hooks.pulled = MoeFusedWork::pulled(L);
+        hooks.l1_done = MoeFusedWork::l1_done(L), hooks.num_tiles_word = MoeFusedWork::kNumTiles;
+        hooks.layout_ready_word = MoeFusedWork::kLayoutReady;
+        moe_exchange_body(p.a, threadIdx.x, kFusedThreads, &hooks);
+    }
+    if (ok) {
+        if (threadIdx.x == 0)
+            ok = fused_wait_counter(work + MoeFusedWork::kLayoutReady, call_new, abort_flag, p.a, 202, call_new);
+        // every thread needs the verdict and the layout
+        __shared__ uint32_t s_layout_ok;
+        if (threadIdx.x == 0) s_layout_ok = ok ? 1u : 0u;
+        __syncthreads();
+        ok = s_layout_ok != 0;
+    }
+    const uint32_t num_tiles = ok ? work[MoeFusedWork::kNumTiles] : 0;
+    const uint32_t* table = work + MoeFusedWork::tile_table(L);
+    uint32_t* pulled = work + MoeFusedWork::pulled(L);
+    uint32_t* l1_done = work + MoeFusedWork::l1_done(L);
+    const uint32_t n1 = 2 * L.inter / 256, n2 = L.hidden / 256;
+    const uint32_t num_slots = ok ? (num_tiles + p.lag) * (n1 + n2) : 0;
+    const uint32_t segments = L.experts_local * L.ranks;
+    if (ok) {
+        for (uint32_t i = threadIdx.x; i <= segments; i += kFusedThreads)
+            s_prefix[i] = work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + i];
+    }
+    __syncthreads();
+
+    DG_FUSED_STAMP(1);
+    uint32_t stage = 0, phase = 0;
+    auto advance = [&]() {
+        stage = stage + 1 == kStages ? 0 : stage + 1;
+        phase ^= (stage == 0);
+    };
+    uint32_t acc_iter = 0;
+    FusedTile tc;
+
+    if (warp == 0) {
+        // ============================================================ TMA producer
+        const uint32_t full_bar0 = map_to_cta(smem_u32(&bars->full[0]), 0);
+        for (uint32_t slot = unit; slot < num_slots && ok; slot += num_units) {
+            if (!fused_slot_to_tile(table, num_tiles, n1, n2, p.lag, slot, tc)) continue;
+            // Data dependencies: pool rows pulled (first GEMM) / activations written (second GEMM)
+            if (tc.kind == 0) {
+                ok = fused_wait_counter(pulled + tc.row0 / 128, tc.valid0, abort_flag, p.a, 203, tc.tile);
+                if (ok && tc.rows > 128) ok = fused_wait_counter(pulled + tc.row0 / 128 + 1, tc.valid1, abort_flag, p.a, 203, tc.tile);
+            } else {
+                ok = fused_wait_counter(l1_done + tc.tile, n1 * 8, abort_flag, p.a, 204, tc.tile);
+            }
+            if (!ok) break;
+            asm volatile("fence.proxy.async;" ::: "memory");   // the rows were written through the generic proxy
+            const uint32_t k = tc.kind;
+            const uint32_t w_rows = k == 0 ? 2 * L.inter : L.hidden;          // weight rows per expert
+            const uint32_t pk = (k == 0 ? L.hidden : L.inter) / 128;          // packed scale words per row
+            const uint32_t r_mn = tc.group * w_rows + tc.n_blk * 256 + cta_rank * 128;
+            const uint32_t sfr_mn = tc.n_blk * 256 + cta_rank * 128, sfr_k = tc.group * pk;
+            const uint32_t c_mn = tc.row0 + cta_rank * (tc.rows / 2);
+            const uint32_t sfc_mn = tc.row0;
+            const uint32_t num_kb = pk;
+            for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
+                ok = wait_barrier(&bars->empty[stage], phase ^ 1, abort_flag, peer_abort, wp, kSiteProducerEmpty, acc_iter, kb, stage);
+                if (!ok) break;
+                if (elect_one()) {
+                    const uint32_t full_bar = full_bar0 + stage * 8;
+                    mbar_arrive_expect_tx_cluster(full_bar, Cfg::kTxBytes);
+                    tma_load_2d<true>(smem_sfr + stage * Cfg::SFR_STAGE, &p.tm_wsf[k], full_bar, sfr_mn, sfr_k + kb);
+                    tma_load_2d<true>(smem_sfc + stage * Cfg::SFC_STAGE, &p.tm_actsf[k], full_bar, sfc_mn, kb);
+                    tma_load_2d<true>(smem_r + stage * Cfg::R_STAGE, &p.tm_w[k], full_bar, kb * 128, r_mn);
+                    tma_load_2d<true>(smem_c + stage * Cfg::C_STAGE, &p.tm_act[k], full_bar, kb * 128, c_mn);
+                }
+                __syncwarp();
+            }
+            ++acc_iter;
+        }
+    } else if (warp == 1) {
+        // ============================================================ UMMA issuer (leader CTA)
+        if (is_leader) {
+            const uint32_t idesc_base = make_idesc_mxf8f6f4(kFmtE2M1, kFmtE4M3, false, false, 256, BN);
+            const uint64_t sf_desc_hi = make_smem_desc(0, 0, 128, kSwizzleNone);
+            const uint32_t op_hi = static_cast<uint32_t>(make_smem_desc(0, 0, 1024, kSwizzle128B) >> 32);
+            const uint32_t r_lo0 = static_cast<uint32_t>(make_smem_desc(smem_r, 0, 1024, kSwizzle128B));
+            const uint32_t c_lo0 = static_cast<uint32_t>(make_smem_desc(smem_c, 0, 1024, kSwizzle128B));
+            const uint32_t sfr_tmem = tmem_base + Cfg::kSfrCol, sfc_tmem = tmem_base + Cfg::kSfcCol;
+            for (uint32_t slot = unit; slot < num_slots && ok; slot += num_units) {
+                if (!fused_slot_to_tile(table, num_tiles, n1, n2, p.lag, slot, tc)) continue;
+                const uint32_t acc = acc_iter & 1, acc_phase = (acc_iter >> 1) & 1;
+                ok = wait_barrier(&bars->tmem_empty[acc], acc_phase ^ 1, abort_flag, peer_abort, wp, kSiteMmaTmemEmpty, acc_iter, 0, acc);
+                if (ok && acc_iter > 0) {
+                    const uint32_t prev = acc_iter - 1;
+                    ok = wait_barrier(&bars->overlap[prev & 1], (prev >> 1) & 1, abort_flag, peer_abort, wp, kSiteMmaOverlap, acc_iter, 0, acc);
+                }
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * Cfg::kAccStride;
+                const uint32_t idesc_tile = idesc_with_n(idesc_base, tc.rows);
+                const uint32_t num_kb = (tc.kind == 0 ? L.hidden : L.inter) / 128;
+                for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
+                    ok = wait_barrier(&bars->full[stage], phase, abort_flag, peer_abort, wp, kSiteMmaFull, acc_iter, kb, stage);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (elect_one()) {
+                        utccp_32x128b_warpx4<2>(sfr_tmem, sf_desc_hi | ((smem_sfr + stage * Cfg::SFR_STAGE) >> 4));
+                        utccp_32x128b_warpx4<2>(sfc_tmem, sf_desc_hi | ((smem_sfc + stage * Cfg::SFC_STAGE) >> 4));
+                        utccp_32x128b_warpx4<2>(sfc_tmem + 4, sf_desc_hi | ((smem_sfc + stage * Cfg::SFC_STAGE + 512) >> 4));
+                        const uint32_t r_lo = r_lo0 + stage * (Cfg::R_STAGE >> 4), c_lo = c_lo0 + stage * (Cfg::C_STAGE >> 4);
+#pragma unroll
+                        for (uint32_t ks = 0; ks < 4; ++ks) {
+                            const uint64_t r_desc = (static_cast<uint64_t>(op_hi) << 32) | (r_lo + ks * 2);
+                            const uint64_t c_desc = (static_cast<uint64_t>(op_hi) << 32) | (c_lo + ks * 2);
+                            umma_mxf8f6f4<2>(d_tmem, r_desc, c_desc, idesc_tile | (ks << 4) | (ks << 29), sfr_tmem, sfc_tmem,
+                                             (kb | ks) != 0);
+                        }
+                        umma_commit<2>(&bars->empty[stage]);
+                        if (kb + 1 == num_kb) umma_commit<2>(&bars->tmem_full[acc]);
+                    }
+                    __syncwarp();
+                }
+                ++acc_iter;
+            }
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ============================================================ epilogue (TMEM lane quadrant = warp % 4)
+        const uint32_t q = warp - 4;
+        const uint32_t tmem_empty_bar = map_to_cta(smem_u32(&bars->tmem_empty[0]), 0);
+        const uint32_t overlap_bar = map_to_cta(smem_u32(&bars->overlap[0]), 0);
+        uint32_t moe_buf = 0, moe_chunks = 0;
+        for (uint32_t slot = unit; slot < num_slots && ok; slot += num_units) {
+            if (!fused_slot_to_tile(table, num_tiles, n1, n2, p.lag, slot, tc)) continue;
+            const uint32_t acc = acc_iter & 1, acc_phase = (acc_iter >> 1) & 1;
+            // Per-token data of the tile, fetched while its UMMAs run.  The reading threads themselves must have
+            // seen the counters that say the pool rows (and, for the second GEMM, the routing metadata) are there.
+            if (tc.kind == 0) {
+                ok = fused_wait_counter(pulled + tc.row0 / 128, tc.valid0, abort_flag, p.a, 207, tc.tile);
+                if (ok && tc.rows > 128) ok = fused_wait_counter(pulled + tc.row0 / 128 + 1, tc.valid1, abort_flag, p.a, 207, tc.tile);
+            } else {
+                ok = fused_wait_counter(l1_done + tc.tile, n1 * 8, abort_flag, p.a, 208, tc.tile);
+            }
+            if (!ok) break;
+            uint64_t* ttab = reinterpret_cast<uint64_t*>(smem_gen + (smem_cd - smem_base) + Cfg::TABLE_OFF) + acc * 256;
+            for (uint32_t tok = q * 32 + lane; tok < tc.rows; tok += 128) {
+                const uint32_t row = tc.row0 + tok;
+                if (tc.kind == 0) {
+                    reinterpret_cast<float*>(ttab)[tok] = p.e.pool_w[row];
+                } else {
+                    const int32_t src_rank = p.e.pool_meta[row * 3];
+                    uint64_t dst = 0;
+                    if (src_rank >= 0) {
+                        const uint64_t token = static_cast<uint32_t>(p.e.pool_meta[row * 3 + 1]);
+                        const uint64_t sl = static_cast<uint32_t>(p.e.pool_meta[row * 3 + 2]);
+                        dst = reinterpret_cast<uint64_t>(p.e.peer_base[src_rank]) + p.e.off_combine +
+                              (sl * p.e.t_max + token) * p.e.hidden * 2;
+                    }
+                    ttab[tok] = dst;
+                }
+            }
+            ok = wait_barrier(&bars->tmem_full[acc], acc_phase, abort_flag, peer_abort, wp, kSiteEpilogueTmemFull, acc_iter, 0, acc);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_acc = tmem_base + acc * Cfg::kAccStride + ((q * 32) << 16);
+            const uint32_t n0 = tc.n_blk * 256 + cta_rank * 128;
+            const uint32_t num_chunks = (tc.rows + 31) / 32;
+            const bool reverse = acc == 0;   // stage 0 shares its last columns, stage 1 its first: drain those first
+#pragma unroll 1
+            for (uint32_t i = 0; i < num_chunks && ok; ++i) {
+                const uint32_t ch = reverse ? num_chunks - 1 - i : i;
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(t_acc + ch * 32, v);
+                tmem_ld_wait();
+                if (i == 0 || i + 1 == num_chunks) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (i == 0) mbar_arrive_cluster(overlap_bar + acc * 8);
+                        if (i + 1 == num_chunks) mbar_arrive_cluster(tmem_empty_bar + acc * 8);
+                    }
+                }
+                uint8_t* stage_gen = smem_gen + (smem_cd - smem_base) + moe_buf * 32 * Cfg::PITCH;
+#pragma unroll
+                for (uint32_t t = 0; t < 32; ++t)
+                    *reinterpret_cast<__nv_bfloat16*>(stage_gen + t * Cfg::PITCH + (q * 32 + lane) * 2) =
+                        __float2bfloat16_rn(__uint_as_float(v[t]));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->epi_sync[moe_buf]);
+                ok = wait_barrier(&bars->epi_sync[moe_buf], (moe_chunks >> 1) & 1, abort_flag, peer_abort, wp, kSiteEpilogueSync,
+                                  acc_iter, ch, moe_buf);
+                ++moe_chunks;
+                if (!ok) break;
+                const uint32_t chunk_rows = min(32u, tc.rows - ch * 32);
+                if (tc.kind == 0)
+                    moe_l1_chunk(p.e, stage_gen, Cfg::PITCH, reinterpret_cast<const float*>(ttab), q, lane, ch, chunk_rows, tc.row0, n0);
+                else
+                    moe_l2_chunk(stage_gen, Cfg::PITCH, ttab, q * 32 + lane, ch, chunk_rows, n0);
+                moe_buf ^= 1;
+            }
+            if (!ok) break;
+            if (tc.kind == 0) {
+                // The tile's activations are read by TMA in other CTAs once all of its n-tiles have reported
+                asm volatile("fence.proxy.async;" ::: "memory");
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) atomicAdd(l1_done + tc.tile, 1u);
+            }
+            ++acc_iter;
+        }
+        __threadfence_system();   // pushes to the source ranks are out before the final barriers
+    } else if (ok) {
+        // ============================================================ pull warps (2, 3, 8..11): fill the pool in pool order
+        const uint32_t pw = warp < 4 ? warp - 2 : warp - 6;   // 0..5
+        moe_pull_rows(p.a, s_prefix, blockIdx.x * 6 + pw, p.num_ctas * 6, lane, pulled);
+    }
+
+    DG_FUSED_STAMP(2);
+    // ---------------------------------------------------------------- combine: everyone has pushed, then reduce
+    bool ok2 = fused_grid_barrier(work + MoeFusedWork::kGridSync, (2 * fused_calls + 2) * p.num_ctas, abort_flag, p.a, 205);
+    if (ok2 && blockIdx.x == 0) {
+        __shared__ uint32_t s_bar_ok;
+        if (threadIdx.x == 0) s_bar_ok = 1;
+        __syncthreads();
+        if (threadIdx.x < L.ranks)
+            if (!moe_cross_rank_barrier(p.a, 1, 2 * call_new, threadIdx.x)) s_bar_ok = 0;
+        __syncthreads();
+        if (threadIdx.x == 0 && s_bar_ok)
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(work + MoeFusedWork::kCombineReady), "r"(call_new) : "memory");
+    }
+    if (ok2) {
+        __shared__ uint32_t s_comb_ok;
+        if (threadIdx.x == 0)
+            s_comb_ok = fused_wait_counter(work + MoeFusedWork::kCombineReady, call_new, abort_flag, p.a, 206, call_new) ? 1u : 0u;
+        __syncthreads();
+        DG_FUSED_STAMP(3);
+        if (s_comb_ok) {
+            // this CTA's tokens (blockIdx.x, + num_ctas, ...) as one flat list of 8-column items: no idle passes
+            const uint32_t chunks = L.hidden / 8;
+            const uint32_t my_tokens = p.a.num_tokens > blockIdx.x ? (p.a.num_tokens - blockIdx.x + p.num_ctas - 1) / p.num_ctas : 0;
+            for (uint32_t item = threadIdx.x; item < my_tokens * chunks; item += kFusedThreads) {
+                const uint32_t t = blockIdx.x + (item / chunks) * p.num_ctas, c = (item % chunks) * 8;
+                moe_reduce_cols<false>(p.a, p.y, p.ldy, t, c, c);
+            }
+        }
+    }
+
+    DG_FUSED_STAMP(4);
+    // ---------------------------------------------------------------- tear-down
+    if (*abort_flag) {
+        for (int i = 0; i < 20; ++i) __nanosleep(10000);
+    }
+    __syncwarp();
+    tc_fence_before();
+    cluster_sync();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<2>(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+}  // namespace dg

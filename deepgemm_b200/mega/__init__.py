@@ -20,6 +20,11 @@ from ..layout import _require, _stream
 from ..utils.math import align
 
 
+def set_fused(enable: bool) -> None:
+    """Run the forward as one persistent kernel (default) or as one kernel per phase; same results."""
+    _lib.check(_lib.lib().dg_set_mega_moe_fused(int(bool(enable))))
+
+
 def get_token_alignment_for_mega_moe() -> int:
     return int(_lib.lib().dg_get_token_alignment_for_mega_moe())
 

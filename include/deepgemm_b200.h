@@ -168,6 +168,11 @@ typedef struct dg_moe_args {
  * group must make the call; calls on one buffer must not overlap. */
 int dg_mega_moe_forward(const dg_moe_args* args);
 
+/* 1 (default): the forward runs as one persistent kernel (dispatch, both expert GEMMs, combine and reduction in a
+ * single launch; needs all of the GPU's SMs free, hidden % 256 == 0 and experts_per_rank * ranks <= 511).
+ * 0: one kernel per phase (7 launches), the same arithmetic; also the path taken when the conditions fail. */
+int dg_set_mega_moe_fused(int32_t enable);
+
 /* ---- Dense FP8 GEMM that allocates nothing ------------------------------------------------------------
  * No counterpart in the reference.  For callers that must not call cudaMalloc (or any allocating library
  * routine) around the GEMM - a plugin running inside another runtime's memory plan, a real-time loop, code

@@ -65,7 +65,8 @@ def run_rank(group, rank, ranks, cfg, results=None):
     buf = dg.get_symm_buffer_for_mega_moe(group, experts, tokens, topk, hidden, inter)
     stats = torch.zeros(el, dtype=torch.int32, device="cuda")
     y = None
-    for it in range(2):                                        # twice: the buffer's epochs and counters must reset
+    for it in range(4):              # repeated calls: epochs and counters must reset; fused and per-phase paths alternate
+        dg.mega.set_fused(it % 2 == 0)
         buf.x[:tokens].copy_(x_fp8)
         buf.x_sf[:tokens].copy_(x_sf)
         buf.topk_idx[:tokens].copy_(idx)
@@ -77,7 +78,7 @@ def run_rank(group, rank, ranks, cfg, results=None):
         if group is not None:
             group.barrier()
         if y is not None:
-            assert torch.equal(y, y_it), "second call differs"
+            assert torch.equal(y, y_it), f"call {it} (fused={it % 2 == 0}) differs from the first"
         y = y_it
     ref, counts = OM.mega_moe_reference(x_deq, idx.cpu().numpy(), w.cpu().numpy(), deq1, deq2, clamp)
     diff = H.calc_diff(H.to_np(y), ref)
@@ -86,7 +87,8 @@ def run_rank(group, rank, ranks, cfg, results=None):
     # Integer-exact side: rows received per local expert (over all ranks' tokens) and the pool's routing metadata
     all_idx = [make_inputs(tokens, hidden, experts, topk, 100 + r, drop=drop)[2].cpu().numpy() for r in range(ranks)]
     expect = np.array([sum(int((a == lo + e).sum()) for a in all_idx) for e in range(el)])
-    assert np.array_equal(stats.cpu().numpy(), 2 * expect)
+    assert np.array_equal(stats.cpu().numpy(), 4 * expect)
+    dg.mega.set_fused(True)
     meta = buf.token_src_metadata.cpu().numpy()
     l1_acts = buf.l1_acts.view(torch.uint8)
     start = 0
