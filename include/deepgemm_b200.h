@@ -127,7 +127,8 @@ typedef struct dg_moe_config {
  * reference): x e4m3 [T, H]; x_sf int32 [T, H/128]; topk_idx int64 [T, K]; topk_weights f32 [T, K];
  * l1_acts e4m3 [P, H]; l1_acts_sf int32 [P, H/128] with strides (1, P); l2_acts e4m3 [P, I];
  * l2_acts_sf int32 [P, I/128] with strides (1, P); token_src_metadata int32 [P, 3];
- * combine bf16 [K, T, H].  P = pool_rows. */
+ * combine bf16 [K, T, H].  P = pool_rows.  Inside every 128 pool rows the scale words of l1_acts_sf and
+ * l2_acts_sf sit in the order tcgen05.cp consumes: row r of the block is stored at (r % 32) * 4 + r / 32. */
 typedef struct dg_moe_layout {
     int64_t num_bytes, pool_rows;
     int64_t off_x, off_x_sf, off_topk_idx, off_topk_weights;

@@ -119,3 +119,15 @@ def test_mega_moe_weight_transforms():
     tr = L.transpose_sf_for_utccp(t)
     i = np.arange(n)
     assert np.array_equal(tr[:, L.utccp_row_index(i)], t[:, i])
+
+
+def test_mega_moe_oracle_matches_reference_baseline():
+    """oracle/mega_moe.py against the output of the reference's own torch baseline
+    (tests/test_mega_moe.py:466-480, run by tests/golden/make_mega_moe_golden.py): masked slots, an expert
+    without tokens, 3 slots per token.  Bit for bit."""
+    import os
+    from oracle import mega_moe as OM
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "mega_moe_golden.npz"))
+    y, counts = OM.mega_moe_reference(g["x_deq"], g["topk_idx"], g["topk_weights"], g["l1_deq"], g["l2_deq"])
+    assert np.array_equal(y, g["y"])
+    assert counts[5] == 0 and counts.sum() == (g["topk_idx"] >= 0).sum()
