@@ -1,6 +1,7 @@
 """Benchmark of the block-scaled GEMM hot path (one JSON line on stdout).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--all-configs]
+                    [--only all|gemm|mega_moe] [--moe-tokens T] [--moe-experts E]
 
 A step is one pass of the hot path over one batch of synthetic input.  The headline workload is
 the contiguous M-grouped FP8 GEMM (8 experts, N=4096, K=7168, rows per expert uniform in
@@ -34,6 +35,8 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# DRAM traffic of one launch of the headline kernel, from one ncu capture (not measured live: ncu is not part of a run)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2.464e9
 NOMINAL_FP8_TFLOPS = 4500.0
 
 
@@ -128,11 +131,12 @@ def make_c2(device, seed=0):
     layout = layout.to(device)
     d = torch.empty((m, n), dtype=torch.bfloat16, device=device)
     flops = 2.0 * sum(actual) * n * k
+    nbytes = m * k + groups * n * k + m * n * 2
     cfg = dict(workload="m_grouped_fp8_gemm_nt_contiguous (BASELINE config 2)", groups=groups, m=m,
                m_valid=sum(actual), n=n, k=k, alignment=alignment, a="e4m3 1x128 UE8M0", b="e4m3 128x128 UE8M0",
                out="bf16", sf="pre-packed int32", l2="inputs (1.2 GB) larger than L2")
     return dict(a=(a_q, sfa), b=(b_q, sfb), a_fp32_sf=a_sf, b_fp32_sf=b_sf, layout=layout, d=d, flops=flops, cfg=cfg,
-                actual=actual, aligned=aligned)
+                actual=actual, aligned=aligned, bytes=nbytes)
 
 
 def run_c2(w):
@@ -353,6 +357,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--all-configs", action="store_true", help="also time the other single-GPU configs")
+    ap.add_argument("--only", default="all", choices=["all", "gemm", "mega_moe"],
+                    help="profiling aid: `gemm` runs the headline GEMM alone (no other configs, no Mega MoE, no CPU "
+                         "baseline); `mega_moe` runs the Mega MoE forward alone and prints its record")
+    ap.add_argument("--moe-tokens", type=int, default=4096, help="tokens per rank of the Mega MoE run")
+    ap.add_argument("--moe-experts", type=int, default=32, help="experts per rank of the Mega MoE run")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -372,6 +381,15 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     import deepgemm_b200 as dg
+
+    if args.only == "mega_moe":
+        moe = mega_moe_bench(device, dist.group.WORLD if world > 1 else None, rank, world, max(1, min(args.steps, 10)),
+                             args.warmup, tokens=args.moe_tokens, experts_per_rank=args.moe_experts)
+        if rank == 0:
+            emit({"mega_moe": moe})
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     w = make_c2(device, seed=0)
     peaks = measured_peaks()
@@ -437,8 +455,10 @@ def main():
     del a_host, sfa_host, d_host, a_dev
     moe = None
     try:
+        if args.only == "gemm":
+            raise RuntimeError("skipped (--only gemm)")
         moe = mega_moe_bench(device, dist.group.WORLD if world > 1 else None, rank, world, max(3, min(args.steps, 10)),
-                             args.warmup)
+                             args.warmup, tokens=args.moe_tokens, experts_per_rank=args.moe_experts)
         peak_fp8 = 2.0 * peaks["bf16"]
         moe["roofline_frac_of_2x_measured_bf16"] = moe["tflops_per_gpu"] / peak_fp8
         moe["roofline_frac_of_nominal_4500"] = moe["tflops_per_gpu"] / NOMINAL_FP8_TFLOPS
@@ -451,7 +471,7 @@ def main():
         return
 
     # ---- checks and baselines (rank 0)
-    cpu, d_cpu, rows = cpu_baseline_sample(w) if world == 1 else (None, None, 0)
+    cpu, d_cpu, rows = cpu_baseline_sample(w) if (world == 1 and args.only == "all") else (None, None, 0)
     parity = None
     if d_cpu is not None:
         from oracle.quant import calc_diff
@@ -459,7 +479,8 @@ def main():
     kernel_ms = sorted(times)[len(times) // 2]
     achieved = w["flops"] / kernel_ms / 1e9
     peak = 2.0 * peaks["bf16"]
-    extra = other_configs(device, min(args.steps, 10), args.warmup) if (args.all_configs or world == 1) else {}
+    extra = other_configs(device, min(args.steps, 10), args.warmup) \
+        if (args.all_configs or (world == 1 and args.only == "all")) else {}
     line = {
         "metric": "fp8_fp4_gemm_tflops", "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -472,7 +493,10 @@ def main():
                      "peak_source": f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']}); FP8 UMMA issues at twice the BF16 rate",
                      "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
                      "frac_of_2x_bf16_sustained": achieved / (2.0 * peaks["bf16_sustained"]),
-                     "traffic": None, "kernel_ms": kernel_ms},
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "traffic_unit": "bytes per launch",
+                     "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this "
+                                       "workload (profiles/gemm_bs_kernel_c2_grouped_contiguous.md)",
+                     "algorithmic_bytes": w["bytes"], "kernel_ms": kernel_ms},
         "cpu_baseline": cpu,
         "clocks": clocks,
         "parity_calc_diff_vs_cpu_oracle": parity,
