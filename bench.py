@@ -52,48 +52,66 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled during the timed region."""
+    """SM clock and clock-event (throttle) reasons of one GPU, polled through NVML every 2 ms by a thread while the
+    timed region runs (read-only queries; nvidia-smi's fastest loop is too slow for a region of a few tens of ms)."""
 
-    def __init__(self, gpu_index: int):
-        self.samples, self.proc, self.gpu = [], None, gpu_index
+    def __init__(self, device):
+        self.samples, self.thread, self.stop_flag, self.handle, self.nv, self.error = [], None, False, None, None, None
+        try:
+            import pynvml as nv
+            import torch
+            nv.nvmlInit()
+            prop = torch.cuda.get_device_properties(device)
+            try:
+                bus = f"{prop.pci_domain_id:08x}:{prop.pci_bus_id:02x}:{prop.pci_device_id:02x}.0"
+                self.handle = nv.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            except Exception:
+                self.handle = nv.nvmlDeviceGetHandleByIndex(device.index or 0)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(self.handle, nv.NVML_CLOCK_SM))
+            self.nv = nv
+        except Exception as exc:
+            self.error = f"NVML unavailable: {type(exc).__name__}"
+
+    def _poll(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.samples.append((float(mhz), int(reasons)))
+            except Exception as exc:
+                self.error = f"NVML query failed: {type(exc).__name__}"
+                return
+            time.sleep(0.002)
 
     def start(self):
-        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
-        except Exception:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.samples.append(line.strip())
+        if self.nv is None:
+            return
+        self.stop_flag = False
+        self.thread = threading.Thread(target=self._poll, daemon=True)
+        self.thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        mhz, mx, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
-            parts = [x.strip() for x in s.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                mhz.append(float(parts[0]))
-                mx = float(parts[1])
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[2:6]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        mhz.sort()
-        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(mhz)}
+        if self.nv is None or self.thread is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self.error or "not started"], "samples": 0}
+        self.stop_flag = True
+        self.thread.join(timeout=1.0)
+        nv = self.nv
+        bits = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                "hw_power_brake_slowdown": 0x80}
+        mhz = sorted(m for m, _ in self.samples)
+        seen = 0
+        for _, r in self.samples:
+            seen |= r
+        reasons = sorted(name for name, bit in bits.items() if seen & bit)
+        out = {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_min_mhz": mhz[0] if mhz else None,
+               "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(mhz)}
+        if self.error:
+            out["note"] = self.error
+        return out
 
 
 # --------------------------------------------------------------------------- workloads
@@ -400,7 +418,7 @@ def main():
         torch.cuda.synchronize()
 
     # ---- kernel-only: inputs resident in HBM
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(device)
     for _ in range(args.warmup):
         run_c2(w)
     barrier()

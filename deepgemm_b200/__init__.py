@@ -38,6 +38,16 @@ m_grouped_fp8_gemm_nt_contiguous = m_grouped_fp8_fp4_gemm_nt_contiguous
 m_grouped_fp8_gemm_nn_contiguous = m_grouped_fp8_fp4_gemm_nn_contiguous
 m_grouped_fp8_gemm_nt_masked = m_grouped_fp8_fp4_gemm_nt_masked
 fp8_m_grouped_gemm_nt_masked = m_grouped_fp8_fp4_gemm_nt_masked
+fp4_gemm_nt = fp8_fp4_gemm_nt
+m_grouped_fp4_gemm_nt_contiguous = m_grouped_fp8_fp4_gemm_nt_contiguous
+m_grouped_fp4_gemm_nt_masked = m_grouped_fp8_fp4_gemm_nt_masked
+
+
+def k_grouped_fp8_gemm_nt_contiguous(*args, **kwargs):
+    """The K-major (NT) form of the K-grouped FP8 GEMM exists for sm_90 only; on sm_100 the reference's dispatch
+    ends in `Unsupported architecture` (csrc/apis/gemm.hpp:377-431).  Use k_grouped_fp8_gemm_tn_contiguous."""
+    raise RuntimeError("Unsupported architecture: k_grouped_fp8_gemm_nt_contiguous is an sm_90 entry point; "
+                       "sm_100 takes k_grouped_fp8_gemm_tn_contiguous")
 
 
 class epilogue:  # namespace, as deep_gemm.epilogue
