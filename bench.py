@@ -283,6 +283,10 @@ def mega_moe_bench(device, group, rank, world, steps, warmup, tokens=4096, exper
         times = []
         for _ in range(steps):
             barrier()
+            # a ~0.5 ms device-side spin first: the host enqueues the events and the call while the GPU is still
+            # busy, so the interval holds GPU time only, and the ranks' kernels start together
+            # (deep_gemm/testing/bench.py:109-113 of the reference aligns ranks the same way)
+            torch.cuda._sleep(1_000_000)
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
             step()
@@ -309,7 +313,8 @@ def mega_moe_bench(device, group, rank, world, steps, warmup, tokens=4096, exper
                 per_phase_path=dict(ms_per_step=ms_phase, tokens_per_s=world * tokens / ms_phase * 1e3,
                                     gpu_launches_per_step=7),
                 note="x: 1x32 UE8M0 E4M3 (the kernel's only recipe); weights MXFP4 ~N(0, 0.02); time = max over ranks, "
-                     "median of per-step CUDA-event times with a cross-rank barrier before each step")
+                     "median of per-step CUDA-event times; before each step a cross-rank barrier and a 0.5 ms device spin "
+                     "that hides the host's enqueue latency")
 
 
 def cpu_baseline_sample(w, budget_s=12.0, max_experts=6):

@@ -109,6 +109,93 @@ DG_DEVICE bool fused_grid_barrier(uint32_t* counter, uint32_t target, volatile u
     return s_ok != 0;
 }
 
+// Top-k reduction of this CTA's tokens (blockIdx.x, + num_ctas, ...) with the combine rows staged through shared
+// memory by bulk copies: one item = one token x one piece of kReducePiece columns x all of its valid slots (up to 8
+// rows of 6 KB), kReduceStages items in flight per CTA, so the memory-level parallelism does not depend on the
+// number of threads.  Thread 0 issues, all threads sum (slot order, FP32) and store BF16.  The kernel's operand
+// stages are free by now (all roles have left their loops and the grid barrier has passed).
+constexpr uint32_t kReducePiece = kFusedThreads * 8, kReduceStages = 4, kReduceSlotBytes = kReducePiece * 2;
+static_assert(kReduceStages * 8 * kReduceSlotBytes <= FusedCfg::kStages * (FusedCfg::R_STAGE + FusedCfg::C_STAGE), "reduce stages");
+
+DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uint32_t smem_base, uint32_t my_tokens,
+                                 volatile uint32_t* abort_flag, const GemmParams& wp) {
+    __shared__ __align__(8) uint64_t s_full[kReduceStages];
+    __shared__ uint32_t s_mask[kReduceStages];
+    const MoeLayout& L = p.a.L;
+    const uint32_t pieces = (L.hidden + kReducePiece - 1) / kReducePiece;
+    const uint32_t num_items = my_tokens * pieces;
+    const uint8_t* combine = p.a.base[p.a.rank] + L.off_combine;
+    const long long* topk_idx = reinterpret_cast<const long long*>(p.a.base[p.a.rank] + L.off_topk_idx);
+    const uint64_t plane = static_cast<uint64_t>(L.t_max) * L.hidden * 2;
+    if (threadIdx.x == 0) {
+        for (uint32_t i = 0; i < kReduceStages; ++i) mbar_init(&s_full[i], 1);
+        fence_mbar_init();
+    }
+    // Valid-slot masks of this CTA's tokens, computed by all threads up front: the issuing thread must not sit on
+    // global loads between items (it is on every item's critical path).
+    auto token_mask = [&](uint32_t i) {
+        const long long* idx = topk_idx + static_cast<uint64_t>(blockIdx.x + i * p.num_ctas) * L.topk;
+        uint32_t mask = 0;
+        for (uint32_t u = 0; u < L.topk; ++u) {
+            const long long e = idx[u];
+            if (e >= 0 && e < static_cast<long long>(L.experts)) mask |= 1u << u;
+        }
+        return mask;
+    };
+    constexpr uint32_t kMaskCap = FusedCfg::CD_BYTES / 4;
+    uint32_t* s_token_mask = reinterpret_cast<uint32_t*>(smem_gen + FusedCfg::kStages * (FusedCfg::R_STAGE + FusedCfg::C_STAGE));
+    for (uint32_t i = threadIdx.x; i < min(my_tokens, kMaskCap); i += kFusedThreads) s_token_mask[i] = token_mask(i);
+    __syncthreads();
+
+    auto issue = [&](uint32_t it) {   // thread 0
+        const uint32_t s = it % kReduceStages, i = it / pieces;
+        const uint32_t t = blockIdx.x + i * p.num_ctas, c0 = (it % pieces) * kReducePiece;
+        const uint32_t bytes = min(kReducePiece, L.hidden - c0) * 2;
+        const uint32_t mask = i < kMaskCap ? s_token_mask[i] : token_mask(i);
+        s_mask[s] = mask;
+        mbar_arrive_expect_tx(&s_full[s], __popc(mask) * bytes);
+        const uint32_t dst = smem_base + s * 8 * kReduceSlotBytes, bar = smem_u32(&s_full[s]);
+        const uint8_t* src = combine + (static_cast<uint64_t>(t) * L.hidden + c0) * 2;
+        for (uint32_t u = 0; u < L.topk; ++u)
+            if (mask >> u & 1) bulk_load(dst + u * kReduceSlotBytes, src + u * plane, bytes, bar);
+    };
+
+    if (threadIdx.x == 0)
+        for (uint32_t it = 0; it + 1 < kReduceStages && it < num_items; ++it) issue(it);
+    for (uint32_t it = 0; it < num_items; ++it) {
+        const uint32_t s = it % kReduceStages;
+        if (threadIdx.x == 0 && it + kReduceStages - 1 < num_items) issue(it + kReduceStages - 1);
+        const bool ok = wait_barrier(&s_full[s], (it / kReduceStages) & 1, abort_flag, 0, wp, 207, it, 0, s);
+        if (ok) {
+            const uint32_t t = blockIdx.x + (it / pieces) * p.num_ctas, c0 = (it % pieces) * kReducePiece;
+            const uint32_t width = min(kReducePiece, L.hidden - c0), c = threadIdx.x * 8;
+            if (c < width) {
+                const uint32_t mask = s_mask[s];
+                const uint8_t* src = smem_gen + s * 8 * kReduceSlotBytes + c * 2;
+                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+                for (uint32_t u = 0; u < 8; ++u) {
+                    if (mask >> u & 1) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(src + u * kReduceSlotBytes);
+                        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 f = __bfloat1622float2(b[i]);
+                            acc[2 * i] += f.x, acc[2 * i + 1] += f.y;
+                        }
+                    }
+                }
+                uint4 out;
+                __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.y) + (static_cast<uint64_t>(t) * p.ldy + c0 + c) * 2) = out;
+            }
+        }
+        if (!__syncthreads_and(ok ? 1 : 0)) break;   // the stage may be refilled; every thread leaves together on a failed wait
+    }
+}
+
 #ifdef DG_TRACE
 #define DG_FUSED_STAMP(slot_) do { if (p.trace != nullptr && lane == 0) p.trace[(blockIdx.x * 16 + warp) * 8 + (slot_)] = global_timer_ns(); } while (0)
 #else
@@ -412,12 +499,16 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
         __syncthreads();
         DG_FUSED_STAMP(3);
         if (s_comb_ok) {
-            // this CTA's tokens (blockIdx.x, + num_ctas, ...) as one flat list of 8-column items: no idle passes
-            const uint32_t chunks = L.hidden / 8;
             const uint32_t my_tokens = p.a.num_tokens > blockIdx.x ? (p.a.num_tokens - blockIdx.x + p.num_ctas - 1) / p.num_ctas : 0;
-            for (uint32_t item = threadIdx.x; item < my_tokens * chunks; item += kFusedThreads) {
-                const uint32_t t = blockIdx.x + (item / chunks) * p.num_ctas, c = (item % chunks) * 8;
-                moe_reduce_cols<false>(p.a, p.y, p.ldy, t, c, c);
+            if (L.topk <= 8) {
+                fused_reduce_bulk(p, smem_gen, smem_base, my_tokens, abort_flag, wp);
+            } else {
+                // this CTA's tokens (blockIdx.x, + num_ctas, ...) as one flat list of 8-column items
+                const uint32_t chunks = L.hidden / 8;
+                for (uint32_t item = threadIdx.x; item < my_tokens * chunks; item += kFusedThreads) {
+                    const uint32_t t = blockIdx.x + (item / chunks) * p.num_ctas, c = (item % chunks) * 8;
+                    moe_reduce_cols<false>(p.a, p.y, p.ldy, t, c, c);
+                }
             }
         }
     }

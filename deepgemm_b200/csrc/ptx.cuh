@@ -175,6 +175,14 @@ DG_DEVICE void tma_reduce_add_3d(const void* tmap, uint32_t src_smem, int32_t c0
         "r"(src_smem), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
+// Untiled bulk copy global -> this CTA's shared memory, completing `bytes` on an mbarrier of this CTA.
+// Both addresses 16-byte aligned, bytes a multiple of 16.
+DG_DEVICE void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t mbar_addr) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(mbar_addr)
+                 : "memory");
+}
+
 DG_DEVICE void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 DG_DEVICE void tma_store_wait_read() {
