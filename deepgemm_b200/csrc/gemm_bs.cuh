@@ -27,6 +27,14 @@
 
 #include "ptx.cuh"
 
+// Timing experiments only (results are wrong when set): the UMMA issuer does not wait for the shared TMEM columns.
+#ifndef DG_EXPERIMENT_SF_EVERY4
+#define DG_EXPERIMENT_SF_EVERY4 0   // per-32 scales fetched for every fourth K block only
+#endif
+#ifndef DG_EXPERIMENT_NO_OVERLAP_WAIT
+#define DG_EXPERIMENT_NO_OVERLAP_WAIT 0
+#endif
+
 namespace dg {
 
 enum GemmType : uint32_t {
@@ -90,6 +98,10 @@ __host__ __device__ inline uint32_t moe_sf_row(uint32_t row) {
 
 struct GemmParams {
     CUtensorMap tm_r, tm_c, tm_sfr, tm_sfc, tm_d;
+    // Swapped tiles with few token rows: the same C operand seen through boxes of 32 and 64 rows per CTA, so a
+    // ragged last tile of an expert does not fetch 128 rows per CTA and K block (c_small != 0 when encoded)
+    CUtensorMap tm_c_small[2];
+    uint32_t c_small;
     OperandParams r, c;
     uint32_t gemm_type;
     uint32_t m, n, k;           // logical GEMM shape (per group where grouped)
@@ -515,8 +527,8 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
     };
 
     // K-blocks covered by one packed scale word: 4 (one scale per 128 K) or 1 (one per 32 K)
-    const uint32_t sf_mask_r = p.r.gran_k == 128 ? 3 : 0, sf_shift_r = p.r.gran_k == 128 ? 2 : 0;
-    const uint32_t sf_mask_c = p.c.gran_k == 128 ? 3 : 0, sf_shift_c = p.c.gran_k == 128 ? 2 : 0;
+    const uint32_t sf_mask_r = (p.r.gran_k == 128 || DG_EXPERIMENT_SF_EVERY4 != 0) ? 3 : 0, sf_shift_r = p.r.gran_k == 128 ? 2 : 0;
+    const uint32_t sf_mask_c = (p.c.gran_k == 128 || DG_EXPERIMENT_SF_EVERY4 != 0) ? 3 : 0, sf_shift_c = p.c.gran_k == 128 ? 2 : 0;
 
     // Shared by the role loops: smem stage / phase bookkeeping and the schedule walk.
     uint32_t stage = 0, phase = 0;
@@ -529,10 +541,12 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
     bool ok = true;
     uint32_t acc_iter = 0;   // accumulator tiles handled so far by this role
 
-    if (warp == 0) {
-        // ============================================================ TMA producer
-        // The whole warp runs the loop (uniform control flow keeps addresses and coordinates in
-        // uniform registers); one elected lane issues the copies.
+    if (warp == 0 || warp == 3) {
+        // ============================================================ TMA producers
+        // Warp 0 fetches the operand tiles, warp 3 the scale factors: with per-32 scales a K block takes four
+        // copies, more than one issuing thread sustains.  The whole warp runs the loop (uniform control flow keeps
+        // addresses and coordinates in uniform registers); one elected lane issues the copies.
+        const bool sf_role = warp == 3;
         const uint32_t full_bar0 = leader_addr(&bars->full[0]);
         const uint32_t stage_tx_bytes = p.r.tx_bytes + p.c.tx_bytes;
         const uint32_t r_boxes = p.r.num_boxes, r_box_bytes = p.r.box_bytes, r_box_mn = p.r.box_mn;
@@ -565,6 +579,15 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                 r_mn += cta_rank * 128, sfr_mn += cta_rank * 128;
                 c_mn += cta_rank * ((kSwap ? tc.rows : BN) / kCtas);
 
+                const CUtensorMap* tm_c_tile = &p.tm_c;
+                uint32_t tile_tx_bytes = stage_tx_bytes;
+                if constexpr (kSwap) {
+                    if (p.c_small != 0) {
+                        const uint32_t per_cta = tc.rows / kCtas;
+                        if (per_cta <= 32) tm_c_tile = &p.tm_c_small[0], tile_tx_bytes = p.r.tx_bytes + 32 * 128;
+                        else if (per_cta <= 64) tm_c_tile = &p.tm_c_small[1], tile_tx_bytes = p.r.tx_bytes + 64 * 128;
+                    }
+                }
                 const uint32_t num_kb = max(1u, (tc.k_len + 127u) / 128u);
                 for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
                     DG_TRACE_AT(0, kb);
@@ -572,8 +595,8 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                                       acc_iter, kb, stage);
                     if (!ok) break;
                     DG_TRACE_AT(1, kb);
-                    if (elect_one()) {
-                        // Scale factors first: the transposer works while the operand tiles are in flight
+                    if (sf_role) {
+                      if (elect_one()) {
                         uint32_t sf_bytes = 0;
                         const uint32_t sf_bar = smem_u32(&bars->sf_full[stage]);
                         if ((kb & sf_mask_r) == 0) {
@@ -589,9 +612,11 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                             sf_bytes += Cfg::SFC_STAGE;
                         }
                         mbar_arrive_expect_tx(&bars->sf_full[stage], sf_bytes);
+                      }
+                    } else if (elect_one()) {
                         // Operand tiles land on the leader's barrier (both CTAs of a pair feed one UMMA)
                         const uint32_t full_bar = full_bar0 + stage * 8;
-                        mbar_arrive_expect_tx_cluster(full_bar, stage_tx_bytes);
+                        mbar_arrive_expect_tx_cluster(full_bar, tile_tx_bytes);
                         const uint32_t kr = r_k + kb * 128, kc = c_k + kb * 128;
                         for (uint32_t b = 0; b < r_boxes; ++b) {
                             const uint32_t dst = smem_r + stage * Cfg::R_STAGE + b * r_box_bytes;
@@ -603,7 +628,7 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                             const uint32_t dst = smem_c + stage * Cfg::C_STAGE + b * c_box_bytes;
                             const uint32_t mn = c_mn + b * c_box_mn;
                             if (c_mn_major) tma_load_2d<kPair>(dst, &p.tm_c, full_bar, mn, kc);
-                            else            tma_load_2d<kPair>(dst, &p.tm_c, full_bar, kc, mn);
+                            else            tma_load_2d<kPair>(dst, tm_c_tile, full_bar, kc, mn);
                         }
                     }
                     __syncwarp();
@@ -637,7 +662,7 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                     ok = wait_barrier(&bars->tmem_empty[acc], acc_phase ^ 1, abort_flag, peer_abort, p,
                                       kSiteMmaTmemEmpty, acc_iter, 0, acc);
                     if (!ok) break;
-                    if (Cfg::kOverlap > 0 && acc_iter > 0) {
+                    if (Cfg::kOverlap > 0 && acc_iter > 0 && !DG_EXPERIMENT_NO_OVERLAP_WAIT) {
                         // The previous tile's epilogue must have drained the columns both stages share
                         const uint32_t prev = acc_iter - 1;
                         ok = wait_barrier(&bars->overlap[prev & 1], (prev >> 1) & 1, abort_flag, peer_abort, p,
@@ -657,11 +682,11 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                         tc_fence_after();
                         if (elect_one()) {
                             // Fresh scale factors: shared memory (already in 32x4 order) -> TMEM
-                            if ((kb & sf_mask_r) == 0) {
+                            if ((kb & sf_mask_r) == 0 || (DG_EXPERIMENT_SF_EVERY4 == 2 && p.r.gran_k != 128)) {
                                 const uint32_t a = smem_sfr + stage * Cfg::SFR_STAGE;
                                 utccp_32x128b_warpx4<kCtas>(sfr_tmem, sf_desc_hi | (a >> 4));
                             }
-                            if ((kb & sf_mask_c) == 0) {
+                            if ((kb & sf_mask_c) == 0 || (DG_EXPERIMENT_SF_EVERY4 == 2 && p.c.gran_k != 128)) {
 #pragma unroll
                                 for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i) {
                                     const uint32_t a = smem_sfc + stage * Cfg::SFC_STAGE + i * 512;

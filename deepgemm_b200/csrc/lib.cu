@@ -453,6 +453,16 @@ static int run_gemm(const dg_gemm_args& a, int epi, const dg::MoeEpilogueParams*
     dg::GemmParams p;
     memset(&p, 0, sizeof(p));
     p.tm_r = plan_r.tm, p.tm_c = plan_c.tm, p.tm_sfr = plan_r.tm_sf, p.tm_sfc = plan_c.tm_sf;
+    if (t.swap && grouped && !op_c.mn_major && op_c.dtype == DG_E4M3 && c_rows_per_cta == 128) {
+        // narrower views of the token operand for ragged tiles
+        for (int i = 0; i < 2; ++i) {
+            OperandPlan small;
+            rc = plan_operand(a, op_c, /*is_a=*/true, i == 0 ? 32 : 64, sfc_rows, &small);
+            if (rc != DG_OK) return rc;
+            p.tm_c_small[i] = small.tm;
+        }
+        p.c_small = 1;
+    }
     p.r = plan_r.params, p.c = plan_c.params;
     p.rows_per_group_r = plan_r.rows_per_group, p.rows_per_group_c = plan_c.rows_per_group;
     p.k_rows_per_group_r = plan_r.k_rows_per_group, p.k_rows_per_group_c = plan_c.k_rows_per_group;
@@ -606,6 +616,12 @@ static int launch_moe_fused(const dg_moe_args& m, const dg::MoeArgs& a, int num_
         rc = plan_operand(g[i], g[i].a, /*is_a=*/true, 128, 256, &act);
         if (rc != DG_OK) return rc;
         p.tm_w[i] = w.tm, p.tm_wsf[i] = w.tm_sf, p.tm_act[i] = act.tm, p.tm_actsf[i] = act.tm_sf;
+        for (int j = 0; j < 2; ++j) {
+            OperandPlan small;
+            rc = plan_operand(g[i], g[i].a, /*is_a=*/true, j == 0 ? 32 : 64, 256, &small);
+            if (rc != DG_OK) return rc;
+            p.tm_act_small[i][j] = small.tm;
+        }
     }
     p.y = static_cast<__nv_bfloat16*>(m.y), p.ldy = m.ldy;
     p.num_ctas = static_cast<uint32_t>(num_sms) / 2 * 2;

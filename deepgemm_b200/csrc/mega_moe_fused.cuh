@@ -22,6 +22,7 @@ constexpr uint32_t kFusedThreads = 384;
 
 struct MoeFusedParams {
     CUtensorMap tm_w[2], tm_wsf[2], tm_act[2], tm_actsf[2];   // [0]: first GEMM (W13, pool tokens), [1]: second (W2, activations)
+    CUtensorMap tm_act_small[2][2];   // [gemm][0: 32, 1: 64 token rows per CTA]: ragged tiles fetch fewer rows
     MoeArgs a;
     MoeEpilogueParams e;
     __nv_bfloat16* y;
@@ -234,7 +235,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             prefetch_tmap(&p.tm_w[i]), prefetch_tmap(&p.tm_wsf[i]), prefetch_tmap(&p.tm_act[i]), prefetch_tmap(&p.tm_actsf[i]);
         }
         for (uint32_t i = 0; i < kStages; ++i) {
-            mbar_init(&bars->full[i], 2);    // both CTAs' producers; every copy of the stage lands here
+            mbar_init(&bars->full[i], 4);    // both CTAs' operand and scale producers; every copy of the stage lands here
             mbar_init(&bars->empty[i], 1);   // UMMA commit
         }
         for (uint32_t i = 0; i < 2; ++i) {
@@ -305,8 +306,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     uint32_t acc_iter = 0;
     FusedTile tc;
 
-    if (warp == 0) {
-        // ============================================================ TMA producer
+    if (warp == 0 || warp == 3) {
+        // ============================================================ TMA producers: warp 0 operand tiles, warp 3 scale factors
+        const bool sf_role = warp == 3;
         const uint32_t full_bar0 = map_to_cta(smem_u32(&bars->full[0]), 0);
         for (uint32_t slot = unit; slot < num_slots && ok; slot += num_units) {
             if (!fused_slot_to_tile(table, num_tiles, n1, n2, p.lag, slot, tc)) continue;
@@ -327,16 +329,23 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             const uint32_t c_mn = tc.row0 + cta_rank * (tc.rows / 2);
             const uint32_t sfc_mn = tc.row0;
             const uint32_t num_kb = pk;
+            const uint32_t per_cta = tc.rows / 2;
+            const CUtensorMap* tm_act = per_cta <= 32 ? &p.tm_act_small[k][0] : per_cta <= 64 ? &p.tm_act_small[k][1] : &p.tm_act[k];
+            const uint32_t tx_bytes = Cfg::R_STAGE / 2 + (per_cta <= 32 ? 32u : per_cta <= 64 ? 64u : 128u) * 128u;   // FP4 weights count packed bytes
             for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
                 ok = wait_barrier(&bars->empty[stage], phase ^ 1, abort_flag, peer_abort, wp, kSiteProducerEmpty, acc_iter, kb, stage);
                 if (!ok) break;
                 if (elect_one()) {
                     const uint32_t full_bar = full_bar0 + stage * 8;
-                    mbar_arrive_expect_tx_cluster(full_bar, Cfg::kTxBytes);
-                    tma_load_2d<true>(smem_sfr + stage * Cfg::SFR_STAGE, &p.tm_wsf[k], full_bar, sfr_mn, sfr_k + kb);
-                    tma_load_2d<true>(smem_sfc + stage * Cfg::SFC_STAGE, &p.tm_actsf[k], full_bar, sfc_mn, kb);
-                    tma_load_2d<true>(smem_r + stage * Cfg::R_STAGE, &p.tm_w[k], full_bar, kb * 128, r_mn);
-                    tma_load_2d<true>(smem_c + stage * Cfg::C_STAGE, &p.tm_act[k], full_bar, kb * 128, c_mn);
+                    if (sf_role) {
+                        mbar_arrive_expect_tx_cluster(full_bar, Cfg::SFR_STAGE + Cfg::SFC_STAGE);
+                        tma_load_2d<true>(smem_sfr + stage * Cfg::SFR_STAGE, &p.tm_wsf[k], full_bar, sfr_mn, sfr_k + kb);
+                        tma_load_2d<true>(smem_sfc + stage * Cfg::SFC_STAGE, &p.tm_actsf[k], full_bar, sfc_mn, kb);
+                    } else {
+                        mbar_arrive_expect_tx_cluster(full_bar, tx_bytes);
+                        tma_load_2d<true>(smem_r + stage * Cfg::R_STAGE, &p.tm_w[k], full_bar, kb * 128, r_mn);
+                        tma_load_2d<true>(smem_c + stage * Cfg::C_STAGE, tm_act, full_bar, kb * 128, c_mn);
+                    }
                 }
                 __syncwarp();
             }
@@ -474,9 +483,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
         }
         __threadfence_system();   // pushes to the source ranks are out before the final barriers
     } else if (ok) {
-        // ============================================================ pull warps (2, 3, 8..11): fill the pool in pool order
-        const uint32_t pw = warp < 4 ? warp - 2 : warp - 6;   // 0..5
-        moe_pull_rows(p.a, s_prefix, blockIdx.x * 6 + pw, p.num_ctas * 6, lane, pulled);
+        // ============================================================ pull warps (2, 8..11): fill the pool in pool order
+        const uint32_t pw = warp == 2 ? 0 : warp - 7;   // 0..4
+        moe_pull_rows(p.a, s_prefix, blockIdx.x * 5 + pw, p.num_ctas * 5, lane, pulled);
     }
 
     DG_FUSED_STAMP(2);
