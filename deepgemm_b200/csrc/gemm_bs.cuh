@@ -383,31 +383,36 @@ DG_DEVICE bool wait_barrier(uint64_t* bar, uint32_t parity, volatile uint32_t* a
 // SwiGLU on the BF16-rounded gate / up pairs, times the route weight, per-32 UE8M0 E4M3 requantisation, stored
 // as rows of the second GEMM's A operand.  m0: first pool row of the tile; n0: first interleaved weight row of
 // this CTA; wtab: the tile's route weights.
-DG_DEVICE void moe_l1_chunk(const MoeEpilogueParams& m, const uint8_t* stage, uint32_t pitch, const float* wtab,
-                            uint32_t q, uint32_t lane, uint32_t ch, uint32_t chunk_rows, uint32_t m0, uint32_t n0) {
+template <bool kFast, bool kClamp>
+DG_DEVICE void moe_l1_chunk_impl(const MoeEpilogueParams& m, const uint8_t* stage, uint32_t pitch, const float* wtab,
+                                 uint32_t q, uint32_t lane, uint32_t ch, uint32_t chunk_rows, uint32_t m0, uint32_t n0) {
     // A warp takes 8 tokens; lane = (token, 32-output group g, half): 16 outputs per
     // thread = 32 interleaved rows laid out as 2 x [8 gate | 8 up] (the weights come
     // interleaved in blocks of 8 rows); the two halves of a group share their amax.
     const uint32_t t = q * 8 + (lane >> 2), g = (lane >> 1) & 1, half = lane & 1;
     const float w = wtab[min(ch * 32 + t, 255u)];
+    const float clamp = m.clamp;
     const uint4* src = reinterpret_cast<const uint4*>(stage + t * pitch + g * 128 + half * 64);
+    const uint4 raw[4] = {src[0], src[1], src[2], src[3]};   // [8 gate | 8 up] x 2, BF16
     float act[16];
     float amax = 0.f;
 #pragma unroll
     for (uint32_t blk = 0; blk < 2; ++blk) {
-        const uint4 gv = src[2 * blk], uv = src[2 * blk + 1];
-        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
-        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&raw[2 * blk]);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&raw[2 * blk + 1]);
 #pragma unroll
         for (uint32_t j = 0; j < 4; ++j) {
             float2 gf = __bfloat1622float2(g2[j]), uf = __bfloat1622float2(u2[j]);
-            gf.x = fminf(gf.x, m.clamp), gf.y = fminf(gf.y, m.clamp);
-            uf.x = fminf(fmaxf(uf.x, -m.clamp), m.clamp);
-            uf.y = fminf(fmaxf(uf.y, -m.clamp), m.clamp);
+            if (kClamp) {
+                gf.x = fminf(gf.x, clamp), gf.y = fminf(gf.y, clamp);
+                uf.x = fminf(fmaxf(uf.x, -clamp), clamp);
+                uf.y = fminf(fmaxf(uf.y, -clamp), clamp);
+            }
             float sx, sy;
-            if (m.fast_math) {
-                sx = gf.x * __frcp_rn(1.0f + __expf(-gf.x));
-                sy = gf.y * __frcp_rn(1.0f + __expf(-gf.y));
+            if (kFast) {
+                // x * sigmoid(x) with the approximate exponential and reciprocal units
+                sx = __fdividef(gf.x, 1.0f + __expf(-gf.x));
+                sy = __fdividef(gf.y, 1.0f + __expf(-gf.y));
             } else {
                 sx = gf.x / (1.0f + expf(-gf.x));
                 sy = gf.y / (1.0f + expf(-gf.y));
@@ -441,6 +446,18 @@ DG_DEVICE void moe_l1_chunk(const MoeEpilogueParams& m, const uint8_t* stage, ui
         if (half == 0)
             m.l2_sf[(static_cast<uint64_t>(kgroup / 4) * m.pool_rows + moe_sf_row(row)) * 4 + (kgroup & 3)] =
                 static_cast<uint8_t>(e);
+    }
+}
+
+DG_DEVICE void moe_l1_chunk(const MoeEpilogueParams& m, const uint8_t* stage, uint32_t pitch, const float* wtab,
+                            uint32_t q, uint32_t lane, uint32_t ch, uint32_t chunk_rows, uint32_t m0, uint32_t n0) {
+    const bool clamp = m.clamp < 3.0e38f;   // +inf: no clamp
+    if (m.fast_math) {
+        if (clamp) moe_l1_chunk_impl<true, true>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
+        else       moe_l1_chunk_impl<true, false>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
+    } else {
+        if (clamp) moe_l1_chunk_impl<false, true>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
+        else       moe_l1_chunk_impl<false, false>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
     }
 }
 

@@ -198,9 +198,17 @@ DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uin
 }
 
 #ifdef DG_TRACE
+// Cycles spent in a wait, summed per warp into trace slots 5..7 (timing studies only)
+#define DG_FUSED_TIMED(slot_, stmt_) do { const long long t0_ = clock64(); stmt_; wait_cycles[(slot_) - 5] += clock64() - t0_; } while (0)
+#define DG_FUSED_FLUSH() do { if (p.trace != nullptr && lane == 0) { for (int i_ = 0; i_ < 3; ++i_) p.trace[(blockIdx.x * 16 + warp) * 8 + 5 + i_] = wait_cycles[i_]; \
+    if (warp == 4) for (int i_ = 0; i_ < 8; ++i_) p.trace[(blockIdx.x * 16 + 12) * 8 + i_] = epi_cycles[i_]; } } while (0)
+#define DG_EPI_TIMED(slot_, stmt_) do { const long long t0_ = clock64(); stmt_; epi_cycles[slot_] += clock64() - t0_; } while (0)
 #define DG_FUSED_STAMP(slot_) do { if (p.trace != nullptr && lane == 0) p.trace[(blockIdx.x * 16 + warp) * 8 + (slot_)] = global_timer_ns(); } while (0)
 #else
 #define DG_FUSED_STAMP(slot_) do { } while (0)
+#define DG_FUSED_TIMED(slot_, stmt_) do { stmt_; } while (0)
+#define DG_FUSED_FLUSH() do { } while (0)
+#define DG_EPI_TIMED(slot_, stmt_) do { stmt_; } while (0)
 #endif
 
 __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const __grid_constant__ MoeFusedParams p) {
@@ -305,6 +313,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     };
     uint32_t acc_iter = 0;
     FusedTile tc;
+    long long wait_cycles[3] = {0, 0, 0};
+    long long epi_cycles[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    (void)wait_cycles, (void)epi_cycles;
 
     if (warp == 0 || warp == 3) {
         // ============================================================ TMA producers: warp 0 operand tiles, warp 3 scale factors
@@ -314,10 +325,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             if (!fused_slot_to_tile(table, num_tiles, n1, n2, p.lag, slot, tc)) continue;
             // Data dependencies: pool rows pulled (first GEMM) / activations written (second GEMM)
             if (tc.kind == 0) {
-                ok = fused_wait_counter(pulled + tc.row0 / 128, tc.valid0, abort_flag, p.a, 203, tc.tile);
-                if (ok && tc.rows > 128) ok = fused_wait_counter(pulled + tc.row0 / 128 + 1, tc.valid1, abort_flag, p.a, 203, tc.tile);
+                DG_FUSED_TIMED(5, ok = fused_wait_counter(pulled + tc.row0 / 128, tc.valid0, abort_flag, p.a, 203, tc.tile));
+                if (ok && tc.rows > 128) DG_FUSED_TIMED(5, ok = fused_wait_counter(pulled + tc.row0 / 128 + 1, tc.valid1, abort_flag, p.a, 203, tc.tile));
             } else {
-                ok = fused_wait_counter(l1_done + tc.tile, n1 * 8, abort_flag, p.a, 204, tc.tile);
+                DG_FUSED_TIMED(7, ok = fused_wait_counter(l1_done + tc.tile, n1 * 8, abort_flag, p.a, 204, tc.tile));
             }
             if (!ok) break;
             asm volatile("fence.proxy.async;" ::: "memory");   // the rows were written through the generic proxy
@@ -333,7 +344,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             const CUtensorMap* tm_act = per_cta <= 32 ? &p.tm_act_small[k][0] : per_cta <= 64 ? &p.tm_act_small[k][1] : &p.tm_act[k];
             const uint32_t tx_bytes = Cfg::R_STAGE / 2 + (per_cta <= 32 ? 32u : per_cta <= 64 ? 64u : 128u) * 128u;   // FP4 weights count packed bytes
             for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
-                ok = wait_barrier(&bars->empty[stage], phase ^ 1, abort_flag, peer_abort, wp, kSiteProducerEmpty, acc_iter, kb, stage);
+                DG_FUSED_TIMED(6, ok = wait_barrier(&bars->empty[stage], phase ^ 1, abort_flag, peer_abort, wp, kSiteProducerEmpty, acc_iter, kb, stage));
                 if (!ok) break;
                 if (elect_one()) {
                     const uint32_t full_bar = full_bar0 + stage * 8;
@@ -363,10 +374,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             for (uint32_t slot = unit; slot < num_slots && ok; slot += num_units) {
                 if (!fused_slot_to_tile(table, num_tiles, n1, n2, p.lag, slot, tc)) continue;
                 const uint32_t acc = acc_iter & 1, acc_phase = (acc_iter >> 1) & 1;
-                ok = wait_barrier(&bars->tmem_empty[acc], acc_phase ^ 1, abort_flag, peer_abort, wp, kSiteMmaTmemEmpty, acc_iter, 0, acc);
+                DG_FUSED_TIMED(5, ok = wait_barrier(&bars->tmem_empty[acc], acc_phase ^ 1, abort_flag, peer_abort, wp, kSiteMmaTmemEmpty, acc_iter, 0, acc));
                 if (ok && acc_iter > 0) {
                     const uint32_t prev = acc_iter - 1;
-                    ok = wait_barrier(&bars->overlap[prev & 1], (prev >> 1) & 1, abort_flag, peer_abort, wp, kSiteMmaOverlap, acc_iter, 0, acc);
+                    DG_FUSED_TIMED(7, ok = wait_barrier(&bars->overlap[prev & 1], (prev >> 1) & 1, abort_flag, peer_abort, wp, kSiteMmaOverlap, acc_iter, 0, acc));
                 }
                 if (!ok) break;
                 tc_fence_after();
@@ -374,7 +385,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                 const uint32_t idesc_tile = idesc_with_n(idesc_base, tc.rows);
                 const uint32_t num_kb = (tc.kind == 0 ? L.hidden : L.inter) / 128;
                 for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
-                    ok = wait_barrier(&bars->full[stage], phase, abort_flag, peer_abort, wp, kSiteMmaFull, acc_iter, kb, stage);
+                    DG_FUSED_TIMED(6, ok = wait_barrier(&bars->full[stage], phase, abort_flag, peer_abort, wp, kSiteMmaFull, acc_iter, kb, stage));
                     if (!ok) break;
                     tc_fence_after();
                     if (elect_one()) {
@@ -409,13 +420,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             // Per-token data of the tile, fetched while its UMMAs run.  The reading threads themselves must have
             // seen the counters that say the pool rows (and, for the second GEMM, the routing metadata) are there.
             if (tc.kind == 0) {
-                ok = fused_wait_counter(pulled + tc.row0 / 128, tc.valid0, abort_flag, p.a, 207, tc.tile);
-                if (ok && tc.rows > 128) ok = fused_wait_counter(pulled + tc.row0 / 128 + 1, tc.valid1, abort_flag, p.a, 207, tc.tile);
+                DG_FUSED_TIMED(7, ok = fused_wait_counter(pulled + tc.row0 / 128, tc.valid0, abort_flag, p.a, 207, tc.tile));
+                if (ok && tc.rows > 128) DG_FUSED_TIMED(7, ok = fused_wait_counter(pulled + tc.row0 / 128 + 1, tc.valid1, abort_flag, p.a, 207, tc.tile));
             } else {
-                ok = fused_wait_counter(l1_done + tc.tile, n1 * 8, abort_flag, p.a, 208, tc.tile);
+                DG_FUSED_TIMED(7, ok = fused_wait_counter(l1_done + tc.tile, n1 * 8, abort_flag, p.a, 208, tc.tile));
             }
             if (!ok) break;
             uint64_t* ttab = reinterpret_cast<uint64_t*>(smem_gen + (smem_cd - smem_base) + Cfg::TABLE_OFF) + acc * 256;
+            DG_EPI_TIMED(0,
             for (uint32_t tok = q * 32 + lane; tok < tc.rows; tok += 128) {
                 const uint32_t row = tc.row0 + tok;
                 if (tc.kind == 0) {
@@ -432,7 +444,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                     ttab[tok] = dst;
                 }
             }
-            ok = wait_barrier(&bars->tmem_full[acc], acc_phase, abort_flag, peer_abort, wp, kSiteEpilogueTmemFull, acc_iter, 0, acc);
+            __syncwarp(););
+            DG_FUSED_TIMED(5, ok = wait_barrier(&bars->tmem_full[acc], acc_phase, abort_flag, peer_abort, wp, kSiteEpilogueTmemFull, acc_iter, 0, acc));
             if (!ok) break;
             tc_fence_after();
             const uint32_t t_acc = tmem_base + acc * Cfg::kAccStride + ((q * 32) << 16);
@@ -443,8 +456,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             for (uint32_t i = 0; i < num_chunks && ok; ++i) {
                 const uint32_t ch = reverse ? num_chunks - 1 - i : i;
                 uint32_t v[32];
-                tmem_ld_32x32b_x32(t_acc + ch * 32, v);
-                tmem_ld_wait();
+                DG_EPI_TIMED(1, tmem_ld_32x32b_x32(t_acc + ch * 32, v); tmem_ld_wait(););
                 if (i == 0 || i + 1 == num_chunks) {
                     tc_fence_before();
                     __syncwarp();
@@ -454,30 +466,35 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                     }
                 }
                 uint8_t* stage_gen = smem_gen + (smem_cd - smem_base) + moe_buf * 32 * Cfg::PITCH;
-#pragma unroll
+                DG_EPI_TIMED(2,
+                _Pragma("unroll")
                 for (uint32_t t = 0; t < 32; ++t)
                     *reinterpret_cast<__nv_bfloat16*>(stage_gen + t * Cfg::PITCH + (q * 32 + lane) * 2) =
                         __float2bfloat16_rn(__uint_as_float(v[t]));
-                __syncwarp();
+                __syncwarp(););
                 if (lane == 0) mbar_arrive(&bars->epi_sync[moe_buf]);
-                ok = wait_barrier(&bars->epi_sync[moe_buf], (moe_chunks >> 1) & 1, abort_flag, peer_abort, wp, kSiteEpilogueSync,
-                                  acc_iter, ch, moe_buf);
+                DG_FUSED_TIMED(6, ok = wait_barrier(&bars->epi_sync[moe_buf], (moe_chunks >> 1) & 1, abort_flag, peer_abort, wp, kSiteEpilogueSync,
+                                  acc_iter, ch, moe_buf));
                 ++moe_chunks;
                 if (!ok) break;
                 const uint32_t chunk_rows = min(32u, tc.rows - ch * 32);
                 if (tc.kind == 0)
-                    moe_l1_chunk(p.e, stage_gen, Cfg::PITCH, reinterpret_cast<const float*>(ttab), q, lane, ch, chunk_rows, tc.row0, n0);
+                    DG_EPI_TIMED(3, moe_l1_chunk(p.e, stage_gen, Cfg::PITCH, reinterpret_cast<const float*>(ttab), q, lane, ch, chunk_rows, tc.row0, n0); __syncwarp(););
                 else
-                    moe_l2_chunk(stage_gen, Cfg::PITCH, ttab, q * 32 + lane, ch, chunk_rows, n0);
+                    DG_EPI_TIMED(4, moe_l2_chunk(stage_gen, Cfg::PITCH, ttab, q * 32 + lane, ch, chunk_rows, n0); __syncwarp(););
                 moe_buf ^= 1;
             }
             if (!ok) break;
             if (tc.kind == 0) {
                 // The tile's activations are read by TMA in other CTAs once all of its n-tiles have reported
+                DG_EPI_TIMED(5,
                 asm volatile("fence.proxy.async;" ::: "memory");
                 __threadfence();
                 __syncwarp();
-                if (lane == 0) atomicAdd(l1_done + tc.tile, 1u);
+                if (lane == 0) atomicAdd(l1_done + tc.tile, 1u););
+                DG_EPI_TIMED(6, ;);
+            } else {
+                DG_EPI_TIMED(7, ;);
             }
             ++acc_iter;
         }
@@ -488,6 +505,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
         moe_pull_rows(p.a, s_prefix, blockIdx.x * 5 + pw, p.num_ctas * 5, lane, pulled);
     }
 
+    DG_FUSED_FLUSH();
     DG_FUSED_STAMP(2);
     // ---------------------------------------------------------------- combine: everyone has pushed, then reduce
     bool ok2 = fused_grid_barrier(work + MoeFusedWork::kGridSync, (2 * fused_calls + 2) * p.num_ctas, abort_flag, p.a, 205);
