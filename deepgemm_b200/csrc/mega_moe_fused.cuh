@@ -110,16 +110,25 @@ DG_DEVICE bool fused_grid_barrier(uint32_t* counter, uint32_t target, volatile u
     return s_ok != 0;
 }
 
-// Top-k reduction of this CTA's tokens (blockIdx.x, + num_ctas, ...) with the combine rows staged through shared
+// Top-k reduction of this CTA's share of the tokens with the combine rows staged through shared
 // memory by bulk copies: one item = one token x one piece of kReducePiece columns x all of its valid slots (up to 8
 // rows of 6 KB), kReduceStages items in flight per CTA, so the memory-level parallelism does not depend on the
 // number of threads.  Thread 0 issues, all threads sum (slot order, FP32) and store BF16.  The kernel's operand
 // stages are free by now (all roles have left their loops and the grid barrier has passed).
-constexpr uint32_t kReducePiece = kFusedThreads * 8, kReduceStages = 4, kReduceSlotBytes = kReducePiece * 2;
+#ifndef DG_REDUCE_PIECE
+#define DG_REDUCE_PIECE (kFusedThreads * 8)
+#define DG_REDUCE_STAGES 4
+#endif
+constexpr uint32_t kReducePiece = DG_REDUCE_PIECE, kReduceStages = DG_REDUCE_STAGES, kReduceSlotBytes = kReducePiece * 2;
+static_assert(kReducePiece <= kFusedThreads * 8 && kReducePiece % 8 == 0, "one 8-column group per thread");
 static_assert(kReduceStages * 8 * kReduceSlotBytes <= FusedCfg::kStages * (FusedCfg::R_STAGE + FusedCfg::C_STAGE), "reduce stages");
 
-DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uint32_t smem_base, uint32_t my_tokens,
+DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uint32_t smem_base,
                                  volatile uint32_t* abort_flag, const GemmParams& wp) {
+    // A contiguous run of tokens per CTA: at any moment the CTAs read rows far apart from one another
+    const uint32_t per_cta = (p.a.num_tokens + p.num_ctas - 1) / p.num_ctas;
+    const uint32_t first_token = min(blockIdx.x * per_cta, p.a.num_tokens);
+    const uint32_t my_tokens = min(per_cta, p.a.num_tokens - first_token);
     __shared__ __align__(8) uint64_t s_full[kReduceStages];
     __shared__ uint32_t s_mask[kReduceStages];
     const MoeLayout& L = p.a.L;
@@ -135,7 +144,7 @@ DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uin
     // Valid-slot masks of this CTA's tokens, computed by all threads up front: the issuing thread must not sit on
     // global loads between items (it is on every item's critical path).
     auto token_mask = [&](uint32_t i) {
-        const long long* idx = topk_idx + static_cast<uint64_t>(blockIdx.x + i * p.num_ctas) * L.topk;
+        const long long* idx = topk_idx + static_cast<uint64_t>(first_token + i) * L.topk;
         uint32_t mask = 0;
         for (uint32_t u = 0; u < L.topk; ++u) {
             const long long e = idx[u];
@@ -148,27 +157,32 @@ DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uin
     for (uint32_t i = threadIdx.x; i < min(my_tokens, kMaskCap); i += kFusedThreads) s_token_mask[i] = token_mask(i);
     __syncthreads();
 
-    auto issue = [&](uint32_t it) {   // thread 0
-        const uint32_t s = it % kReduceStages, i = it / pieces;
-        const uint32_t t = blockIdx.x + i * p.num_ctas, c0 = (it % pieces) * kReducePiece;
+    // Lane 0 of warp u issues slot u's copy (eight issuing threads: one thread issuing all eight copies of an item
+    // spends longer on that than the copies take); thread 0 also posts the expected byte count.
+    auto issue = [&](uint32_t it) {   // threads 0, 32, ..., 224
+        const uint32_t s = it % kReduceStages, i = it / pieces, u = threadIdx.x / 32;
+        const uint32_t t = first_token + i, c0 = (it % pieces) * kReducePiece;
         const uint32_t bytes = min(kReducePiece, L.hidden - c0) * 2;
         const uint32_t mask = i < kMaskCap ? s_token_mask[i] : token_mask(i);
-        s_mask[s] = mask;
-        mbar_arrive_expect_tx(&s_full[s], __popc(mask) * bytes);
-        const uint32_t dst = smem_base + s * 8 * kReduceSlotBytes, bar = smem_u32(&s_full[s]);
-        const uint8_t* src = combine + (static_cast<uint64_t>(t) * L.hidden + c0) * 2;
-        for (uint32_t u = 0; u < L.topk; ++u)
-            if (mask >> u & 1) bulk_load(dst + u * kReduceSlotBytes, src + u * plane, bytes, bar);
+        if (threadIdx.x == 0) {
+            s_mask[s] = mask;
+            mbar_arrive_expect_tx(&s_full[s], __popc(mask) * bytes);
+        }
+        if (mask >> u & 1) {
+            const uint8_t* src = combine + (static_cast<uint64_t>(t) * L.hidden + c0) * 2;
+            bulk_load(smem_base + (s * 8 + u) * kReduceSlotBytes, src + u * plane, bytes, smem_u32(&s_full[s]));
+        }
     };
+    const bool issuer = threadIdx.x % 32 == 0 && threadIdx.x / 32 < 8;
 
-    if (threadIdx.x == 0)
+    if (issuer)
         for (uint32_t it = 0; it + 1 < kReduceStages && it < num_items; ++it) issue(it);
     for (uint32_t it = 0; it < num_items; ++it) {
         const uint32_t s = it % kReduceStages;
-        if (threadIdx.x == 0 && it + kReduceStages - 1 < num_items) issue(it + kReduceStages - 1);
+        if (issuer && it + kReduceStages - 1 < num_items) issue(it + kReduceStages - 1);
         const bool ok = wait_barrier(&s_full[s], (it / kReduceStages) & 1, abort_flag, 0, wp, 207, it, 0, s);
         if (ok) {
-            const uint32_t t = blockIdx.x + (it / pieces) * p.num_ctas, c0 = (it % pieces) * kReducePiece;
+            const uint32_t t = first_token + it / pieces, c0 = (it % pieces) * kReducePiece;
             const uint32_t width = min(kReducePiece, L.hidden - c0), c = threadIdx.x * 8;
             if (c < width) {
                 const uint32_t mask = s_mask[s];
@@ -528,7 +542,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
         if (s_comb_ok) {
             const uint32_t my_tokens = p.a.num_tokens > blockIdx.x ? (p.a.num_tokens - blockIdx.x + p.num_ctas - 1) / p.num_ctas : 0;
             if (L.topk <= 8) {
-                fused_reduce_bulk(p, smem_gen, smem_base, my_tokens, abort_flag, wp);
+                fused_reduce_bulk(p, smem_gen, smem_base, abort_flag, wp);
             } else {
                 // this CTA's tokens (blockIdx.x, + num_ctas, ...) as one flat list of 8-column items
                 const uint32_t chunks = L.hidden / 8;
