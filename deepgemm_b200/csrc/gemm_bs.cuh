@@ -282,7 +282,7 @@ struct GemmConfig {
     static_assert(!(kSwap && kCdF32), "the transposed epilogue writes BF16 only");
     static_assert(BN % 16 == 0 && BN >= 32 && BN <= 256, "UMMA N");
 
-    static constexpr uint32_t kThreads = 256;
+    static constexpr uint32_t kThreads = 288;   // warps 0-3: R copies, UMMA, scale transposer, scale copies; 4-7: epilogue; 8: C copies
     static constexpr uint32_t BLOCK_K = 128;
     static constexpr uint32_t R_ROWS = 128;
     static constexpr uint32_t C_ROWS_PER_CTA = BN / kCtas;
@@ -478,7 +478,7 @@ DG_DEVICE void moe_l2_chunk(const uint8_t* stage, uint32_t pitch, const uint64_t
 }
 
 template <class Cfg>
-__global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__ GemmParams p) {
+__global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__ GemmParams p) {
     constexpr int kCtas = Cfg::kCtas;
     constexpr uint32_t BN = Cfg::BN;
     constexpr uint32_t kStages = Cfg::kStages;
@@ -515,7 +515,7 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
         prefetch_tmap(&p.tm_sfc);
         prefetch_tmap(&p.tm_d);
         for (uint32_t i = 0; i < kStages; ++i) {
-            mbar_init(&bars->full[i], kCtas * 2);   // per CTA: producer + transposer
+            mbar_init(&bars->full[i], kCtas * 3);   // per CTA: R producer, C producer, transposer
             mbar_init(&bars->empty[i], 1);          // UMMA commit
             mbar_init(&bars->sf_full[i], 1);        // producer (SF copies land here)
         }
@@ -558,12 +558,13 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
     bool ok = true;
     uint32_t acc_iter = 0;   // accumulator tiles handled so far by this role
 
-    if (warp == 0 || warp == 3) {
+    if (warp == 0 || warp == 3 || warp == 8) {
         // ============================================================ TMA producers
-        // Warp 0 fetches the operand tiles, warp 3 the scale factors: with per-32 scales a K block takes four
-        // copies, more than one issuing thread sustains.  The whole warp runs the loop (uniform control flow keeps
-        // addresses and coordinates in uniform registers); one elected lane issues the copies.
-        const bool sf_role = warp == 3;
+        // Warp 0 fetches the R tiles, warp 8 the C tiles, warp 3 the scale factors: one thread needs some 150-200
+        // cycles to issue a copy, so a K block's copies (up to four) are spread over three issuing threads.  The
+        // whole warp runs the loop (uniform control flow keeps addresses and coordinates in uniform registers); one
+        // elected lane issues the copies.
+        const bool sf_role = warp == 3, r_role = warp == 0;
         const uint32_t full_bar0 = leader_addr(&bars->full[0]);
         const uint32_t stage_tx_bytes = p.r.tx_bytes + p.c.tx_bytes;
         const uint32_t r_boxes = p.r.num_boxes, r_box_bytes = p.r.box_bytes, r_box_mn = p.r.box_mn;
@@ -630,17 +631,23 @@ __global__ void __launch_bounds__(256, 1) gemm_bs_kernel(const __grid_constant__
                         }
                         mbar_arrive_expect_tx(&bars->sf_full[stage], sf_bytes);
                       }
-                    } else if (elect_one()) {
+                    } else if (r_role) {
+                      if (elect_one()) {
                         // Operand tiles land on the leader's barrier (both CTAs of a pair feed one UMMA)
                         const uint32_t full_bar = full_bar0 + stage * 8;
-                        mbar_arrive_expect_tx_cluster(full_bar, tile_tx_bytes);
-                        const uint32_t kr = r_k + kb * 128, kc = c_k + kb * 128;
+                        mbar_arrive_expect_tx_cluster(full_bar, p.r.tx_bytes);
+                        const uint32_t kr = r_k + kb * 128;
                         for (uint32_t b = 0; b < r_boxes; ++b) {
                             const uint32_t dst = smem_r + stage * Cfg::R_STAGE + b * r_box_bytes;
                             const uint32_t mn = r_mn + b * r_box_mn;
                             if (r_mn_major) tma_load_2d<kPair>(dst, &p.tm_r, full_bar, mn, kr);
                             else            tma_load_2d<kPair>(dst, &p.tm_r, full_bar, kr, mn);
                         }
+                      }
+                    } else if (elect_one()) {
+                        const uint32_t full_bar = full_bar0 + stage * 8;
+                        mbar_arrive_expect_tx_cluster(full_bar, tile_tx_bytes - p.r.tx_bytes);
+                        const uint32_t kc = c_k + kb * 128;
                         for (uint32_t b = 0; b < c_boxes; ++b) {
                             const uint32_t dst = smem_c + stage * Cfg::C_STAGE + b * c_box_bytes;
                             const uint32_t mn = c_mn + b * c_box_mn;

@@ -18,7 +18,7 @@
 
 namespace dg {
 
-constexpr uint32_t kFusedThreads = 384;
+constexpr uint32_t kFusedThreads = 416;   // 13 warps: 0 weight copies, 1 UMMA, 2 + 8..11 pull, 3 scale copies, 4..7 epilogue, 12 token copies
 
 struct MoeFusedParams {
     CUtensorMap tm_w[2], tm_wsf[2], tm_act[2], tm_actsf[2];   // [0]: first GEMM (W13, pool tokens), [1]: second (W2, activations)
@@ -116,7 +116,7 @@ DG_DEVICE bool fused_grid_barrier(uint32_t* counter, uint32_t target, volatile u
 // number of threads.  Thread 0 issues, all threads sum (slot order, FP32) and store BF16.  The kernel's operand
 // stages are free by now (all roles have left their loops and the grid barrier has passed).
 #ifndef DG_REDUCE_PIECE
-#define DG_REDUCE_PIECE (kFusedThreads * 8)
+#define DG_REDUCE_PIECE 3072
 #define DG_REDUCE_STAGES 4
 #endif
 constexpr uint32_t kReducePiece = DG_REDUCE_PIECE, kReduceStages = DG_REDUCE_STAGES, kReduceSlotBytes = kReducePiece * 2;
@@ -215,7 +215,7 @@ DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uin
 // Cycles spent in a wait, summed per warp into trace slots 5..7 (timing studies only)
 #define DG_FUSED_TIMED(slot_, stmt_) do { const long long t0_ = clock64(); stmt_; wait_cycles[(slot_) - 5] += clock64() - t0_; } while (0)
 #define DG_FUSED_FLUSH() do { if (p.trace != nullptr && lane == 0) { for (int i_ = 0; i_ < 3; ++i_) p.trace[(blockIdx.x * 16 + warp) * 8 + 5 + i_] = wait_cycles[i_]; \
-    if (warp == 4) for (int i_ = 0; i_ < 8; ++i_) p.trace[(blockIdx.x * 16 + 12) * 8 + i_] = epi_cycles[i_]; } } while (0)
+    if (warp == 4) for (int i_ = 0; i_ < 8; ++i_) p.trace[(blockIdx.x * 16 + 13) * 8 + i_] = epi_cycles[i_]; } } while (0)
 #define DG_EPI_TIMED(slot_, stmt_) do { const long long t0_ = clock64(); stmt_; epi_cycles[slot_] += clock64() - t0_; } while (0)
 #define DG_FUSED_STAMP(slot_) do { if (p.trace != nullptr && lane == 0) p.trace[(blockIdx.x * 16 + warp) * 8 + (slot_)] = global_timer_ns(); } while (0)
 #else
@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             prefetch_tmap(&p.tm_w[i]), prefetch_tmap(&p.tm_wsf[i]), prefetch_tmap(&p.tm_act[i]), prefetch_tmap(&p.tm_actsf[i]);
         }
         for (uint32_t i = 0; i < kStages; ++i) {
-            mbar_init(&bars->full[i], 4);    // both CTAs' operand and scale producers; every copy of the stage lands here
+            mbar_init(&bars->full[i], 6);    // both CTAs' weight, token and scale producers; every copy of the stage lands here
             mbar_init(&bars->empty[i], 1);   // UMMA commit
         }
         for (uint32_t i = 0; i < 2; ++i) {
@@ -331,9 +331,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     long long epi_cycles[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     (void)wait_cycles, (void)epi_cycles;
 
-    if (warp == 0 || warp == 3) {
-        // ============================================================ TMA producers: warp 0 operand tiles, warp 3 scale factors
-        const bool sf_role = warp == 3;
+    if (warp == 0 || warp == 3 || warp == 12) {
+        // ============================================================ TMA producers: warp 0 weight tiles, warp 12 token tiles,
+        // warp 3 scale factors (one thread needs 150-200 cycles per copy it issues; a K block has four)
+        const bool sf_role = warp == 3, w_role = warp == 0;
         const uint32_t full_bar0 = map_to_cta(smem_u32(&bars->full[0]), 0);
         for (uint32_t slot = unit; slot < num_slots && ok; slot += num_units) {
             if (!fused_slot_to_tile(table, num_tiles, n1, n2, p.lag, slot, tc)) continue;
@@ -356,7 +357,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             const uint32_t num_kb = pk;
             const uint32_t per_cta = tc.rows / 2;
             const CUtensorMap* tm_act = per_cta <= 32 ? &p.tm_act_small[k][0] : per_cta <= 64 ? &p.tm_act_small[k][1] : &p.tm_act[k];
-            const uint32_t tx_bytes = Cfg::R_STAGE / 2 + (per_cta <= 32 ? 32u : per_cta <= 64 ? 64u : 128u) * 128u;   // FP4 weights count packed bytes
+            const uint32_t tx_bytes = (per_cta <= 32 ? 32u : per_cta <= 64 ? 64u : 128u) * 128u;
             for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
                 DG_FUSED_TIMED(6, ok = wait_barrier(&bars->empty[stage], phase ^ 1, abort_flag, peer_abort, wp, kSiteProducerEmpty, acc_iter, kb, stage));
                 if (!ok) break;
@@ -366,9 +367,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                         mbar_arrive_expect_tx_cluster(full_bar, Cfg::SFR_STAGE + Cfg::SFC_STAGE);
                         tma_load_2d<true>(smem_sfr + stage * Cfg::SFR_STAGE, &p.tm_wsf[k], full_bar, sfr_mn, sfr_k + kb);
                         tma_load_2d<true>(smem_sfc + stage * Cfg::SFC_STAGE, &p.tm_actsf[k], full_bar, sfc_mn, kb);
+                    } else if (w_role) {
+                        mbar_arrive_expect_tx_cluster(full_bar, Cfg::R_STAGE / 2);   // FP4 weights count packed bytes
+                        tma_load_2d<true>(smem_r + stage * Cfg::R_STAGE, &p.tm_w[k], full_bar, kb * 128, r_mn);
                     } else {
                         mbar_arrive_expect_tx_cluster(full_bar, tx_bytes);
-                        tma_load_2d<true>(smem_r + stage * Cfg::R_STAGE, &p.tm_w[k], full_bar, kb * 128, r_mn);
                         tma_load_2d<true>(smem_c + stage * Cfg::C_STAGE, tm_act, full_bar, kb * 128, c_mn);
                     }
                 }
