@@ -431,23 +431,41 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
         const uint32_t tmem_empty_bar = map_to_cta(smem_u32(&bars->tmem_empty[0]), 0);
         const uint32_t overlap_bar = map_to_cta(smem_u32(&bars->overlap[0]), 0);
         uint32_t moe_buf = 0, moe_chunks = 0;
-        for (uint32_t slot = unit; slot < num_slots && ok; slot += num_units) {
-            if (!fused_slot_to_tile(table, num_tiles, n1, n2, p.lag, slot, tc)) continue;
-            const uint32_t acc = acc_iter & 1, acc_phase = (acc_iter >> 1) & 1;
-            // Per-token data of the tile, fetched while its UMMAs run.  The reading threads themselves must have
-            // seen the counters that say the pool rows (and, for the second GEMM, the routing metadata) are there.
-            if (tc.kind == 0) {
-                DG_FUSED_TIMED(7, ok = fused_wait_counter(pulled + tc.row0 / 128, tc.valid0, abort_flag, p.a, 207, tc.tile));
-                if (ok && tc.rows > 128) DG_FUSED_TIMED(7, ok = fused_wait_counter(pulled + tc.row0 / 128 + 1, tc.valid1, abort_flag, p.a, 207, tc.tile));
+        uint64_t* ttab0 = reinterpret_cast<uint64_t*>(smem_gen + (smem_cd - smem_base) + Cfg::TABLE_OFF);
+
+        // Next tile of this pair's schedule at or after `slot`; false when the schedule is exhausted.
+        auto next_tile = [&](uint32_t& slot, FusedTile& t) {
+            for (; slot < num_slots; slot += num_units)
+                if (fused_slot_to_tile(table, num_tiles, n1, n2, p.lag, slot, t)) return true;
+            return false;
+        };
+        // The reading threads themselves must have seen the counters that say the pool rows (and, for the second
+        // GEMM, the routing metadata) are there.  Non-blocking form: one look at each counter.
+        auto deps_ready = [&](const FusedTile& t) {
+            auto seen = [&](const uint32_t* counter, uint32_t target) {
+                uint32_t v;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+                return static_cast<int32_t>(v - target) >= 0;
+            };
+            if (t.kind != 0) return seen(l1_done + t.tile, n1 * 8);
+            return seen(pulled + t.row0 / 128, t.valid0) && (t.rows <= 128 || seen(pulled + t.row0 / 128 + 1, t.valid1));
+        };
+        auto wait_deps = [&](const FusedTile& t) {
+            bool r;
+            if (t.kind == 0) {
+                r = fused_wait_counter(pulled + t.row0 / 128, t.valid0, abort_flag, p.a, 207, t.tile);
+                if (r && t.rows > 128) r = fused_wait_counter(pulled + t.row0 / 128 + 1, t.valid1, abort_flag, p.a, 207, t.tile);
             } else {
-                DG_FUSED_TIMED(7, ok = fused_wait_counter(l1_done + tc.tile, n1 * 8, abort_flag, p.a, 208, tc.tile));
+                r = fused_wait_counter(l1_done + t.tile, n1 * 8, abort_flag, p.a, 208, t.tile);
             }
-            if (!ok) break;
-            uint64_t* ttab = reinterpret_cast<uint64_t*>(smem_gen + (smem_cd - smem_base) + Cfg::TABLE_OFF) + acc * 256;
-            DG_EPI_TIMED(0,
-            for (uint32_t tok = q * 32 + lane; tok < tc.rows; tok += 128) {
-                const uint32_t row = tc.row0 + tok;
-                if (tc.kind == 0) {
+            return r;
+        };
+        // Per-token data of a tile: route weights (first GEMM) or destination rows in the source ranks' combine
+        // planes (second GEMM; 0 = the pool row carries no token)
+        auto fill_table = [&](const FusedTile& t, uint64_t* ttab) {
+            for (uint32_t tok = q * 32 + lane; tok < t.rows; tok += 128) {
+                const uint32_t row = t.row0 + tok;
+                if (t.kind == 0) {
                     reinterpret_cast<float*>(ttab)[tok] = p.e.pool_w[row];
                 } else {
                     const int32_t src_rank = p.e.pool_meta[row * 3];
@@ -461,7 +479,19 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                     ttab[tok] = dst;
                 }
             }
-            __syncwarp(););
+        };
+
+        uint32_t slot = unit;
+        FusedTile nt;
+        bool have = ok && next_tile(slot, tc), prepared = false;
+        while (have && ok) {
+            const uint32_t acc = acc_iter & 1, acc_phase = (acc_iter >> 1) & 1;
+            uint64_t* ttab = ttab0 + acc * 256;
+            if (!prepared) {
+                DG_FUSED_TIMED(7, ok = wait_deps(tc));
+                if (!ok) break;
+                DG_EPI_TIMED(0, fill_table(tc, ttab); __syncwarp(););
+            }
             DG_FUSED_TIMED(5, ok = wait_barrier(&bars->tmem_full[acc], acc_phase, abort_flag, peer_abort, wp, kSiteEpilogueTmemFull, acc_iter, 0, acc));
             if (!ok) break;
             tc_fence_after();
@@ -469,6 +499,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             const uint32_t n0 = tc.n_blk * 256 + cta_rank * 128;
             const uint32_t num_chunks = (tc.rows + 31) / 32;
             const bool reverse = acc == 0;   // stage 0 shares its last columns, stage 1 its first: drain those first
+            bool have_next = false;
+            prepared = false;
 #pragma unroll 1
             for (uint32_t i = 0; i < num_chunks && ok; ++i) {
                 const uint32_t ch = reverse ? num_chunks - 1 - i : i;
@@ -494,6 +526,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                                   acc_iter, ch, moe_buf));
                 ++moe_chunks;
                 if (!ok) break;
+                if (i == 0) {
+                    // Every epilogue warp has left the previous tile (they all arrived at this chunk's barrier), so its
+                    // table buffer is free: fetch the next tile's descriptor and, if its inputs are already there,
+                    // its per-token table, so that its epilogue can start the moment its UMMAs finish
+                    slot += num_units;
+                    have_next = next_tile(slot, nt);
+                    if (have_next && deps_ready(nt)) {
+                        DG_EPI_TIMED(0, fill_table(nt, ttab0 + (acc ^ 1) * 256); __syncwarp(););
+                        prepared = true;
+                    }
+                }
                 const uint32_t chunk_rows = min(32u, tc.rows - ch * 32);
                 if (tc.kind == 0)
                     DG_EPI_TIMED(3, moe_l1_chunk(p.e, stage_gen, Cfg::PITCH, reinterpret_cast<const float*>(ttab), q, lane, ch, chunk_rows, tc.row0, n0); __syncwarp(););
@@ -509,11 +552,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                 __threadfence();
                 __syncwarp();
                 if (lane == 0) atomicAdd(l1_done + tc.tile, 1u););
-                DG_EPI_TIMED(6, ;);
-            } else {
-                DG_EPI_TIMED(7, ;);
             }
             ++acc_iter;
+            have = have_next;
+            tc = nt;
         }
         __threadfence_system();   // pushes to the source ranks are out before the final barriers
     } else if (ok) {
