@@ -19,6 +19,7 @@ EXPORTS = (
     "dg_get_mk_alignment_for_contiguous_layout", "dg_get_theoretical_mk_alignment_for_contiguous_layout",
     "dg_set_wait_timeout_ms", "dg_check_status", "dg_last_error", "dg_version",
     "dg_mega_moe_buffer_layout", "dg_get_token_alignment_for_mega_moe", "dg_mega_moe_forward", "dg_set_mega_moe_fused", "dg_gemm_fp8_fp32sf_noalloc", "dg_noalloc_scratch_bytes",
+    "dg_per_token_cast_to_fp8",
 )
 
 
@@ -64,6 +65,14 @@ class GemmNoAllocArgs(C.Structure):
                 ("lda", C.c_int64), ("ldb", C.c_int64), ("ldd", C.c_int64), ("stream", C.c_void_p)]
 
 
+class CastArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("ldx", C.c_int64), ("rows", C.c_int32), ("cols", C.c_int32), ("gran_k", C.c_int32),
+                ("q", C.c_void_p), ("ldq", C.c_int64), ("sf", C.c_void_p), ("sf_mode", C.c_int32), ("sf_ld", C.c_int64),
+                ("stream", C.c_void_p)]
+
+
+CAST_SF_FLOAT, CAST_SF_PACKED_ROW_MAJOR, CAST_SF_PACKED_MN_MAJOR = 0, 1, 2
+
 _lib = None
 
 
@@ -88,6 +97,7 @@ def lib() -> C.CDLL:
         l.dg_mega_moe_buffer_layout.argtypes = [C.POINTER(MoeConfig), C.POINTER(MoeLayout)]
         l.dg_mega_moe_forward.argtypes = [C.POINTER(MoeArgs)]
         l.dg_gemm_fp8_fp32sf_noalloc.argtypes = [C.POINTER(GemmNoAllocArgs)]
+        l.dg_per_token_cast_to_fp8.argtypes = [C.POINTER(CastArgs)]
         for name in ("dg_set_num_sms", "dg_set_tc_util", "dg_set_mk_alignment_for_contiguous_layout",
                      "dg_get_theoretical_mk_alignment_for_contiguous_layout", "dg_set_wait_timeout_ms",
                      "dg_set_mega_moe_fused"):

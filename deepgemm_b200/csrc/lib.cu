@@ -16,6 +16,7 @@
 #include "sf_pack.cuh"
 #include "mega_moe.cuh"
 #include "mega_moe_fused.cuh"
+#include "cast_fp8.cuh"
 
 namespace {
 
@@ -365,6 +366,43 @@ int dg_sf_pack_ue8m0(const float* sf, int32_t* out, int32_t num_batches, int32_t
     DG_REQUIRE(num_batches <= 65535 && (p.packed_k + 31) / 32 <= 65535, "grid");
     dim3 grid((mn + 31) / 32, (p.packed_k + 31) / 32, num_batches);
     dg::sf_pack_ue8m0_kernel<<<grid, dim3(32, 8, 1), 0, static_cast<cudaStream_t>(stream)>>>(p);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+int dg_per_token_cast_to_fp8(const dg_cast_args* args) {
+    DG_REQUIRE(args != nullptr, "args");
+    const dg_cast_args& a = *args;
+    DG_REQUIRE(a.x != nullptr && a.q != nullptr && a.sf != nullptr, "x/q/sf");
+    DG_REQUIRE(a.rows >= 0 && a.cols >= 0, "shape");
+    DG_REQUIRE(a.gran_k == 32 || a.gran_k == 128, "gran_k");
+    DG_REQUIRE(a.cols % 8 == 0 && a.ldx % 8 == 0 && a.ldx >= a.cols, "cols % 8 == 0 and ldx % 8 == 0");
+    DG_REQUIRE(a.ldq % 8 == 0 && a.ldq >= a.cols, "ldq % 8 == 0");
+    DG_REQUIRE(reinterpret_cast<uintptr_t>(a.x) % 16 == 0 && reinterpret_cast<uintptr_t>(a.q) % 8 == 0, "alignment of x / q");
+    DG_REQUIRE(a.sf_mode >= DG_CAST_SF_FLOAT && a.sf_mode <= DG_CAST_SF_PACKED_MN_MAJOR, "sf_mode");
+    if (a.rows == 0 || a.cols == 0) return DG_OK;
+    const int64_t groups = (a.cols + a.gran_k - 1) / a.gran_k, words = (groups + 3) / 4;
+    if (a.sf_mode == DG_CAST_SF_FLOAT) DG_REQUIRE(a.sf_ld >= groups, "sf_ld >= groups");
+    if (a.sf_mode == DG_CAST_SF_PACKED_ROW_MAJOR) DG_REQUIRE(a.sf_ld >= words, "sf_ld >= packed words per row");
+    if (a.sf_mode == DG_CAST_SF_PACKED_MN_MAJOR) DG_REQUIRE(a.sf_ld >= a.rows, "sf_ld >= rows");
+    dg::CastParams p;
+    p.x = static_cast<const __nv_bfloat16*>(a.x), p.ldx = a.ldx;
+    p.rows = static_cast<uint32_t>(a.rows), p.cols = static_cast<uint32_t>(a.cols), p.gran_k = static_cast<uint32_t>(a.gran_k);
+    p.q = static_cast<uint8_t*>(a.q), p.ldq = a.ldq, p.sf = a.sf, p.sf_mode = static_cast<uint32_t>(a.sf_mode), p.sf_ld = a.sf_ld;
+    const uint32_t warps_per_cta = dg::kCastThreads / 32;
+    int num_sms = 0;
+    {
+        std::lock_guard<std::mutex> lk(g_knobs.mu);
+        num_sms = g_knobs.num_sms;
+    }
+    if (num_sms <= 0) {
+        int dev = 0;
+        DG_CUDA(cudaGetDevice(&dev));
+        DG_CUDA(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    const uint32_t want = (p.rows + warps_per_cta - 1) / warps_per_cta;
+    const uint32_t grid = want < static_cast<uint32_t>(num_sms) * 8u ? want : static_cast<uint32_t>(num_sms) * 8u;
+    dg::cast_bf16_to_fp8_ue8m0_kernel<<<grid, dg::kCastThreads, 0, static_cast<cudaStream_t>(a.stream)>>>(p);
     DG_CUDA(cudaGetLastError());
     return DG_OK;
 }

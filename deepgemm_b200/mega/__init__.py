@@ -95,6 +95,20 @@ class SymmBuffer:
         self.num_ring_tokens = p
         self.num_sf_ring_tokens = p
 
+    def load_tokens(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor) -> int:
+        """Fill the input views from BF16 activations: one fused kernel casts x to E4M3 with per-32 UE8M0 scales
+        straight into `self.x` / `self.x_sf` (the recipe the forward consumes), the routing tensors are copied.
+        Returns the number of tokens, i.e. the row count to give `y`."""
+        from ..cast import per_token_cast_to_fp8_fused
+        n = x.size(0)
+        _require(n <= self.num_max_tokens_per_rank and x.size(1) == self.hidden, "x fits the buffer")
+        _require(tuple(topk_idx.shape) == (n, self.num_topk) and tuple(topk_weights.shape) == (n, self.num_topk),
+                 "topk_idx / topk_weights are [num_tokens, num_topk]")
+        per_token_cast_to_fp8_fused(x, 32, "packed", out=self.x[:n], sf_out=self.x_sf[:n])
+        self.topk_idx[:n].copy_(topk_idx)
+        self.topk_weights[:n].copy_(topk_weights)
+        return n
+
     def destroy(self):
         self.handle = self.buffer = self.group = None
         self.x = self.x_sf = self.topk_idx = self.topk_weights = None

@@ -174,6 +174,33 @@ int dg_mega_moe_forward(const dg_moe_args* args);
  * 0: one kernel per phase (7 launches), the same arithmetic; also the path taken when the conditions fail. */
 int dg_set_mega_moe_fused(int32_t enable);
 
+/* ---- Fused activation cast ------------------------------------------------------------------------------
+ * BF16 [rows, cols] -> E4M3 [rows, cols] + one UE8M0 scale per 1 x gran_k group, in one kernel.  The arithmetic is
+ * per_token_cast_to_fp8(use_ue8m0=True) of the reference (deep_gemm/utils/math.py:13-49); the reference runs it as
+ * torch eager code and recommends fusing it into the producer (README.md:71,133-138), which this is.  The scales
+ * are written directly in the form the consumer wants (no separate dg_sf_pack_ue8m0 launch):
+ *   DG_CAST_SF_FLOAT             float32 [rows, ceil(cols / gran_k)], sf_ld elements between rows
+ *   DG_CAST_SF_PACKED_ROW_MAJOR  int32 [rows, ceil(groups / 4)], four exponent bytes per word, sf_ld words between
+ *                                rows (the use_packed_ue8m0 form; the x_sf view of the Mega MoE buffer)
+ *   DG_CAST_SF_PACKED_MN_MAJOR   the same words at [kw * sf_ld + row]: what dg_gemm_bs reads (sf_ld >= align(rows, 4))
+ * Groups of a word that cover no data get the exponent byte 127, as the reference pads.
+ * x: 16-byte aligned, ldx (elements) % 8 == 0, cols % 8 == 0; q: 8-byte aligned, ldq (bytes) % 8 == 0. */
+enum { DG_CAST_SF_FLOAT = 0, DG_CAST_SF_PACKED_ROW_MAJOR = 1, DG_CAST_SF_PACKED_MN_MAJOR = 2 };
+
+typedef struct dg_cast_args {
+    const void* x;      /* bf16 */
+    int64_t ldx;
+    int32_t rows, cols, gran_k; /* gran_k: 32 or 128 */
+    void* q;            /* e4m3 bytes */
+    int64_t ldq;
+    void* sf;
+    int32_t sf_mode;
+    int64_t sf_ld;
+    void* stream;
+} dg_cast_args;
+
+int dg_per_token_cast_to_fp8(const dg_cast_args* args);
+
 /* ---- Dense FP8 GEMM that allocates nothing ------------------------------------------------------------
  * No counterpart in the reference.  For callers that must not call cudaMalloc (or any allocating library
  * routine) around the GEMM - a plugin running inside another runtime's memory plan, a real-time loop, code
