@@ -666,7 +666,7 @@ static int launch_moe_fused(const dg_moe_args& m, const dg::MoeArgs& a, int num_
     p.trace = g_trace;
     {
         const char* env = getenv("DG_MEGA_MOE_LAG");   // tuning aid
-        p.lag = env != nullptr ? static_cast<uint32_t>(atoi(env)) : 4;
+        p.lag = env != nullptr ? static_cast<uint32_t>(atoi(env)) : 8;
         if (p.lag < 1) p.lag = 1;
     }
     DG_CUDA(cudaFuncSetAttribute(dg::mega_moe_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -18,7 +18,11 @@
 
 namespace dg {
 
-constexpr uint32_t kFusedThreads = 416;   // 13 warps: 0 weight copies, 1 UMMA, 2 + 8..11 pull, 3 scale copies, 4..7 epilogue, 12 token copies
+#ifndef DG_EXPERIMENT_PULL_FIRST
+#define DG_EXPERIMENT_PULL_FIRST 0   // timing study: the whole CTA pulls before the GEMM roles start
+#endif
+constexpr uint32_t kFusedThreads = 544;   // 17 warps: 0 weight copies, 1 UMMA, 2 + 8..11 pull, 3 scale copies, 12 token copies,
+                                          // 4..7 and 13..16 the two epilogue groups
 
 struct MoeFusedParams {
     CUtensorMap tm_w[2], tm_wsf[2], tm_act[2], tm_actsf[2];   // [0]: first GEMM (W13, pool tokens), [1]: second (W2, activations)
@@ -214,10 +218,10 @@ DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uin
 #ifdef DG_TRACE
 // Cycles spent in a wait, summed per warp into trace slots 5..7 (timing studies only)
 #define DG_FUSED_TIMED(slot_, stmt_) do { const long long t0_ = clock64(); stmt_; wait_cycles[(slot_) - 5] += clock64() - t0_; } while (0)
-#define DG_FUSED_FLUSH() do { if (p.trace != nullptr && lane == 0) { for (int i_ = 0; i_ < 3; ++i_) p.trace[(blockIdx.x * 16 + warp) * 8 + 5 + i_] = wait_cycles[i_]; \
-    if (warp == 4) for (int i_ = 0; i_ < 8; ++i_) p.trace[(blockIdx.x * 16 + 13) * 8 + i_] = epi_cycles[i_]; } } while (0)
+#define DG_FUSED_FLUSH() do { if (p.trace != nullptr && lane == 0) { for (int i_ = 0; i_ < 3; ++i_) p.trace[(blockIdx.x * 20 + warp) * 8 + 5 + i_] = wait_cycles[i_]; \
+    if (warp == 4) for (int i_ = 0; i_ < 8; ++i_) p.trace[(blockIdx.x * 20 + 18) * 8 + i_] = epi_cycles[i_]; } } while (0)
 #define DG_EPI_TIMED(slot_, stmt_) do { const long long t0_ = clock64(); stmt_; epi_cycles[slot_] += clock64() - t0_; } while (0)
-#define DG_FUSED_STAMP(slot_) do { if (p.trace != nullptr && lane == 0) p.trace[(blockIdx.x * 16 + warp) * 8 + (slot_)] = global_timer_ns(); } while (0)
+#define DG_FUSED_STAMP(slot_) do { if (p.trace != nullptr && lane == 0) p.trace[(blockIdx.x * 20 + warp) * 8 + (slot_)] = global_timer_ns(); } while (0)
 #else
 #define DG_FUSED_STAMP(slot_) do { } while (0)
 #define DG_FUSED_TIMED(slot_, stmt_) do { stmt_; } while (0)
@@ -246,6 +250,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     const bool is_leader = cta_rank == 0;
     const uint32_t unit = blockIdx.x / 2, num_units = p.num_ctas / 2;
     volatile uint32_t* abort_flag = &bars->abort;
+    __shared__ __align__(8) uint64_t s_epi_bar[2][2];   // per epilogue group: staging buffer written / read
     const uint32_t peer_abort = map_to_cta(smem_u32(&bars->abort), cta_rank ^ 1);
     uint32_t* work = reinterpret_cast<uint32_t*>(p.a.base[p.a.rank] + L.off_work);
     GemmParams wp;   // only the fields wait_barrier reports through
@@ -264,7 +269,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             mbar_init(&bars->tmem_full[i], 1);
             mbar_init(&bars->tmem_empty[i], 2 * 4);
             mbar_init(&bars->overlap[i], 2 * 4);
-            mbar_init(&bars->epi_sync[i], 4);
+            mbar_init(&s_epi_bar[i][0], 4), mbar_init(&s_epi_bar[i][1], 4);
         }
         bars->abort = 0;
         fence_mbar_init();
@@ -319,6 +324,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     }
     __syncthreads();
 
+#if DG_EXPERIMENT_PULL_FIRST
+    if (ok) moe_pull_rows(p.a, s_prefix, blockIdx.x * (kFusedThreads / 32) + warp, p.num_ctas * (kFusedThreads / 32), lane, pulled);
+    __syncthreads();
+#endif
     DG_FUSED_STAMP(1);
     uint32_t stage = 0, phase = 0;
     auto advance = [&]() {
@@ -425,47 +434,44 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                 ++acc_iter;
             }
         }
-    } else if (warp >= 4 && warp < 8) {
-        // ============================================================ epilogue (TMEM lane quadrant = warp % 4)
-        const uint32_t q = warp - 4;
+    } else if ((warp >= 4 && warp < 8) || warp >= 13) {
+        // ============================================================ epilogue: two groups of four warps (4..7 and
+        // 13..16; TMEM lane quadrant = warp % 4).  Group g drains the tiles that land in accumulator stage g, so a
+        // group has two tile periods for one tile; with one group the UMMA issuer waited for the epilogue 17 % of
+        // the time.  Each group owns one staging buffer, one per-token table and two barriers (buffer written /
+        // buffer read).
+        const uint32_t group = warp >= 13 ? 1u : 0u, q = warp % 4;
         const uint32_t tmem_empty_bar = map_to_cta(smem_u32(&bars->tmem_empty[0]), 0);
         const uint32_t overlap_bar = map_to_cta(smem_u32(&bars->overlap[0]), 0);
-        uint32_t moe_buf = 0, moe_chunks = 0;
-        uint64_t* ttab0 = reinterpret_cast<uint64_t*>(smem_gen + (smem_cd - smem_base) + Cfg::TABLE_OFF);
+        uint64_t* bar_written = &s_epi_bar[group][0];
+        uint64_t* bar_read = &s_epi_bar[group][1];
+        uint8_t* stage_gen = smem_gen + (smem_cd - smem_base) + group * 32 * Cfg::PITCH;
+        uint64_t* ttab = reinterpret_cast<uint64_t*>(smem_gen + (smem_cd - smem_base) + Cfg::TABLE_OFF) + group * 256;
+        uint32_t chunks_done = 0;
 
-        // Next tile of this pair's schedule at or after `slot`; false when the schedule is exhausted.
-        auto next_tile = [&](uint32_t& slot, FusedTile& t) {
-            for (; slot < num_slots; slot += num_units)
-                if (fused_slot_to_tile(table, num_tiles, n1, n2, p.lag, slot, t)) return true;
-            return false;
-        };
-        // The reading threads themselves must have seen the counters that say the pool rows (and, for the second
-        // GEMM, the routing metadata) are there.  Non-blocking form: one look at each counter.
-        auto deps_ready = [&](const FusedTile& t) {
-            auto seen = [&](const uint32_t* counter, uint32_t target) {
-                uint32_t v;
-                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
-                return static_cast<int32_t>(v - target) >= 0;
-            };
-            if (t.kind != 0) return seen(l1_done + t.tile, n1 * 8);
-            return seen(pulled + t.row0 / 128, t.valid0) && (t.rows <= 128 || seen(pulled + t.row0 / 128 + 1, t.valid1));
-        };
-        auto wait_deps = [&](const FusedTile& t) {
-            bool r;
-            if (t.kind == 0) {
-                r = fused_wait_counter(pulled + t.row0 / 128, t.valid0, abort_flag, p.a, 207, t.tile);
-                if (r && t.rows > 128) r = fused_wait_counter(pulled + t.row0 / 128 + 1, t.valid1, abort_flag, p.a, 207, t.tile);
+        for (uint32_t slot = unit; slot < num_slots && ok; slot += num_units) {
+            if (!fused_slot_to_tile(table, num_tiles, n1, n2, p.lag, slot, tc)) continue;
+            const uint32_t acc = acc_iter & 1, acc_phase = (acc_iter >> 1) & 1;
+            ++acc_iter;
+            if (acc != group) continue;
+            // Per-token data of the tile, fetched while its UMMAs run.  The reading threads themselves must have
+            // seen the counters that say the pool rows (and, for the second GEMM, the routing metadata) are there.
+            if (tc.kind == 0) {
+                DG_FUSED_TIMED(7, ok = fused_wait_counter(pulled + tc.row0 / 128, tc.valid0, abort_flag, p.a, 207, tc.tile));
+                if (ok && tc.rows > 128) DG_FUSED_TIMED(7, ok = fused_wait_counter(pulled + tc.row0 / 128 + 1, tc.valid1, abort_flag, p.a, 207, tc.tile));
             } else {
-                r = fused_wait_counter(l1_done + t.tile, n1 * 8, abort_flag, p.a, 208, t.tile);
+                DG_FUSED_TIMED(7, ok = fused_wait_counter(l1_done + tc.tile, n1 * 8, abort_flag, p.a, 208, tc.tile));
             }
-            return r;
-        };
-        // Per-token data of a tile: route weights (first GEMM) or destination rows in the source ranks' combine
-        // planes (second GEMM; 0 = the pool row carries no token)
-        auto fill_table = [&](const FusedTile& t, uint64_t* ttab) {
-            for (uint32_t tok = q * 32 + lane; tok < t.rows; tok += 128) {
-                const uint32_t row = t.row0 + tok;
-                if (t.kind == 0) {
+            if (!ok) break;
+            // The table's previous readers (this group's previous tile) are done: every warp of the group passed
+            // that tile's last `bar_read` arrival before coming here, and the first chunk below waits for it.
+            if (chunks_done > 0)
+                DG_FUSED_TIMED(6, ok = wait_barrier(bar_read, (chunks_done - 1) & 1, abort_flag, peer_abort, wp, kSiteEpilogueSync, acc_iter, 0, 2));
+            if (!ok) break;
+            DG_EPI_TIMED(0,
+            for (uint32_t tok = q * 32 + lane; tok < tc.rows; tok += 128) {
+                const uint32_t row = tc.row0 + tok;
+                if (tc.kind == 0) {
                     reinterpret_cast<float*>(ttab)[tok] = p.e.pool_w[row];
                 } else {
                     const int32_t src_rank = p.e.pool_meta[row * 3];
@@ -479,19 +485,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                     ttab[tok] = dst;
                 }
             }
-        };
-
-        uint32_t slot = unit;
-        FusedTile nt;
-        bool have = ok && next_tile(slot, tc), prepared = false;
-        while (have && ok) {
-            const uint32_t acc = acc_iter & 1, acc_phase = (acc_iter >> 1) & 1;
-            uint64_t* ttab = ttab0 + acc * 256;
-            if (!prepared) {
-                DG_FUSED_TIMED(7, ok = wait_deps(tc));
-                if (!ok) break;
-                DG_EPI_TIMED(0, fill_table(tc, ttab); __syncwarp(););
-            }
+            __syncwarp(););
             DG_FUSED_TIMED(5, ok = wait_barrier(&bars->tmem_full[acc], acc_phase, abort_flag, peer_abort, wp, kSiteEpilogueTmemFull, acc_iter, 0, acc));
             if (!ok) break;
             tc_fence_after();
@@ -499,8 +493,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             const uint32_t n0 = tc.n_blk * 256 + cta_rank * 128;
             const uint32_t num_chunks = (tc.rows + 31) / 32;
             const bool reverse = acc == 0;   // stage 0 shares its last columns, stage 1 its first: drain those first
-            bool have_next = false;
-            prepared = false;
 #pragma unroll 1
             for (uint32_t i = 0; i < num_chunks && ok; ++i) {
                 const uint32_t ch = reverse ? num_chunks - 1 - i : i;
@@ -514,35 +506,28 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                         if (i + 1 == num_chunks) mbar_arrive_cluster(tmem_empty_bar + acc * 8);
                     }
                 }
-                uint8_t* stage_gen = smem_gen + (smem_cd - smem_base) + moe_buf * 32 * Cfg::PITCH;
+                // the staging buffer's previous chunk has been read by all four warps (the tile's first chunk
+                // already waited above)
+                if (i > 0)
+                    DG_FUSED_TIMED(6, ok = wait_barrier(bar_read, (chunks_done - 1) & 1, abort_flag, peer_abort, wp, kSiteEpilogueSync, acc_iter, ch, 2));
+                if (!ok) break;
                 DG_EPI_TIMED(2,
                 _Pragma("unroll")
                 for (uint32_t t = 0; t < 32; ++t)
                     *reinterpret_cast<__nv_bfloat16*>(stage_gen + t * Cfg::PITCH + (q * 32 + lane) * 2) =
                         __float2bfloat16_rn(__uint_as_float(v[t]));
                 __syncwarp(););
-                if (lane == 0) mbar_arrive(&bars->epi_sync[moe_buf]);
-                DG_FUSED_TIMED(6, ok = wait_barrier(&bars->epi_sync[moe_buf], (moe_chunks >> 1) & 1, abort_flag, peer_abort, wp, kSiteEpilogueSync,
-                                  acc_iter, ch, moe_buf));
-                ++moe_chunks;
+                if (lane == 0) mbar_arrive(bar_written);
+                DG_FUSED_TIMED(6, ok = wait_barrier(bar_written, chunks_done & 1, abort_flag, peer_abort, wp, kSiteEpilogueSync, acc_iter, ch, 3));
                 if (!ok) break;
-                if (i == 0) {
-                    // Every epilogue warp has left the previous tile (they all arrived at this chunk's barrier), so its
-                    // table buffer is free: fetch the next tile's descriptor and, if its inputs are already there,
-                    // its per-token table, so that its epilogue can start the moment its UMMAs finish
-                    slot += num_units;
-                    have_next = next_tile(slot, nt);
-                    if (have_next && deps_ready(nt)) {
-                        DG_EPI_TIMED(0, fill_table(nt, ttab0 + (acc ^ 1) * 256); __syncwarp(););
-                        prepared = true;
-                    }
-                }
                 const uint32_t chunk_rows = min(32u, tc.rows - ch * 32);
                 if (tc.kind == 0)
                     DG_EPI_TIMED(3, moe_l1_chunk(p.e, stage_gen, Cfg::PITCH, reinterpret_cast<const float*>(ttab), q, lane, ch, chunk_rows, tc.row0, n0); __syncwarp(););
                 else
                     DG_EPI_TIMED(4, moe_l2_chunk(stage_gen, Cfg::PITCH, ttab, q * 32 + lane, ch, chunk_rows, n0); __syncwarp(););
-                moe_buf ^= 1;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_read);
+                ++chunks_done;
             }
             if (!ok) break;
             if (tc.kind == 0) {
@@ -553,15 +538,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                 __syncwarp();
                 if (lane == 0) atomicAdd(l1_done + tc.tile, 1u););
             }
-            ++acc_iter;
-            have = have_next;
-            tc = nt;
         }
         __threadfence_system();   // pushes to the source ranks are out before the final barriers
     } else if (ok) {
         // ============================================================ pull warps (2, 8..11): fill the pool in pool order
         const uint32_t pw = warp == 2 ? 0 : warp - 7;   // 0..4
-        moe_pull_rows(p.a, s_prefix, blockIdx.x * 5 + pw, p.num_ctas * 5, lane, pulled);
+        if (!DG_EXPERIMENT_PULL_FIRST) moe_pull_rows(p.a, s_prefix, blockIdx.x * 5 + pw, p.num_ctas * 5, lane, pulled);
     }
 
     DG_FUSED_FLUSH();
