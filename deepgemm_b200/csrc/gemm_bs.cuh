@@ -844,6 +844,13 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                         }
                     }
                     if constexpr (Cfg::kEpi == 0) {
+                    // A K group without rows (K-grouped layouts allow them) contributes nothing: its single K block
+                    // ran on whatever follows it in memory, so the accumulator is replaced by zeros
+                    // (D = 0, or D unchanged when accumulating).
+                    if (tc.k_len == 0) {
+#pragma unroll
+                        for (uint32_t j = 0; j < Cfg::CHUNK_COLS; ++j) v[j] = 0;
+                    }
                     // The slab we are about to overwrite must have been read by its previous store
                     if (lane == 0) tma_store_wait_read<Cfg::kStoreBufs - 1>();
                     __syncwarp();

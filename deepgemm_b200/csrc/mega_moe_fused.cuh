@@ -221,7 +221,7 @@ DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uin
 #define DG_FUSED_FLUSH() do { if (p.trace != nullptr && lane == 0) { for (int i_ = 0; i_ < 3; ++i_) p.trace[(blockIdx.x * 20 + warp) * 8 + 5 + i_] = wait_cycles[i_]; \
     if (warp == 4) for (int i_ = 0; i_ < 8; ++i_) p.trace[(blockIdx.x * 20 + 18) * 8 + i_] = epi_cycles[i_]; } } while (0)
 #define DG_EPI_TIMED(slot_, stmt_) do { const long long t0_ = clock64(); stmt_; epi_cycles[slot_] += clock64() - t0_; } while (0)
-#define DG_FUSED_STAMP(slot_) do { if (p.trace != nullptr && lane == 0) p.trace[(blockIdx.x * 20 + warp) * 8 + (slot_)] = global_timer_ns(); } while (0)
+#define DG_FUSED_STAMP(slot_) do { if (p.trace != nullptr && lane == 0) { p.trace[(blockIdx.x * 20 + warp) * 8 + (slot_)] = global_timer_ns(); if (warp == 0) p.trace[(blockIdx.x * 20 + 19) * 8 + (slot_)] = clock64(); } } while (0)
 #else
 #define DG_FUSED_STAMP(slot_) do { } while (0)
 #define DG_FUSED_TIMED(slot_, stmt_) do { stmt_; } while (0)

@@ -323,6 +323,36 @@ def test_k_grouped_tn(gran_k, accumulate, out_dtype):
         dg.set_mk_alignment_for_contiguous_layout(old)
 
 
+@pytest.mark.parametrize("accumulate,out_dtype", [(True, torch.float32), (False, torch.float32), (False, torch.bfloat16)])
+@pytest.mark.parametrize("ks", [[0, 256, 0, 512, 128, 0], [0, 0, 384, 0]])
+def test_k_grouped_tn_empty_groups(ks, accumulate, out_dtype):
+    """Groups without K rows give D = 0 (or leave C alone), first, last and in between: the variants of
+    tests/generators.py:265-273."""
+    old = dg.get_mk_alignment_for_contiguous_layout()
+    try:
+        dg.set_mk_alignment_for_contiguous_layout(128)
+        m, n = 256, 512
+        case = H.make_k_grouped(len(ks), m, n, ks, gran_k=128, seed=len(ks))
+        d = torch.randn((len(ks), m, n), dtype=out_dtype, device="cuda") * 32 if accumulate else \
+            torch.full((len(ks), m, n), float("nan"), dtype=out_dtype, device="cuda")
+        c = d if accumulate else None
+        cref = H.to_np(d).astype(np.float32) if accumulate else None
+        layout = torch.tensor(ks, dtype=torch.int32, device="cuda")
+        dg.k_grouped_fp8_gemm_tn_contiguous(case["a"], case["b"], d, ks, layout, c=c, recipe=(1, 1, 128))
+        torch.cuda.synchronize()
+        dg.check_status()
+        ref = OG.k_grouped_tn(case["ref_a"], case["ref_b"], case["bounds"], c=cref,
+                              cd_dtype="f32" if out_dtype == torch.float32 else "bf16")
+        got = H.to_np(d)
+        assert not np.isnan(got).any()
+        for g, kk in enumerate(ks):
+            if kk == 0:
+                assert np.array_equal(got[g], ref[g]), f"empty group {g}"
+        assert H.calc_diff(got, ref) < FP8_TOL
+    finally:
+        dg.set_mk_alignment_for_contiguous_layout(old)
+
+
 # --------------------------------------------------------------------------- full-size properties
 def test_full_size_dense_known_answer_and_torch_reference():
     """4096 x 4096 x 7168 (the dense headline shape): all-ones known answer, then seeded inputs against a
