@@ -55,7 +55,8 @@ class MoeArgs(C.Structure):
                 ("num_tokens", C.c_int32), ("y", C.c_void_p), ("ldy", C.c_int64),
                 ("l1_w", C.c_void_p), ("l1_sf", C.c_void_p), ("l2_w", C.c_void_p), ("l2_sf", C.c_void_p),
                 ("l1_sf_ld", C.c_int64), ("l2_sf_ld", C.c_int64), ("stats", C.c_void_p),
-                ("activation_clamp", C.c_float), ("fast_math", C.c_int32), ("stream", C.c_void_p)]
+                ("activation_clamp", C.c_float), ("fast_math", C.c_int32), ("stream", C.c_void_p),
+                ("activation", C.c_int32), ("situ_beta", C.c_float), ("situ_linear_beta", C.c_float)]
 
 
 class GemmNoAllocArgs(C.Structure):

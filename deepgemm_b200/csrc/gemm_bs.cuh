@@ -88,6 +88,9 @@ struct MoeEpilogueParams {
     uint32_t pool_rows, inter, hidden, t_max;
     float clamp;               // activation clamp; +inf = none
     uint32_t fast_math;
+    uint32_t activation;       // 0 SwiGLU, 1 GeGLU (tanh form), 2 SiTU
+    float situ_beta;           // SiTU: beta * tanh(gate / beta) * sigmoid(gate)
+    float situ_linear_beta;    // SiTU: up -> lb * tanh(up / lb); +inf = up unchanged
 };
 
 // Position of pool row `row` inside its 128-row group in the order tcgen05.cp.32x128b.warpx4 copies to TMEM.
@@ -383,7 +386,27 @@ DG_DEVICE bool wait_barrier(uint64_t* bar, uint32_t parity, volatile uint32_t* a
 // SwiGLU on the BF16-rounded gate / up pairs, times the route weight, per-32 UE8M0 E4M3 requantisation, stored
 // as rows of the second GEMM's A operand.  m0: first pool row of the tile; n0: first interleaved weight row of
 // this CTA; wtab: the tile's route weights.
-template <bool kFast, bool kClamp>
+// tanh by the approximate unit (fast math) or the library routine
+template <bool kFast>
+DG_DEVICE float moe_tanh(float x) {
+    if (kFast) {
+        float y;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+        return y;
+    }
+    return tanhf(x);
+}
+
+// gate -> the gated factor that multiplies `up` (deep_gemm tests/test_mega_moe.py:451-463 states the three forms)
+template <bool kFast, int kAct>
+DG_DEVICE float moe_gate(float g, float beta) {
+    const float sig = kFast ? __fdividef(1.0f, 1.0f + __expf(-g)) : 1.0f / (1.0f + expf(-g));
+    if (kAct == 0) return g * sig;
+    if (kAct == 1) return 0.5f * g * (1.0f + moe_tanh<kFast>(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return beta * moe_tanh<kFast>(kFast ? __fdividef(g, beta) : g / beta) * sig;
+}
+
+template <bool kFast, bool kClamp, int kAct>
 DG_DEVICE void moe_l1_chunk_impl(const MoeEpilogueParams& m, const uint8_t* stage, uint32_t pitch, const float* wtab,
                                  uint32_t q, uint32_t lane, uint32_t ch, uint32_t chunk_rows, uint32_t m0, uint32_t n0) {
     // A warp takes 8 tokens; lane = (token, 32-output group g, half): 16 outputs per
@@ -391,7 +414,9 @@ DG_DEVICE void moe_l1_chunk_impl(const MoeEpilogueParams& m, const uint8_t* stag
     // interleaved in blocks of 8 rows); the two halves of a group share their amax.
     const uint32_t t = q * 8 + (lane >> 2), g = (lane >> 1) & 1, half = lane & 1;
     const float w = wtab[min(ch * 32 + t, 255u)];
-    const float clamp = m.clamp;
+    const float clamp = m.clamp, beta = m.situ_beta, lin_beta = m.situ_linear_beta;
+    const bool squash_up = lin_beta < 3.0e38f;
+    (void)beta, (void)squash_up;
     const uint4* src = reinterpret_cast<const uint4*>(stage + t * pitch + g * 128 + half * 64);
     const uint4 raw[4] = {src[0], src[1], src[2], src[3]};   // [8 gate | 8 up] x 2, BF16
     float act[16];
@@ -408,14 +433,10 @@ DG_DEVICE void moe_l1_chunk_impl(const MoeEpilogueParams& m, const uint8_t* stag
                 uf.x = fminf(fmaxf(uf.x, -clamp), clamp);
                 uf.y = fminf(fmaxf(uf.y, -clamp), clamp);
             }
-            float sx, sy;
-            if (kFast) {
-                // x * sigmoid(x) with the approximate exponential and reciprocal units
-                sx = __fdividef(gf.x, 1.0f + __expf(-gf.x));
-                sy = __fdividef(gf.y, 1.0f + __expf(-gf.y));
-            } else {
-                sx = gf.x / (1.0f + expf(-gf.x));
-                sy = gf.y / (1.0f + expf(-gf.y));
+            const float sx = moe_gate<kFast, kAct>(gf.x, beta), sy = moe_gate<kFast, kAct>(gf.y, beta);
+            if (kAct == 2 && squash_up) {
+                uf.x = lin_beta * moe_tanh<kFast>(kFast ? __fdividef(uf.x, lin_beta) : uf.x / lin_beta);
+                uf.y = lin_beta * moe_tanh<kFast>(kFast ? __fdividef(uf.y, lin_beta) : uf.y / lin_beta);
             }
             const float ax = (sx * uf.x) * w, ay = (sy * uf.y) * w;
             act[blk * 8 + j * 2] = ax, act[blk * 8 + j * 2 + 1] = ay;
@@ -449,16 +470,24 @@ DG_DEVICE void moe_l1_chunk_impl(const MoeEpilogueParams& m, const uint8_t* stag
     }
 }
 
-DG_DEVICE void moe_l1_chunk(const MoeEpilogueParams& m, const uint8_t* stage, uint32_t pitch, const float* wtab,
-                            uint32_t q, uint32_t lane, uint32_t ch, uint32_t chunk_rows, uint32_t m0, uint32_t n0) {
+template <int kAct>
+DG_DEVICE void moe_l1_chunk_act(const MoeEpilogueParams& m, const uint8_t* stage, uint32_t pitch, const float* wtab,
+                                uint32_t q, uint32_t lane, uint32_t ch, uint32_t chunk_rows, uint32_t m0, uint32_t n0) {
     const bool clamp = m.clamp < 3.0e38f;   // +inf: no clamp
     if (m.fast_math) {
-        if (clamp) moe_l1_chunk_impl<true, true>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
-        else       moe_l1_chunk_impl<true, false>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
+        if (clamp) moe_l1_chunk_impl<true, true, kAct>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
+        else       moe_l1_chunk_impl<true, false, kAct>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
     } else {
-        if (clamp) moe_l1_chunk_impl<false, true>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
-        else       moe_l1_chunk_impl<false, false>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
+        if (clamp) moe_l1_chunk_impl<false, true, kAct>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
+        else       moe_l1_chunk_impl<false, false, kAct>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
     }
+}
+
+DG_DEVICE void moe_l1_chunk(const MoeEpilogueParams& m, const uint8_t* stage, uint32_t pitch, const float* wtab,
+                            uint32_t q, uint32_t lane, uint32_t ch, uint32_t chunk_rows, uint32_t m0, uint32_t n0) {
+    if (m.activation == 0)      moe_l1_chunk_act<0>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
+    else if (m.activation == 1) moe_l1_chunk_act<1>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
+    else                        moe_l1_chunk_act<2>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
 }
 
 // One 32-token chunk of the second expert GEMM's epilogue: 16 lanes move one token's 256 B segment of BF16

@@ -1,5 +1,6 @@
 // Host side of libdeepgemm_b200.so: argument checks, tile selection, tensor-map encoding and
 // launches behind the C ABI declared in include/deepgemm_b200.h.
+#include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -623,6 +624,9 @@ static void fill_moe_gemm_args(const dg_moe_args& m, const dg::MoeArgs& a, dg::M
     for (uint32_t r = 0; r < L.ranks; ++r) e->peer_base[r] = a.base[r];
     e->off_combine = L.off_combine, e->pool_rows = L.pool_rows, e->inter = L.inter, e->hidden = L.hidden, e->t_max = L.t_max;
     e->clamp = m.activation_clamp, e->fast_math = m.fast_math ? 1 : 0;
+    e->activation = static_cast<uint32_t>(m.activation);
+    e->situ_beta = m.situ_beta > 0.0f ? m.situ_beta : 1.0f;
+    e->situ_linear_beta = m.situ_linear_beta > 0.0f ? m.situ_linear_beta : INFINITY;
     dg_gemm_args g;
     memset(&g, 0, sizeof(g));
     g.gemm_type = DG_GEMM_M_PSUM, g.num_groups = L.experts_local, g.alignment = dg::kMoePoolAlign;
@@ -716,6 +720,7 @@ int dg_mega_moe_forward(const dg_moe_args* args) {
     DG_REQUIRE(m.num_tokens >= 0 && m.num_tokens <= m.cfg.num_max_tokens_per_rank, "num_tokens <= num_max_tokens_per_rank");
     DG_REQUIRE(m.buffer_ptrs != nullptr && m.y != nullptr, "null argument");
     DG_REQUIRE(m.l1_w && m.l1_sf && m.l2_w && m.l2_sf, "null weights");
+    DG_REQUIRE(m.activation >= DG_ACT_SWIGLU && m.activation <= DG_ACT_SITU, "activation");
     const dg::MoeLayout L = dg::make_moe_layout(m.cfg.num_ranks, m.cfg.num_experts, m.cfg.num_max_tokens_per_rank,
                                                 m.cfg.num_topk, m.cfg.hidden, m.cfg.intermediate_hidden);
     dg::MoeArgs a;

@@ -35,6 +35,9 @@ def get_block_m_for_mega_moe(num_ranks: int, num_experts: int, num_max_tokens_pe
     return 256
 
 
+_ACTIVATIONS = {"swiglu": 0, "geglu": 1, "situ": 2}
+
+
 class SymmBuffer:
     """One symmetric buffer per rank plus the views user code fills (deep_gemm/mega/__init__.py:32-134)."""
 
@@ -44,7 +47,7 @@ class SymmBuffer:
                  side_lora: bool = False):
         if mma_type != "fp8xfp4" or num_shared_experts or side_lora:
             raise NotImplementedError("only the FP8 x FP4 routed-expert forward is part of this build")
-        if activation != "swiglu":
+        if activation not in _ACTIVATIONS:
             raise NotImplementedError(f"activation `{activation}` is not part of this build")
         num_max_tokens_per_rank = align(num_max_tokens_per_rank, get_token_alignment_for_mega_moe())
         self.group = group
@@ -166,7 +169,9 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tens
                      l2_weights: Tuple[torch.Tensor, torch.Tensor], sym_buffer: SymmBuffer,
                      cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
                      recipe: Tuple[int, int, int] = (1, 1, 32), activation: str = "swiglu",
-                     activation_clamp: Optional[float] = None, fast_math: bool = True, **unsupported) -> None:
+                     activation_clamp: Optional[float] = None, fast_math: bool = True, *,
+                     situ_beta: Optional[float] = None, situ_linear_beta: Optional[float] = None,
+                     **unsupported) -> None:
     """Fused expert-parallel MoE forward into y [num_tokens, hidden] (deep_gemm/mega/__init__.py:273-348).
 
     The caller has filled sym_buffer.x / x_sf / topk_idx / topk_weights for its num_tokens = y.size(0) tokens;
@@ -178,7 +183,7 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tens
     if str(unsupported.get("route_weight_mode", "pre_down")).split(".")[-1].lower() not in ("pre_down",):
         raise NotImplementedError("only route_weight_mode='pre_down' is part of this build")
     _require(tuple(recipe) == (1, 1, 32), "recipe == (1, 1, 32)")
-    _require(activation == "swiglu", "activation == 'swiglu'")
+    _require(activation in _ACTIVATIONS, "activation in ('swiglu', 'geglu', 'situ')")
     b = sym_buffer
     (w1, sf1), (w2, sf2) = l1_weights, l2_weights
     el, h, i = b.num_experts // b.num_ranks, b.hidden, b.intermediate_hidden
@@ -204,5 +209,9 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tens
     args.stats = stats.data_ptr() if stats is not None else None
     args.activation_clamp = float("inf") if activation_clamp is None else float(activation_clamp)
     args.fast_math = int(bool(fast_math))
+    # SiTU parameters are ignored by the other activations (tests/test_mega_moe.py:551-559 of the reference)
+    args.activation = _ACTIVATIONS[activation]
+    args.situ_beta = 0.0 if situ_beta is None else float(situ_beta)
+    args.situ_linear_beta = 0.0 if situ_linear_beta is None else float(situ_linear_beta)
     args.stream = _stream(y)
     _lib.check(_lib.lib().dg_mega_moe_forward(C.byref(args)))

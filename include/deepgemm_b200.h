@@ -142,6 +142,8 @@ int dg_mega_moe_buffer_layout(const dg_moe_config* cfg, dg_moe_layout* out);
 /* Row granularity of num_max_tokens_per_rank (csrc/apis/mega_moe.hpp:34-36). */
 int dg_get_token_alignment_for_mega_moe(void);
 
+enum { DG_ACT_SWIGLU = 0, DG_ACT_GEGLU = 1, DG_ACT_SITU = 2 };
+
 typedef struct dg_moe_args {
     dg_moe_config cfg;
     void* const* buffer_ptrs;   /* host array [num_ranks] of device addresses */
@@ -161,6 +163,12 @@ typedef struct dg_moe_args {
     float activation_clamp;     /* +inf: none */
     int32_t fast_math;
     void* stream;
+    /* Gated activation (tests/test_mega_moe.py:451-463 of the reference): DG_ACT_SWIGLU gate * sigmoid(gate) * up;
+     * DG_ACT_GEGLU the tanh form of GELU(gate) * up; DG_ACT_SITU situ_beta * tanh(gate / situ_beta) * sigmoid(gate)
+     * * up', up' = situ_linear_beta * tanh(up / situ_linear_beta), or up when situ_linear_beta is +inf.
+     * situ_beta <= 0 means the default 1. */
+    int32_t activation;
+    float situ_beta, situ_linear_beta;
 } dg_moe_args;
 
 /* y[t] = bf16( sum over slots of bf16( Q32( SwiGLU(bf16(x_t W13_e^T)) * w_{t,slot} ) W2_e^T ) ) with the tokens

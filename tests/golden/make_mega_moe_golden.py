@@ -56,6 +56,11 @@ def main(ref_root):
     y = ref(x_deq.float(), idx, w, l1.float(), l2.float(), "swiglu")
     out = dict(x_deq=x_deq.float().numpy(), topk_idx=idx.numpy(), topk_weights=w.numpy(), l1_deq=l1.float().numpy(),
                l2_deq=l2.float().numpy(), y=y.float().numpy())
+    # the other gated activations of the reference's test (tests/test_mega_moe.py:551-566), same inputs
+    out["y_geglu"] = ref(x_deq.float(), idx, w, l1.float(), l2.float(), "geglu").float().numpy()
+    for tag, kw in (("situ_4_25", dict(situ_beta=4.0, situ_linear_beta=25.0)), ("situ_4_none", dict(situ_beta=4.0)),
+                    ("situ_2_3", dict(situ_beta=2.0, situ_linear_beta=3.0))):
+        out[f"y_{tag}"] = ref(x_deq.float(), idx, w, l1.float(), l2.float(), "situ", **kw).float().numpy()
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mega_moe_golden.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

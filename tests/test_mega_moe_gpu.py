@@ -117,6 +117,45 @@ def test_mega_moe_single_rank(cfg):
     run_rank(None, 0, 1, cfg)
 
 
+def test_mega_moe_gated_activations():
+    """The reference's test_mega_moe_gated_activations (tests/test_mega_moe.py:484-566) on one GPU: SwiGLU, GeGLU and
+    SiTU against the dequantised reference at its shape; SiTU parameters are ignored by the other two; SiTU is far
+    from SwiGLU (so the check has teeth)."""
+    hidden, inter, experts, topk, tokens = 4096, 1536, 16, 4, 96
+    (q1, sf1, deq1), (q2, sf2, deq2) = make_weights(experts, hidden, inter)
+    l1 = (q1, dg.transform_sf_into_required_layout(sf1, 2 * inter, hidden, (1, 32), experts))
+    l2 = (q2, dg.transform_sf_into_required_layout(sf2, hidden, inter, (1, 32), experts))
+    x_fp8, x_sf, idx, w, x_deq = make_inputs(tokens, hidden, experts, topk, 100)
+
+    def run(activation, **kw):
+        buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter, use_fp8_dispatch=True,
+                                              activation=activation)
+        a1, a2 = dg.transform_weights_for_mega_moe(l1, l2, activation=activation)
+        buf.x[:tokens].copy_(x_fp8), buf.x_sf[:tokens].copy_(x_sf)
+        buf.topk_idx[:tokens].copy_(idx), buf.topk_weights[:tokens].copy_(w)
+        y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device="cuda")
+        dg.fp8_fp4_mega_moe(y, a1, a2, buf, recipe=(1, 1, 32), activation=activation, activation_clamp=None,
+                            fast_math=True, **kw)
+        torch.cuda.synchronize()
+        dg.check_status()
+        buf.destroy()
+        return y
+
+    def reference(activation, **kw):
+        return OM.mega_moe_reference(x_deq, idx.cpu().numpy(), w.cpu().numpy(), deq1, deq2, None, activation, **kw)[0]
+
+    swiglu_ref = reference("swiglu")
+    for activation in ("swiglu", "geglu"):
+        y = run(activation)
+        assert H.calc_diff(H.to_np(y), reference(activation)) < MOE_TOL, activation
+        assert torch.equal(y, run(activation, situ_beta=None, situ_linear_beta=None)), activation
+        assert torch.equal(y, run(activation, situ_beta=4.0, situ_linear_beta=25.0)), activation
+    for beta, lin in ((4.0, 25.0), (4.0, None), (2.0, 3.0)):
+        y = H.to_np(run("situ", situ_beta=beta, situ_linear_beta=lin))
+        assert H.calc_diff(y, reference("situ", situ_beta=beta, situ_linear_beta=lin)) < MOE_TOL, (beta, lin)
+        assert H.calc_diff(y, swiglu_ref) > 50 * MOE_TOL, (beta, lin)
+
+
 def _worker(local_rank, ranks, cfg, port, results):
     import torch.distributed as dist
     torch.cuda.set_device(local_rank)

@@ -131,3 +131,10 @@ def test_mega_moe_oracle_matches_reference_baseline():
     y, counts = OM.mega_moe_reference(g["x_deq"], g["topk_idx"], g["topk_weights"], g["l1_deq"], g["l2_deq"])
     assert np.array_equal(y, g["y"])
     assert counts[5] == 0 and counts.sum() == (g["topk_idx"] >= 0).sum()
+    # the other gated activations of the reference's test (tests/test_mega_moe.py:551-566)
+    for tag, kw in (("y_geglu", dict(activation="geglu")),
+                    ("y_situ_4_25", dict(activation="situ", situ_beta=4.0, situ_linear_beta=25.0)),
+                    ("y_situ_4_none", dict(activation="situ", situ_beta=4.0)),
+                    ("y_situ_2_3", dict(activation="situ", situ_beta=2.0, situ_linear_beta=3.0))):
+        y, _ = OM.mega_moe_reference(g["x_deq"], g["topk_idx"], g["topk_weights"], g["l1_deq"], g["l2_deq"], **kw)
+        assert np.array_equal(y, g[tag]), tag
