@@ -158,7 +158,10 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const MoeArgs a) {
 struct MoeFusedHooks {
     uint32_t tile_table, pulled, l1_done, num_tiles_word, layout_ready_word;   // word offsets in the work area
 };
-DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthreads, const MoeFusedHooks* fused) {
+// `scratch`: kMoeScanWords words of shared memory for the layout scan (nullptr: scan in global memory).
+constexpr uint32_t kMoeScanCap = 512, kMoeScanWords = 4 * kMoeScanCap + 1;
+DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthreads, const MoeFusedHooks* fused,
+                                 uint32_t* scratch) {
     const MoeLayout& L = a.L;
     uint32_t* work = reinterpret_cast<uint32_t*>(a.base[a.rank] + L.off_work);
     __shared__ uint32_t s_call, s_ok, s_tiles, s_rows;
@@ -180,18 +183,36 @@ DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthrea
     // Pool layout: expert el owns rows [align(prev_end), end); inside, sources in rank order.
     const uint32_t* recv = reinterpret_cast<const uint32_t*>(a.base[a.rank] + L.off_recv_count);
     int32_t* meta = reinterpret_cast<int32_t*>(a.base[a.rank] + L.off_pool_meta);
+    // The counts come to shared memory in parallel, one thread scans them there (a scan over global memory costs
+    // a round trip per segment: 256 of them at 32 experts x 8 ranks), all threads write the tables out.
+    const uint32_t segs = L.experts_local * L.ranks;
+    uint32_t* s_cnt = scratch;                 // [segs]   rows per (expert, source) segment
+    uint32_t* s_off = scratch + kMoeScanCap;   // [segs]   first pool row of the segment
+    uint32_t* s_pre = scratch + 2 * kMoeScanCap;   // [segs + 1] rows before the segment, unaligned
+    uint32_t* s_end = scratch + 3 * kMoeScanCap + 1;   // [experts_local] end of the expert's rows
+    const bool staged = scratch != nullptr && segs <= kMoeScanCap;
+    if (staged) {
+        for (uint32_t i = tid; i < segs; i += nthreads) s_cnt[i] = recv[(i % L.ranks) * L.experts_local + i / L.ranks];
+        __syncthreads();
+    }
     if (tid == 0) {
         uint32_t prev_end = 0, flat = 0, tiles = 0;
         for (uint32_t el = 0; el < L.experts_local; ++el) {
             const uint32_t start = (prev_end + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
             uint32_t row = start;
             for (uint32_t src = 0; src < L.ranks; ++src) {
-                const uint32_t cnt = recv[src * L.experts_local + el];
-                work[MoeWork::seg_off(L.experts, L.experts_local) + el * L.ranks + src] = row;
-                work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + el * L.ranks + src] = flat;
+                const uint32_t i = el * L.ranks + src;
+                const uint32_t cnt = staged ? s_cnt[i] : recv[src * L.experts_local + el];
+                if (staged) {
+                    s_off[i] = row, s_pre[i] = flat;
+                } else {
+                    work[MoeWork::seg_off(L.experts, L.experts_local) + i] = row;
+                    work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + i] = flat;
+                }
                 row += cnt, flat += cnt;
             }
-            work[MoeWork::psum_end(L.experts) + el] = row;
+            if (staged) s_end[el] = row;
+            else        work[MoeWork::psum_end(L.experts) + el] = row;
             if (a.stats != nullptr) a.stats[el] += static_cast<int32_t>(row - start);
             if (fused != nullptr) {
                 // 256-token tiles over the expert's aligned extent
@@ -206,16 +227,27 @@ DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthrea
             }
             prev_end = row;
         }
-        work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + L.experts_local * L.ranks] = flat;
+        if (staged) s_pre[segs] = flat;
+        else        work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + segs] = flat;
         s_rows = (prev_end + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
         work[MoeWork::kTotalRows] = s_rows;
         s_tiles = tiles;
         if (fused != nullptr) work[fused->num_tiles_word] = tiles;
     }
     __syncthreads();
+    if (staged) {
+        for (uint32_t i = tid; i < segs; i += nthreads) {
+            work[MoeWork::seg_off(L.experts, L.experts_local) + i] = s_off[i];
+            work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + i] = s_pre[i];
+        }
+        if (tid == 0) work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + segs] = s_pre[segs];
+        for (uint32_t el = tid; el < L.experts_local; el += nthreads) work[MoeWork::psum_end(L.experts) + el] = s_end[el];
+        __threadfence();
+    }
+    __syncthreads();
     // Rows between an expert's end and the next boundary carry no token: mark them
     for (uint32_t el = 0; el < L.experts_local; ++el) {
-        const uint32_t end = work[MoeWork::psum_end(L.experts) + el];
+        const uint32_t end = staged ? s_end[el] : work[MoeWork::psum_end(L.experts) + el];
         const uint32_t stop = (end + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
         for (uint32_t r = end + tid; r < stop; r += nthreads) meta[r * 3] = -1;
     }
@@ -230,7 +262,8 @@ DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthrea
 }
 
 __global__ void __launch_bounds__(256) moe_exchange_kernel(const MoeArgs a) {
-    moe_exchange_body(a, threadIdx.x, 256, nullptr);
+    __shared__ uint32_t s_scan[kMoeScanWords];
+    moe_exchange_body(a, threadIdx.x, 256, nullptr, s_scan);
 }
 
 // ---- step 3: pull every routed token (row, packed scales, route weight) into the pool.  One warp per row:

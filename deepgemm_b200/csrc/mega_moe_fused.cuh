@@ -300,7 +300,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
         hooks.tile_table = MoeFusedWork::tile_table(L), hooks.pulled = MoeFusedWork::pulled(L);
         hooks.l1_done = MoeFusedWork::l1_done(L), hooks.num_tiles_word = MoeFusedWork::kNumTiles;
         hooks.layout_ready_word = MoeFusedWork::kLayoutReady;
-        moe_exchange_body(p.a, threadIdx.x, kFusedThreads, &hooks);
+        // the operand stages are idle until the roles start: their first words serve the layout scan
+        moe_exchange_body(p.a, threadIdx.x, kFusedThreads, &hooks, reinterpret_cast<uint32_t*>(smem_gen));
     }
     if (ok) {
         if (threadIdx.x == 0)
