@@ -27,14 +27,6 @@
 
 #include "ptx.cuh"
 
-// Timing experiments only (results are wrong when set): the UMMA issuer does not wait for the shared TMEM columns.
-#ifndef DG_EXPERIMENT_SF_EVERY4
-#define DG_EXPERIMENT_SF_EVERY4 0   // per-32 scales fetched for every fourth K block only
-#endif
-#ifndef DG_EXPERIMENT_NO_OVERLAP_WAIT
-#define DG_EXPERIMENT_NO_OVERLAP_WAIT 0
-#endif
-
 namespace dg {
 
 enum GemmType : uint32_t {
@@ -573,8 +565,8 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
     };
 
     // K-blocks covered by one packed scale word: 4 (one scale per 128 K) or 1 (one per 32 K)
-    const uint32_t sf_mask_r = (p.r.gran_k == 128 || DG_EXPERIMENT_SF_EVERY4 != 0) ? 3 : 0, sf_shift_r = p.r.gran_k == 128 ? 2 : 0;
-    const uint32_t sf_mask_c = (p.c.gran_k == 128 || DG_EXPERIMENT_SF_EVERY4 != 0) ? 3 : 0, sf_shift_c = p.c.gran_k == 128 ? 2 : 0;
+    const uint32_t sf_mask_r = p.r.gran_k == 128 ? 3 : 0, sf_shift_r = p.r.gran_k == 128 ? 2 : 0;
+    const uint32_t sf_mask_c = p.c.gran_k == 128 ? 3 : 0, sf_shift_c = p.c.gran_k == 128 ? 2 : 0;
 
     // Shared by the role loops: smem stage / phase bookkeeping and the schedule walk.
     uint32_t stage = 0, phase = 0;
@@ -715,7 +707,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                     ok = wait_barrier(&bars->tmem_empty[acc], acc_phase ^ 1, abort_flag, peer_abort, p,
                                       kSiteMmaTmemEmpty, acc_iter, 0, acc);
                     if (!ok) break;
-                    if (Cfg::kOverlap > 0 && acc_iter > 0 && !DG_EXPERIMENT_NO_OVERLAP_WAIT) {
+                    if (Cfg::kOverlap > 0 && acc_iter > 0) {
                         // The previous tile's epilogue must have drained the columns both stages share
                         const uint32_t prev = acc_iter - 1;
                         ok = wait_barrier(&bars->overlap[prev & 1], (prev >> 1) & 1, abort_flag, peer_abort, p,
@@ -735,11 +727,11 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                         tc_fence_after();
                         if (elect_one()) {
                             // Fresh scale factors: shared memory (already in 32x4 order) -> TMEM
-                            if ((kb & sf_mask_r) == 0 || (DG_EXPERIMENT_SF_EVERY4 == 2 && p.r.gran_k != 128)) {
+                            if ((kb & sf_mask_r) == 0) {
                                 const uint32_t a = smem_sfr + stage * Cfg::SFR_STAGE;
                                 utccp_32x128b_warpx4<kCtas>(sfr_tmem, sf_desc_hi | (a >> 4));
                             }
-                            if ((kb & sf_mask_c) == 0 || (DG_EXPERIMENT_SF_EVERY4 == 2 && p.c.gran_k != 128)) {
+                            if ((kb & sf_mask_c) == 0) {
 #pragma unroll
                                 for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i) {
                                     const uint32_t a = smem_sfc + stage * Cfg::SFC_STAGE + i * 512;

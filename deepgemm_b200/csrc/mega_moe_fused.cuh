@@ -18,9 +18,6 @@
 
 namespace dg {
 
-#ifndef DG_EXPERIMENT_PULL_FIRST
-#define DG_EXPERIMENT_PULL_FIRST 0   // timing study: the whole CTA pulls before the GEMM roles start
-#endif
 constexpr uint32_t kFusedThreads = 544;   // 17 warps: 0 weight copies, 1 UMMA, 2 + 8..11 pull, 3 scale copies, 12 token copies,
                                           // 4..7 and 13..16 the two epilogue groups
 
@@ -325,10 +322,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     }
     __syncthreads();
 
-#if DG_EXPERIMENT_PULL_FIRST
-    if (ok) moe_pull_rows(p.a, s_prefix, blockIdx.x * (kFusedThreads / 32) + warp, p.num_ctas * (kFusedThreads / 32), lane, pulled);
-    __syncthreads();
-#endif
     DG_FUSED_STAMP(1);
     uint32_t stage = 0, phase = 0;
     auto advance = [&]() {
@@ -544,7 +537,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     } else if (ok) {
         // ============================================================ pull warps (2, 8..11): fill the pool in pool order
         const uint32_t pw = warp == 2 ? 0 : warp - 7;   // 0..4
-        if (!DG_EXPERIMENT_PULL_FIRST) moe_pull_rows(p.a, s_prefix, blockIdx.x * 5 + pw, p.num_ctas * 5, lane, pulled);
+        moe_pull_rows(p.a, s_prefix, blockIdx.x * 5 + pw, p.num_ctas * 5, lane, pulled);
     }
 
     DG_FUSED_FLUSH();
