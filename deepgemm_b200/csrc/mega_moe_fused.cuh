@@ -303,7 +303,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     if (ok) {
         if (threadIdx.x == 0)
             ok = fused_wait_counter(work + MoeFusedWork::kLayoutReady, call_new, abort_flag, p.a, 202, call_new);
-        // every thread needs the verdict and the layout
+        // every thread needs the outcome and the layout
         __shared__ uint32_t s_layout_ok;
         if (threadIdx.x == 0) s_layout_ok = ok ? 1u : 0u;
         __syncthreads();
