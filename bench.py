@@ -235,6 +235,26 @@ def other_configs(device, steps, warmup):
     out["c3_masked_16x(256 of 1024)x4096x7168"] = dict(ms=ms, tflops=2.0 * valid * n * k / ms / 1e9,
                                                        gbs=nbytes / ms / 1e6)
     del a_q, a_s, b_q, b_s, d
+    # K-grouped TN (weight-gradient shape of the reference's tests, tests/generators.py:251-254): 4 groups,
+    # D[g] = A[k_g, :]^T B[k_g, :], m 4096, n 7168, k 8192 per group, FP32 accumulate into D
+    g, m, n, kk = 4, 4096, 7168, 8192
+    ks = [kk] * g
+    a = torch.empty((g * kk, m), dtype=torch.float8_e4m3fn, device=device)
+    b = torch.empty((g * kk, n), dtype=torch.float8_e4m3fn, device=device)
+    sa = torch.empty((g * kk // 128, m), dtype=torch.float32, device=device)
+    sb = torch.empty((g * kk // 128, n), dtype=torch.float32, device=device)
+    for i in range(g):
+        r = slice(i * kk, (i + 1) * kk)
+        rs = slice(i * kk // 128, (i + 1) * kk // 128)
+        a[r], sa[rs] = dg.utils.per_channel_cast_to_fp8(torch.randn((kk, m), device=device, dtype=torch.bfloat16), True, 128)
+        b[r], sb[rs] = dg.utils.per_channel_cast_to_fp8(torch.randn((kk, n), device=device, dtype=torch.bfloat16), True, 128)
+    layout = torch.tensor(ks, dtype=torch.int32, device=device)
+    d = torch.zeros((g, m, n), dtype=torch.float32, device=device)
+    t = time_steps(lambda: dg.k_grouped_fp8_gemm_tn_contiguous((a, sa), (b, sb), d, ks, layout, c=d), steps, warmup, flush)
+    ms = sorted(t)[len(t) // 2]
+    out["k_grouped_tn_4x4096x7168x8192_fp32_accumulate"] = dict(ms=ms, tflops=2.0 * g * m * n * kk / ms / 1e9,
+                                                                note="includes packing the FP32 scales (2 launches)")
+    del a, b, sa, sb, d
     # Fused activation cast (BF16 -> E4M3 + UE8M0 scales in GEMM-ready layout): HBM bound, 3 + 1/gran bytes per element
     for rows, cols, gran in ((4096, 7168, 32), (65536, 7168, 128)):
         x = torch.randn((rows, cols), device=device, dtype=torch.bfloat16)
