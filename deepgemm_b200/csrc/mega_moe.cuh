@@ -211,9 +211,13 @@ DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthrea
                 }
                 row += cnt, flat += cnt;
             }
-            if (staged) s_end[el] = row;
-            else        work[MoeWork::psum_end(L.experts) + el] = row;
-            if (a.stats != nullptr) a.stats[el] += static_cast<int32_t>(row - start);
+            if (staged) {
+                s_end[el] = row;
+                s_cnt[el] = row - start;   // the expert's row count, for the statistics (entry el is consumed by now)
+            } else {
+                work[MoeWork::psum_end(L.experts) + el] = row;
+                if (a.stats != nullptr) a.stats[el] += static_cast<int32_t>(row - start);
+            }
             if (fused != nullptr) {
                 // 256-token tiles over the expert's aligned extent
                 const uint32_t total = row - start;
@@ -241,7 +245,11 @@ DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthrea
             work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + i] = s_pre[i];
         }
         if (tid == 0) work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + segs] = s_pre[segs];
-        for (uint32_t el = tid; el < L.experts_local; el += nthreads) work[MoeWork::psum_end(L.experts) + el] = s_end[el];
+        for (uint32_t el = tid; el < L.experts_local; el += nthreads) {
+            work[MoeWork::psum_end(L.experts) + el] = s_end[el];
+            // one thread per expert: a serial read-modify-write per expert costs a memory round trip each
+            if (a.stats != nullptr) a.stats[el] += static_cast<int32_t>(s_cnt[el]);
+        }
         __threadfence();
     }
     __syncthreads();
