@@ -335,12 +335,21 @@ def mega_moe_bench(device, group, rank, world, steps, warmup, tokens=4096, exper
         return float(t.item()), float(rows.item())
 
     ms_phase, _ = timed(False)            # one launch per phase (7 kernels)
+    y_phase = y.clone()
     ms, rows = timed(True)                # the library's default: one persistent kernel
+    # full-size property: the two paths sum in the same order, so their outputs agree bit for bit on every rank
+    agree = torch.tensor([1.0 if torch.equal(y, y_phase) and bool(torch.isfinite(y.float()).all()) else 0.0],
+                         device=device, dtype=torch.float64)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+    del y_phase
     flops = 2.0 * rows * hidden * inter * 3
     buf.destroy()
     return dict(ep=world, tokens_per_rank=tokens, experts=experts, topk=topk, hidden=hidden, intermediate=inter,
                 ms_per_step=ms, tokens_per_s=world * tokens / ms * 1e3, rows_per_rank_max=rows,
                 tflops_per_gpu=flops / ms / 1e9, gpu_launches_per_step=1,
+                paths_agree_bitwise=bool(agree.item() == 1.0),
                 per_phase_path=dict(ms_per_step=ms_phase, tokens_per_s=world * tokens / ms_phase * 1e3,
                                     gpu_launches_per_step=7),
                 note="x: 1x32 UE8M0 E4M3 (the kernel's only recipe); weights MXFP4 ~N(0, 0.02); time = max over ranks, "
