@@ -270,7 +270,7 @@ def other_configs(device, steps, warmup):
 
 
 def mega_moe_bench(device, group, rank, world, steps, warmup, tokens=4096, experts_per_rank=32, topk=8, hidden=7168,
-                   inter=2048):
+                   inter=2048, check_tokens=512, check_experts=2):
     """Mega MoE forward of BASELINE config 5 under weak scaling: 32 experts and 4096 tokens per GPU, top-8,
     hidden 7168, intermediate 2048; activations E4M3 with per-32 UE8M0 scales, expert weights MXFP4."""
     import torch
@@ -278,12 +278,15 @@ def mega_moe_bench(device, group, rank, world, steps, warmup, tokens=4096, exper
     experts = experts_per_rank * world
     torch.manual_seed(1000 + rank)
 
+    raw = []                     # (codes, FP32 scales) as quantised, kept for the CPU check
+
     def fp4(n, k, scale):
         q = torch.empty((experts_per_rank, n, k // 2), dtype=torch.int8, device=device)
         sf = torch.empty((experts_per_rank, n, k // 32), dtype=torch.float32, device=device)
         for e in range(experts_per_rank):
             q[e], sf[e] = dg.utils.per_token_cast_to_fp4(torch.randn((n, k), device=device, dtype=torch.bfloat16) * scale,
                                                          True, 32)
+        raw.append((q, sf))
         return q, dg.transform_sf_into_required_layout(sf, n, k, (1, 32), experts_per_rank)
 
     l1, l2 = dg.transform_weights_for_mega_moe(fp4(2 * inter, hidden, 0.02), fp4(hidden, inter, 0.02))
@@ -344,12 +347,39 @@ def mega_moe_bench(device, group, rank, world, steps, warmup, tokens=4096, exper
         import torch.distributed as dist
         dist.all_reduce(agree, op=dist.ReduceOp.MIN)
     del y_phase
+    # full-size parity sample against the CPU oracle (one GPU only): the contributions of the first `check_experts`
+    # experts to the first `check_tokens` tokens, taken from the combine planes (one BF16 row per token and slot)
+    # before the top-k reduction; those experts' weights are dequantised on the host
+    parity = None
+    if world == 1 and check_tokens > 0:
+        import numpy as np
+        from oracle import mega_moe as OM
+        from oracle import quant as OQ
+
+        class LazyDeq:
+            def __init__(self, q, sf):
+                self.q, self.sf, self.shape = q, sf, (q.size(0), q.size(1), q.size(2) * 2)
+
+            def __getitem__(self, e):
+                return OQ.cast_back_from_fp4(self.q[e].cpu().view(torch.uint8).numpy(), self.sf[e].cpu().numpy(), 32)
+
+        n_chk = min(check_tokens, tokens)
+        idx_sub = idx[:n_chk].clone()
+        idx_sub[idx_sub >= check_experts] = -1                       # the oracle skips negative slots
+        x_deq = OQ.cast_back_from_fp8(buf.x[:n_chk].cpu().view(torch.uint8).numpy(), buf.x_sf[:n_chk].cpu().numpy(), 32,
+                                      use_packed_ue8m0=True)
+        ref, counts = OM.mega_moe_reference(x_deq, idx_sub.cpu().numpy(), w[:n_chk].cpu().numpy(), LazyDeq(*raw[0]),
+                                            LazyDeq(*raw[1]))
+        mask = (idx_sub >= 0).t().unsqueeze(-1)                      # [topk, tokens, 1]
+        got = (buf.combine[:, :n_chk].float() * mask).sum(0).to(torch.bfloat16).float().cpu().numpy()
+        parity = dict(tokens=n_chk, experts=check_experts, rows=int(counts.sum()),
+                      calc_diff=float(OQ.calc_diff(got, ref)), tolerance=2e-4)
     flops = 2.0 * rows * hidden * inter * 3
     buf.destroy()
     return dict(ep=world, tokens_per_rank=tokens, experts=experts, topk=topk, hidden=hidden, intermediate=inter,
                 ms_per_step=ms, tokens_per_s=world * tokens / ms * 1e3, rows_per_rank_max=rows,
                 tflops_per_gpu=flops / ms / 1e9, gpu_launches_per_step=1,
-                paths_agree_bitwise=bool(agree.item() == 1.0),
+                paths_agree_bitwise=bool(agree.item() == 1.0), parity_vs_cpu_oracle=parity,
                 per_phase_path=dict(ms_per_step=ms_phase, tokens_per_s=world * tokens / ms_phase * 1e3,
                                     gpu_launches_per_step=7),
                 note="x: 1x32 UE8M0 E4M3 (the kernel's only recipe); weights MXFP4 ~N(0, 0.02); time = max over ranks, "
