@@ -29,7 +29,7 @@ from . import cast  # noqa: F401,E402
 from .cast import per_token_cast_to_fp8_fused  # noqa: F401,E402
 from .mega import (  # noqa: F401,E402
     SymmBuffer, get_symm_buffer_for_mega_moe, transform_weights_for_mega_moe, fp8_fp4_mega_moe,
-    get_token_alignment_for_mega_moe, get_block_m_for_mega_moe,
+    get_token_alignment_for_mega_moe, get_block_m_for_mega_moe, RouteWeightMode,
 )
 
 __version__ = "0.1.0"

@@ -56,7 +56,8 @@ class MoeArgs(C.Structure):
                 ("l1_w", C.c_void_p), ("l1_sf", C.c_void_p), ("l2_w", C.c_void_p), ("l2_sf", C.c_void_p),
                 ("l1_sf_ld", C.c_int64), ("l2_sf_ld", C.c_int64), ("stats", C.c_void_p),
                 ("activation_clamp", C.c_float), ("fast_math", C.c_int32), ("stream", C.c_void_p),
-                ("activation", C.c_int32), ("situ_beta", C.c_float), ("situ_linear_beta", C.c_float)]
+                ("activation", C.c_int32), ("situ_beta", C.c_float), ("situ_linear_beta", C.c_float),
+                ("post_down", C.c_int32)]
 
 
 class GemmNoAllocArgs(C.Structure):

@@ -83,6 +83,8 @@ struct MoeEpilogueParams {
     uint32_t activation;       // 0 SwiGLU, 1 GeGLU (tanh form), 2 SiTU
     float situ_beta;           // SiTU: beta * tanh(gate / beta) * sigmoid(gate)
     float situ_linear_beta;    // SiTU: up -> lb * tanh(up / lb); +inf = up unchanged
+    uint32_t post_down;        // route weight applied to the BF16 layer-2 row at the combine write instead of to the
+                               // layer-2 input (impls/sm100_fp8_fp4_mega_moe.cuh:1538-1566 of the reference)
 };
 
 // Position of pool row `row` inside its 128-row group in the order tcgen05.cp.32x128b.warpx4 copies to TMEM.
@@ -405,7 +407,7 @@ DG_DEVICE void moe_l1_chunk_impl(const MoeEpilogueParams& m, const uint8_t* stag
     // thread = 32 interleaved rows laid out as 2 x [8 gate | 8 up] (the weights come
     // interleaved in blocks of 8 rows); the two halves of a group share their amax.
     const uint32_t t = q * 8 + (lane >> 2), g = (lane >> 1) & 1, half = lane & 1;
-    const float w = wtab[min(ch * 32 + t, 255u)];
+    const float w = m.post_down ? 1.0f : wtab[min(ch * 32 + t, 255u)];
     const float clamp = m.clamp, beta = m.situ_beta, lin_beta = m.situ_linear_beta;
     const bool squash_up = lin_beta < 3.0e38f;
     (void)beta, (void)squash_up;
@@ -485,14 +487,25 @@ DG_DEVICE void moe_l1_chunk(const MoeEpilogueParams& m, const uint8_t* stage, ui
 // One 32-token chunk of the second expert GEMM's epilogue: 16 lanes move one token's 256 B segment of BF16
 // results to that token's slot plane in its source rank's buffer (dtab: per-token destination row address, 0 = none).
 DG_DEVICE void moe_l2_chunk(const uint8_t* stage, uint32_t pitch, const uint64_t* dtab, uint32_t et, uint32_t ch,
-                            uint32_t chunk_rows, uint32_t n0) {
-    // 32 tokens x 256 B: 16 lanes move one token's 256 B segment to its source rank
+                            uint32_t chunk_rows, uint32_t n0, const float* row_w) {
+    // 32 tokens x 256 B: 16 lanes move one token's 256 B segment to its source rank.  row_w (post-down route
+    // weights, one per pool row of the tile, or nullptr): every BF16 value is multiplied by its row's weight and
+    // rounded to BF16 again.
 #pragma unroll
     for (uint32_t i = 0; i < 4; ++i) {
         const uint32_t piece = i * 128 + et, t = piece >> 4, part = piece & 15;
         const uint64_t base = t < chunk_rows ? dtab[ch * 32 + t] : 0;
         if (base != 0) {
-            const uint4 val = *reinterpret_cast<const uint4*>(stage + t * pitch + part * 16);
+            uint4 val = *reinterpret_cast<const uint4*>(stage + t * pitch + part * 16);
+            if (row_w != nullptr) {
+                const float w = row_w[ch * 32 + t];
+                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&val);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(h[j]);
+                    h[j] = __floats2bfloat162_rn(f.x * w, f.y * w);
+                }
+            }
             *reinterpret_cast<uint4*>(base + static_cast<uint64_t>(n0) * 2 + part * 16) = val;
         }
     }
@@ -950,7 +963,8 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                             moe_l1_chunk(p.moe, stage_gen, Cfg::MOE_PITCH, reinterpret_cast<const float*>(table), q, lane, ch,
                                          chunk_rows, m0, n0);
                         else
-                            moe_l2_chunk(stage_gen, Cfg::MOE_PITCH, table, q * 32 + lane, ch, chunk_rows, n0);
+                            moe_l2_chunk(stage_gen, Cfg::MOE_PITCH, table, q * 32 + lane, ch, chunk_rows, n0,
+                                         p.moe.post_down ? p.moe.pool_w + m0 : nullptr);
                         moe_buf ^= 1;
                     }
                 }

@@ -625,6 +625,7 @@ static void fill_moe_gemm_args(const dg_moe_args& m, const dg::MoeArgs& a, dg::M
     e->off_combine = L.off_combine, e->pool_rows = L.pool_rows, e->inter = L.inter, e->hidden = L.hidden, e->t_max = L.t_max;
     e->clamp = m.activation_clamp, e->fast_math = m.fast_math ? 1 : 0;
     e->activation = static_cast<uint32_t>(m.activation);
+    e->post_down = m.post_down ? 1u : 0u;
     e->situ_beta = m.situ_beta > 0.0f ? m.situ_beta : 1.0f;
     e->situ_linear_beta = m.situ_linear_beta > 0.0f ? m.situ_linear_beta : INFINITY;
     dg_gemm_args g;

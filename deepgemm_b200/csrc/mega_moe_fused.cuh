@@ -518,7 +518,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                 if (tc.kind == 0)
                     DG_EPI_TIMED(3, moe_l1_chunk(p.e, stage_gen, Cfg::PITCH, reinterpret_cast<const float*>(ttab), q, lane, ch, chunk_rows, tc.row0, n0); __syncwarp(););
                 else
-                    DG_EPI_TIMED(4, moe_l2_chunk(stage_gen, Cfg::PITCH, ttab, q * 32 + lane, ch, chunk_rows, n0); __syncwarp(););
+                    DG_EPI_TIMED(4, moe_l2_chunk(stage_gen, Cfg::PITCH, ttab, q * 32 + lane, ch, chunk_rows, n0, p.e.post_down ? p.e.pool_w + tc.row0 : nullptr); __syncwarp(););
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_read);
                 ++chunks_done;

@@ -9,6 +9,7 @@ movement happens in the library's kernels through peer loads / stores.
 from __future__ import annotations
 
 import ctypes as C
+import enum
 import math
 import types
 from typing import Optional, Tuple
@@ -36,6 +37,13 @@ def get_block_m_for_mega_moe(num_ranks: int, num_experts: int, num_max_tokens_pe
 
 
 _ACTIVATIONS = {"swiglu": 0, "geglu": 1, "situ": 2}
+
+
+class RouteWeightMode(enum.Enum):
+    """Where the route weight enters (deep_gemm/mega/__init__.py RouteWeightMode): before the second GEMM's input is
+    quantised, or on the second GEMM's BF16 output at the combine write."""
+    PRE_DOWN = "pre_down"
+    POST_DOWN = "post_down"
 
 
 class SymmBuffer:
@@ -180,8 +188,9 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tens
     for name, val in unsupported.items():
         if val is not None and name not in ("route_weight_mode", "num_config_tokens"):
             raise NotImplementedError(f"`{name}` is not part of this build")
-    if str(unsupported.get("route_weight_mode", "pre_down")).split(".")[-1].lower() not in ("pre_down",):
-        raise NotImplementedError("only route_weight_mode='pre_down' is part of this build")
+    mode = unsupported.get("route_weight_mode", "pre_down")
+    mode = (mode.value if isinstance(mode, RouteWeightMode) else str(mode).split(".")[-1]).lower()
+    _require(mode in ("pre_down", "post_down"), "route_weight_mode in ('pre_down', 'post_down')")
     _require(tuple(recipe) == (1, 1, 32), "recipe == (1, 1, 32)")
     _require(activation in _ACTIVATIONS, "activation in ('swiglu', 'geglu', 'situ')")
     b = sym_buffer
@@ -211,6 +220,7 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights: Tuple[torch.Tensor, torch.Tens
     args.fast_math = int(bool(fast_math))
     # SiTU parameters are ignored by the other activations (tests/test_mega_moe.py:551-559 of the reference)
     args.activation = _ACTIVATIONS[activation]
+    args.post_down = int(mode == "post_down")
     args.situ_beta = 0.0 if situ_beta is None else float(situ_beta)
     args.situ_linear_beta = 0.0 if situ_linear_beta is None else float(situ_linear_beta)
     args.stream = _stream(y)

@@ -169,6 +169,11 @@ typedef struct dg_moe_args {
      * situ_beta <= 0 means the default 1. */
     int32_t activation;
     float situ_beta, situ_linear_beta;
+    /* 0 (pre-down, default): the route weight multiplies the gated activation before it is requantised for the
+     * second GEMM.  1 (post-down): the activation stays unweighted and each BF16 row of the second GEMM's output
+     * is multiplied by its route weight and rounded to BF16 again where it is written to the combine plane
+     * (impls/sm100_fp8_fp4_mega_moe.cuh:1538-1566 of the reference). */
+    int32_t post_down;
 } dg_moe_args;
 
 /* y[t] = bf16( sum over slots of bf16( Q32( SwiGLU(bf16(x_t W13_e^T)) * w_{t,slot} ) W2_e^T ) ) with the tokens

@@ -156,6 +156,41 @@ def test_mega_moe_gated_activations():
         assert H.calc_diff(y, swiglu_ref) > 50 * MOE_TOL, (beta, lin)
 
 
+@pytest.mark.parametrize("fused", [True, False])
+def test_mega_moe_post_down_route_weights(fused):
+    """route_weight_mode='post_down': the gated activation is requantised unweighted and the BF16 row of the second
+    GEMM is multiplied by its route weight (and rounded again) at the combine write
+    (impls/sm100_fp8_fp4_mega_moe.cuh:1538-1566 of the reference).  Against the oracle's statement of that boundary;
+    the result must differ from the pre-down one (the two modes round at different places)."""
+    hidden, inter, experts, topk, tokens = 2048, 1024, 16, 4, 300
+    (q1, sf1, deq1), (q2, sf2, deq2) = make_weights(experts, hidden, inter)
+    l1 = (q1, dg.transform_sf_into_required_layout(sf1, 2 * inter, hidden, (1, 32), experts))
+    l2 = (q2, dg.transform_sf_into_required_layout(sf2, hidden, inter, (1, 32), experts))
+    l1, l2 = dg.transform_weights_for_mega_moe(l1, l2)
+    x_fp8, x_sf, idx, w, x_deq = make_inputs(tokens, hidden, experts, topk, 321, drop=9)
+    buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter)
+    dg.mega.set_fused(fused)
+    try:
+        outs = {}
+        for mode in (dg.RouteWeightMode.POST_DOWN, "pre_down"):
+            buf.x[:tokens].copy_(x_fp8), buf.x_sf[:tokens].copy_(x_sf)
+            buf.topk_idx[:tokens].copy_(idx), buf.topk_weights[:tokens].copy_(w)
+            y = torch.full((tokens, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+            dg.fp8_fp4_mega_moe(y, l1, l2, buf, route_weight_mode=mode)
+            torch.cuda.synchronize()
+            dg.check_status()
+            outs[str(mode)] = H.to_np(y)
+        ref = OM.mega_moe_reference(x_deq, idx.cpu().numpy(), w.cpu().numpy(), deq1, deq2,
+                                    route_weight_mode="post_down")[0]
+        got = outs[str(dg.RouteWeightMode.POST_DOWN)]
+        assert not np.isnan(got).any()
+        assert H.calc_diff(got, ref) < MOE_TOL
+        assert not np.array_equal(got, outs["pre_down"])
+    finally:
+        dg.mega.set_fused(True)
+        buf.destroy()
+
+
 def _worker(local_rank, ranks, cfg, port, results):
     import torch.distributed as dist
     torch.cuda.set_device(local_rank)
