@@ -136,3 +136,21 @@ def test_mega_moe_buffer_layout_and_checks():
     assert _lib.lib().dg_mega_moe_buffer_layout(ctypes.byref(bad), ctypes.byref(lay)) != 0
     assert b"num_experts" in _lib.lib().dg_last_error()
     assert dg.get_token_alignment_for_mega_moe() == 128
+
+
+def test_header_is_plain_c_and_library_answers_without_gpu(tmp_path):
+    """include/deepgemm_b200.h compiles as C; a C program dlopens the library, finds every exported symbol and gets
+    answers from the entry points that touch no device (tests/c_abi/abi_check.c)."""
+    import shutil
+    import subprocess
+    from deepgemm_b200 import _lib
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no gcc")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "abi_check")
+    subprocess.run([gcc, "-std=c11", "-Wall", "-Werror", "-I", os.path.join(root, "include"),
+                    os.path.join(root, "tests", "c_abi", "abi_check.c"), "-o", exe, "-ldl"], check=True)
+    res = subprocess.run([exe, _lib.LIB_PATH, *_lib.EXPORTS], capture_output=True, text=True)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "align=128" in res.stdout and "bad_rc=" in res.stdout
