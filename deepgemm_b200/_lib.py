@@ -19,7 +19,7 @@ EXPORTS = (
     "dg_get_mk_alignment_for_contiguous_layout", "dg_get_theoretical_mk_alignment_for_contiguous_layout",
     "dg_set_wait_timeout_ms", "dg_check_status", "dg_last_error", "dg_version",
     "dg_mega_moe_buffer_layout", "dg_get_token_alignment_for_mega_moe", "dg_mega_moe_forward", "dg_set_mega_moe_fused", "dg_gemm_fp8_fp32sf_noalloc", "dg_noalloc_scratch_bytes",
-    "dg_per_token_cast_to_fp8",
+    "dg_per_token_cast_to_fp8", "dg_debug_set_tile_override", "dg_get_mega_moe_num_sms", "dg_debug_copy",
 )
 
 
@@ -34,14 +34,12 @@ class GemmArgs(C.Structure):
                 ("a", Operand), ("b", Operand),
                 ("d", C.c_void_p), ("ldd", C.c_int64), ("d_dtype", C.c_int32), ("accumulate", C.c_int32),
                 ("alpha", C.c_float), ("expected_m", C.c_int32),
-                ("grouped_layout", C.c_void_p), ("stream", C.c_void_p),
-                ("force_cta_group", C.c_int32), ("force_block_n", C.c_int32), ("force_swap", C.c_int32),
-                ("reserved", C.c_int32)]
+                ("grouped_layout", C.c_void_p), ("stream", C.c_void_p)]
 
 
 class MoeConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("num_ranks", "num_experts", "num_max_tokens_per_rank", "num_topk", "hidden",
-                                          "intermediate_hidden")]
+                                          "intermediate_hidden", "num_ring_tokens", "reserved")]
 
 
 class MoeLayout(C.Structure):
@@ -104,6 +102,8 @@ def lib() -> C.CDLL:
                      "dg_get_theoretical_mk_alignment_for_contiguous_layout", "dg_set_wait_timeout_ms",
                      "dg_set_mega_moe_fused"):
             getattr(l, name).argtypes = [C.c_int32]
+        l.dg_debug_set_tile_override.argtypes = [C.c_int32, C.c_int32, C.c_int32]
+        l.dg_debug_copy.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
         _lib = l
     return _lib
 

@@ -15,7 +15,13 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_DIR = os.path.join(PKG_DIR, "lib")
 LIB_PATH = os.environ.get("DEEPGEMM_B200_LIB") or os.path.join(LIB_DIR, "libdeepgemm_b200.so")
 SOURCES = ["lib.cu"]
-HEADERS = ["ptx.cuh", "gemm_bs.cuh", "sf_pack.cuh", "mega_moe.cuh", os.path.join("..", "..", "include", "deepgemm_b200.h")]
+PUBLIC_HEADER = os.path.join(PKG_DIR, "..", "include", "deepgemm_b200.h")
+
+
+def dependencies():
+    """Every file the library is built from: all sources and headers under csrc/ plus the public header."""
+    files = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith((".cu", ".cuh", ".h"))]
+    return files + [PUBLIC_HEADER]
 
 
 def nvcc_path() -> str:
@@ -29,8 +35,7 @@ def needs_build() -> bool:
     if not os.path.exists(LIB_PATH):
         return True
     t = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
-    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps)
+    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in dependencies())
 
 
 def build(force: bool = False, verbose: bool = False) -> str:

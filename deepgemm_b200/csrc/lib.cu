@@ -57,6 +57,8 @@ struct Knobs {
     int mk_alignment = 128;
     int timeout_ms = 2000;
     int moe_fused = 1;     // Mega MoE: one persistent kernel (1) or the kernel-per-phase path (0)
+    int pdl = 0;           // launch with programmatic stream serialisation
+    int force_cta_group = 0, force_block_n = 0, force_swap = 0;   // dg_debug_set_tile_override
 } g_knobs;
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -127,12 +129,9 @@ struct TileChoice {
 
 template <class Cfg>
 int launch_gemm(dg::GemmParams& p, const dg_gemm_args& a, uint32_t num_units) {
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
     // The attribute is per device; set it on every call (cheap) so that multi-device processes work.
-    attr_err = cudaFuncSetAttribute(dg::gemm_bs_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(Cfg::kSmemBytes));
-    (void)once;
+    const cudaError_t attr_err = cudaFuncSetAttribute(dg::gemm_bs_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                      static_cast<int>(Cfg::kSmemBytes));
     if (attr_err != cudaSuccess)
         return fail(DG_ERR_CUDA, "CUDA error: %s setting %u bytes of dynamic shared memory",
                     cudaGetErrorString(attr_err), Cfg::kSmemBytes);
@@ -261,11 +260,13 @@ int choose_tile(const dg_gemm_args& a, int num_sms, TileChoice* t) {
         c.ctas = (a.m > 128 && num_sms % 2 == 0) ? 2 : 1;
         c.bn = a.n >= 256 ? 256 : 128;
         if (c.ctas == 2 && c.bn == 128 && mn_major_b) c.ctas = 1;   // half tiles of an MN-major B need 128 rows
-        if (a.d_dtype == DG_F32 && false) c.bn = 128;
     }
-    if (a.force_cta_group) c.ctas = a.force_cta_group;
-    if (a.force_block_n) c.bn = a.force_block_n;
-    if (a.force_swap) c.swap = a.force_swap == 2;
+    {
+        std::lock_guard<std::mutex> lk(g_knobs.mu);
+        if (g_knobs.force_cta_group) c.ctas = g_knobs.force_cta_group;
+        if (g_knobs.force_block_n) c.bn = g_knobs.force_block_n;
+        if (g_knobs.force_swap) c.swap = g_knobs.force_swap == 2;
+    }
     *t = c;
     return DG_OK;
 }
@@ -327,9 +328,40 @@ int dg_get_mk_alignment_for_contiguous_layout(void) {
     return g_knobs.mk_alignment;
 }
 int dg_get_theoretical_mk_alignment_for_contiguous_layout(int32_t expected_m) {
+    // UMMA N = 256 makes a fixed 256-row alignment the best choice on sm_100, whatever the expected group size
+    // (csrc/jit_kernels/heuristics/runtime.hpp:57-64 of the reference; expected_m is ignored there too)
     (void)expected_m;
-    return 128;
+    return 256;
 }
+int dg_debug_set_tile_override(int32_t cta_group, int32_t block_n, int32_t swap) {
+    DG_REQUIRE(cta_group >= 0 && cta_group <= 2 && block_n >= 0 && block_n <= 256 && swap >= 0 && swap <= 2, "tile override");
+    std::lock_guard<std::mutex> lk(g_knobs.mu);
+    g_knobs.force_cta_group = cta_group, g_knobs.force_block_n = block_n, g_knobs.force_swap = swap;
+    return DG_OK;
+}
+// Plain 16-byte loads / stores, four in flight per thread: the access pattern of the Mega MoE token pull
+__global__ void __launch_bounds__(256) debug_copy_kernel(uint4* dst, const uint4* src, uint64_t n_vec) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * 256;
+    uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
+    for (; i + 3 * stride < n_vec; i += 4 * stride) {
+        const uint4 v0 = src[i], v1 = src[i + stride], v2 = src[i + 2 * stride], v3 = src[i + 3 * stride];
+        dst[i] = v0, dst[i + stride] = v1, dst[i + 2 * stride] = v2, dst[i + 3 * stride] = v3;
+    }
+    for (; i < n_vec; i += stride) dst[i] = src[i];
+}
+
+int dg_debug_copy(void* dst, const void* src, int64_t bytes, void* stream) {
+    DG_REQUIRE(dst != nullptr && src != nullptr && bytes >= 0 && bytes % 16 == 0, "dst / src / bytes % 16 == 0");
+    DG_REQUIRE(reinterpret_cast<uintptr_t>(dst) % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0, "16-byte alignment");
+    if (bytes == 0) return DG_OK;
+    int num_sms = dg_get_num_sms();
+    DG_REQUIRE(num_sms > 0, "num_sms");
+    debug_copy_kernel<<<num_sms * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint4*>(dst), static_cast<const uint4*>(src), static_cast<uint64_t>(bytes) / 16);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
 int dg_set_wait_timeout_ms(int32_t ms) {
     DG_REQUIRE(ms > 0, "timeout");
     std::lock_guard<std::mutex> lk(g_knobs.mu);
@@ -454,7 +486,10 @@ static int run_gemm(const dg_gemm_args& a, int epi, const dg::MoeEpilogueParams*
     DG_REQUIRE(num_sms > 0, "num_sms");
     TileChoice t;
     choose_tile(a, num_sms, &t);
-    if (epi != 0) t.swap = true, t.bn = a.force_block_n ? a.force_block_n : 256;
+    if (epi != 0) {
+        std::lock_guard<std::mutex> lk(g_knobs.mu);
+        t.swap = true, t.bn = g_knobs.force_block_n ? g_knobs.force_block_n : 256;
+    }
     DG_REQUIRE(t.ctas == 1 || t.ctas == 2, "cta group");
     DG_REQUIRE(!(t.swap && a.d_dtype == DG_F32), "swapped tiles write BF16 only");
     DG_REQUIRE(!(t.swap && a.accumulate), "swapped tiles do not accumulate");
@@ -604,8 +639,10 @@ int dg_gemm_bs(const dg_gemm_args* args) {
 static int check_moe_config(const dg_moe_config& c) {
     DG_REQUIRE(c.num_ranks > 0 && c.num_ranks <= static_cast<int>(dg::kMoeMaxRanks), "num_ranks");
     DG_REQUIRE(c.num_experts > 0 && c.num_experts % c.num_ranks == 0, "num_experts % num_ranks == 0");
+    DG_REQUIRE(c.num_experts <= static_cast<int>(dg::kMoeMaxExperts), "num_experts <= 4032");
     DG_REQUIRE(c.num_topk > 0 && c.num_topk <= c.num_experts, "num_topk");
     DG_REQUIRE(c.num_max_tokens_per_rank > 0, "num_max_tokens_per_rank");
+    DG_REQUIRE(c.num_ring_tokens >= 0, "num_ring_tokens >= 0");
     DG_REQUIRE(c.hidden > 0 && c.hidden % 128 == 0 && c.intermediate_hidden > 0 && c.intermediate_hidden % 128 == 0,
                "hidden % 128 == 0 and intermediate_hidden % 128 == 0");
     return DG_OK;
@@ -631,7 +668,7 @@ static void fill_moe_gemm_args(const dg_moe_args& m, const dg::MoeArgs& a, dg::M
     dg_gemm_args g;
     memset(&g, 0, sizeof(g));
     g.gemm_type = DG_GEMM_M_PSUM, g.num_groups = L.experts_local, g.alignment = dg::kMoePoolAlign;
-    g.grouped_layout = reinterpret_cast<const int32_t*>(mine + L.off_work) + dg::MoeWork::psum_end(L.experts);
+    g.grouped_layout = reinterpret_cast<const int32_t*>(mine + L.off_work) + dg::MoeWork::psum_end();
     g.stream = m.stream, g.alpha = 1.0f, g.d_dtype = DG_BF16;
     g.m = L.pool_rows, g.n = 2 * L.inter, g.k = L.hidden;
     g.a.data = mine + L.off_l1_acts, g.a.sf = reinterpret_cast<const int32_t*>(mine + L.off_l1_sf);
@@ -643,6 +680,25 @@ static void fill_moe_gemm_args(const dg_moe_args& m, const dg::MoeArgs& a, dg::M
     g.a.data = mine + L.off_l2_acts, g.a.sf = reinterpret_cast<const int32_t*>(mine + L.off_l2_sf), g.a.ld = L.inter;
     g.b.data = m.l2_w, g.b.sf = m.l2_sf, g.b.ld = L.inter / 2, g.b.sf_ld = m.l2_sf_ld;
     *g2 = g;
+}
+
+// SMs the persistent Mega MoE grid may take: the num_sms knob (at most the device's SMs: every CTA must be resident at
+// the same time for the kernel's grid barrier) minus DG_MEGA_MOE_SM_HEADROOM rounded up to even, which leaves room for
+// kernels of other streams that run beside it (csrc/jit_kernels/impls/runtime_utils.hpp:35-82 of the reference).
+static int mega_moe_num_sms(int* out) {
+    int num_sms = dg_get_num_sms();
+    DG_REQUIRE(num_sms > 0, "num_sms");
+    int device_sms = 0;
+    if (device_sm_count(&device_sms) == DG_OK && device_sms > 0 && num_sms > device_sms) num_sms = device_sms;
+    int headroom = 0;
+    if (const char* env = getenv("DG_MEGA_MOE_SM_HEADROOM")) headroom = atoi(env);
+    DG_REQUIRE(headroom >= 0, "DG_MEGA_MOE_SM_HEADROOM must be non-negative");
+    headroom = (headroom + 1) / 2 * 2;
+    DG_REQUIRE(headroom < num_sms, "DG_MEGA_MOE_SM_HEADROOM leaves no SMs for the mega-MoE grid");
+    num_sms -= headroom;
+    DG_REQUIRE(num_sms % 2 == 0, "num_sms % 2 == 0");
+    *out = num_sms;
+    return DG_OK;
 }
 
 static int launch_moe_fused(const dg_moe_args& m, const dg::MoeArgs& a, int num_sms) {
@@ -669,11 +725,7 @@ static int launch_moe_fused(const dg_moe_args& m, const dg::MoeArgs& a, int num_
     p.y = static_cast<__nv_bfloat16*>(m.y), p.ldy = m.ldy;
     p.num_ctas = static_cast<uint32_t>(num_sms) / 2 * 2;
     p.trace = g_trace;
-    {
-        const char* env = getenv("DG_MEGA_MOE_LAG");   // tuning aid
-        p.lag = env != nullptr ? static_cast<uint32_t>(atoi(env)) : 8;
-        if (p.lag < 1) p.lag = 1;
-    }
+    p.lag = 8;
     DG_CUDA(cudaFuncSetAttribute(dg::mega_moe_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(dg::FusedCfg::kSmemBytes)));
     cudaLaunchConfig_t cfg;
@@ -696,13 +748,18 @@ int dg_set_mega_moe_fused(int32_t enable) {
 
 int dg_get_token_alignment_for_mega_moe(void) { return 128; }
 
+int dg_get_mega_moe_num_sms(void) {
+    int n = 0;
+    return mega_moe_num_sms(&n) == DG_OK ? n : -1;
+}
+
 int dg_mega_moe_buffer_layout(const dg_moe_config* cfg, dg_moe_layout* out) {
     DG_REQUIRE(cfg != nullptr && out != nullptr, "null argument");
     int rc = check_moe_config(*cfg);
     if (rc != DG_OK) return rc;
     DG_REQUIRE(cfg->num_max_tokens_per_rank % dg_get_token_alignment_for_mega_moe() == 0, "token alignment");
     const dg::MoeLayout L = dg::make_moe_layout(cfg->num_ranks, cfg->num_experts, cfg->num_max_tokens_per_rank,
-                                                cfg->num_topk, cfg->hidden, cfg->intermediate_hidden);
+                                                cfg->num_topk, cfg->hidden, cfg->intermediate_hidden, cfg->num_ring_tokens);
     out->num_bytes = static_cast<int64_t>(L.total_bytes);
     out->pool_rows = static_cast<int64_t>(L.pool_rows);
     out->off_x = L.off_x, out->off_x_sf = L.off_x_sf, out->off_topk_idx = L.off_topk_idx;
@@ -723,7 +780,7 @@ int dg_mega_moe_forward(const dg_moe_args* args) {
     DG_REQUIRE(m.l1_w && m.l1_sf && m.l2_w && m.l2_sf, "null weights");
     DG_REQUIRE(m.activation >= DG_ACT_SWIGLU && m.activation <= DG_ACT_SITU, "activation");
     const dg::MoeLayout L = dg::make_moe_layout(m.cfg.num_ranks, m.cfg.num_experts, m.cfg.num_max_tokens_per_rank,
-                                                m.cfg.num_topk, m.cfg.hidden, m.cfg.intermediate_hidden);
+                                                m.cfg.num_topk, m.cfg.hidden, m.cfg.intermediate_hidden, m.cfg.num_ring_tokens);
     dg::MoeArgs a;
     memset(&a, 0, sizeof(a));
     a.L = L;
@@ -741,8 +798,9 @@ int dg_mega_moe_forward(const dg_moe_args* args) {
     a.status = static_cast<uint32_t*>(status_ptr);
     a.stats = m.stats;
     cudaStream_t stream = static_cast<cudaStream_t>(m.stream);
-    int num_sms = dg_get_num_sms();
-    DG_REQUIRE(num_sms > 0, "num_sms");
+    int num_sms = 0;
+    rc = mega_moe_num_sms(&num_sms);
+    if (rc != DG_OK) return rc;
     bool fused;
     {
         std::lock_guard<std::mutex> lk(g_knobs.mu);

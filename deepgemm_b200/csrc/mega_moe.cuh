@@ -19,11 +19,27 @@ namespace dg {
 constexpr uint32_t kMoeMaxRanks = 16;
 constexpr uint32_t kMoePoolAlign = 128;   // rows: every expert's pool segment starts on this boundary
 
+// The first kMoeCtrlBytes of every buffer hold the control block: words whose meaning and place do not depend on the
+// configuration (num_experts, tokens, hidden ...), so that a buffer may be reused for another configuration between
+// calls (SymmBuffer(base=...)): barrier flags and their epoch, the grid barrier, the per-expert send counters.
+// Everything after it is rewritten by each call before it is read.
+constexpr uint32_t kMoeCtrlBytes = 16384;
+struct MoeCtrl {   // u32 word indices inside the control block
+    static constexpr uint32_t kSignals = 0;      // [2][kMoeMaxRanks]: barrier flags written by peers
+    static constexpr uint32_t kCall = 32;        // calls made so far (epoch of the barrier flags)
+    static constexpr uint32_t kTotalRows = 33;   // pool rows in use, aligned
+    static constexpr uint32_t kGridCount = 34;   // grid barrier: arrivals of the current generation (back to 0 when it opens)
+    static constexpr uint32_t kGridGen = 35;     // grid barrier: generation, bumped by the last arriver
+    static constexpr uint32_t kLayoutReady = 36, kNumTiles = 37, kCombineReady = 38;
+    static constexpr uint32_t kSendCount = 64;   // [experts]: rows this rank sends to each expert (zero between calls)
+};
+constexpr uint32_t kMoeMaxExperts = kMoeCtrlBytes / 4 - MoeCtrl::kSendCount;
+
 // Byte offsets inside one rank's symmetric buffer (identical on every rank).
 struct MoeLayout {
     uint32_t ranks, experts, experts_local, t_max, topk, hidden, inter;
     uint32_t pool_rows;      // capacity of the expert-sorted pool (multiple of 256)
-    uint64_t off_signals;    // u32 [2][kMoeMaxRanks]: barrier flags written by peers
+    uint64_t off_ctrl;       // control block, always 0
     uint64_t off_recv_count; // u32 [ranks][experts_local]: rows each source rank sends to each local expert
     uint64_t off_src_idx;    // u32 [experts_local][ranks][t_max]: token * topk + slot, written by the source rank
     uint64_t off_x, off_x_sf, off_topk_idx, off_topk_w;   // inputs the caller fills
@@ -33,27 +49,20 @@ struct MoeLayout {
     uint64_t total_bytes;
 };
 
-// Local scratch at off_work (u32 words)
+// Local tables at off_work (u32 words), all rewritten by every call
 struct MoeWork {
-    static constexpr uint32_t kCall = 0;        // calls made so far (epoch of the barrier flags)
-    static constexpr uint32_t kTotalRows = 1;   // pool rows in use, aligned
-    static constexpr uint32_t kSendCount = 16;  // [experts]
-    __host__ __device__ static uint32_t psum_end(uint32_t experts) { return kSendCount + experts; }   // [experts_local]
-    __host__ __device__ static uint32_t seg_off(uint32_t experts, uint32_t el) { return psum_end(experts) + el; }
+    __host__ __device__ static uint32_t psum_end() { return 0; }   // [experts_local]: end of each expert's pool rows
+    __host__ __device__ static uint32_t seg_off(uint32_t el) { return el; }
     // [experts_local * ranks]: first pool row of each (expert, source) segment
-    __host__ __device__ static uint32_t seg_prefix(uint32_t experts, uint32_t el, uint32_t ranks) {
-        return seg_off(experts, el) + el * ranks;
-    }   // [experts_local * ranks + 1]: rows before each segment, unaligned (the pull kernel's work list)
-    __host__ __device__ static uint32_t words(uint32_t experts, uint32_t el, uint32_t ranks) {
-        return seg_prefix(experts, el, ranks) + el * ranks + 1;
-    }
+    __host__ __device__ static uint32_t seg_prefix(uint32_t el, uint32_t ranks) { return seg_off(el) + el * ranks; }
+    // [experts_local * ranks + 1]: rows before each segment, unaligned (the pull kernel's work list)
+    __host__ __device__ static uint32_t words(uint32_t el, uint32_t ranks) { return seg_prefix(el, ranks) + el * ranks + 1; }
 };
 
-// Work-area words used only by the fused kernel (after the tables of MoeWork)
+// Work-area tables used only by the fused kernel (after the tables of MoeWork)
 struct MoeFusedWork {
-    static constexpr uint32_t kGridSync = 2, kLayoutReady = 3, kNumTiles = 4, kCombineReady = 5, kFusedCalls = 6;
     __host__ __device__ static uint32_t max_tiles(const MoeLayout& L) { return L.pool_rows / 256 + L.experts_local; }
-    __host__ __device__ static uint32_t tile_table(const MoeLayout& L) { return MoeWork::words(L.experts, L.experts_local, L.ranks); }
+    __host__ __device__ static uint32_t tile_table(const MoeLayout& L) { return MoeWork::words(L.experts_local, L.ranks); }
     // per tile: row0, rows (UMMA N), expert, valid rows in its first 128-row block, valid rows in its second
     __host__ __device__ static uint32_t pulled(const MoeLayout& L) { return tile_table(L) + max_tiles(L) * 8; }   // [pool_rows / 128]
     __host__ __device__ static uint32_t l1_done(const MoeLayout& L) { return pulled(L) + L.pool_rows / 128; }      // [max_tiles]
@@ -62,21 +71,25 @@ struct MoeFusedWork {
 
 inline uint64_t moe_align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 
+// pool_cap: rows the expert-sorted pool must hold; 0 = the worst case (every token of every rank picks this rank's
+// experts with all the slots it can).  A smaller pool makes a call whose rows do not fit fail with kStatusPoolOverflow.
 inline MoeLayout make_moe_layout(uint32_t ranks, uint32_t experts, uint32_t t_max, uint32_t topk, uint32_t hidden,
-                                 uint32_t inter) {
+                                 uint32_t inter, uint32_t pool_cap = 0) {
     MoeLayout L{};
     L.ranks = ranks, L.experts = experts, L.experts_local = experts / ranks, L.t_max = t_max, L.topk = topk;
     L.hidden = hidden, L.inter = inter;
     const uint64_t active_topk = topk < L.experts_local ? topk : L.experts_local;
-    L.pool_rows = static_cast<uint32_t>(moe_align_up(static_cast<uint64_t>(t_max) * ranks * active_topk +
-                                                     static_cast<uint64_t>(L.experts_local) * kMoePoolAlign, 256));
+    const uint64_t slack = static_cast<uint64_t>(L.experts_local) * kMoePoolAlign;   // every expert's rows start on a boundary
+    uint64_t rows = static_cast<uint64_t>(t_max) * ranks * active_topk;
+    if (pool_cap != 0 && pool_cap < rows) rows = pool_cap;
+    L.pool_rows = static_cast<uint32_t>(moe_align_up(rows + slack, 256));
     uint64_t off = 0;
     auto take = [&](uint64_t bytes) {
         const uint64_t o = off;
         off = moe_align_up(off + bytes, 1024);
         return o;
     };
-    L.off_signals = take(2 * kMoeMaxRanks * 4);
+    L.off_ctrl = take(kMoeCtrlBytes);
     L.off_recv_count = take(static_cast<uint64_t>(ranks) * L.experts_local * 4);
     L.off_src_idx = take(static_cast<uint64_t>(L.experts_local) * ranks * t_max * 4);
     L.off_x = take(static_cast<uint64_t>(t_max) * hidden);
@@ -103,7 +116,7 @@ struct MoeArgs {
     int32_t* stats;                // cumulative_local_expert_recv_stats [experts_local] or null
 };
 
-enum : uint32_t { kStatusPeerTimeout = 2 };
+enum : uint32_t { kStatusPeerTimeout = 2, kStatusPoolOverflow = 3 };
 
 DG_DEVICE void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -118,9 +131,9 @@ DG_DEVICE uint32_t ld_acquire_sys(const uint32_t* p) {
 // at least `value`.  Called by threads 0..ranks-1 of one CTA; returns false on timeout.
 DG_DEVICE bool moe_cross_rank_barrier(const MoeArgs& a, uint32_t which, uint32_t value, uint32_t peer) {
     __threadfence_system();
-    uint32_t* remote = reinterpret_cast<uint32_t*>(a.base[peer] + a.L.off_signals) + which * kMoeMaxRanks + a.rank;
+    uint32_t* remote = reinterpret_cast<uint32_t*>(a.base[peer]) + MoeCtrl::kSignals + which * kMoeMaxRanks + a.rank;
     st_release_sys(remote, value);
-    const uint32_t* mine = reinterpret_cast<const uint32_t*>(a.base[a.rank] + a.L.off_signals) + which * kMoeMaxRanks + peer;
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(a.base[a.rank]) + MoeCtrl::kSignals + which * kMoeMaxRanks + peer;
     const uint64_t t0 = global_timer_ns();
     const uint64_t budget = static_cast<uint64_t>(a.timeout_ms) * 1000000ull;
     while (static_cast<int32_t>(ld_acquire_sys(mine) - value) < 0) {
@@ -141,8 +154,11 @@ DG_DEVICE bool moe_cross_rank_barrier(const MoeArgs& a, uint32_t which, uint32_t
 DG_DEVICE void moe_scatter_pair(const MoeArgs& a, uint32_t i) {
     const long long e = reinterpret_cast<const long long*>(a.base[a.rank] + a.L.off_topk_idx)[i];
     if (e < 0 || e >= static_cast<long long>(a.L.experts)) return;
-    uint32_t* work = reinterpret_cast<uint32_t*>(a.base[a.rank] + a.L.off_work);
-    const uint32_t j = atomicAdd(work + MoeWork::kSendCount + static_cast<uint32_t>(e), 1u);
+    uint32_t* ctrl = reinterpret_cast<uint32_t*>(a.base[a.rank]);
+    const uint32_t j = atomicAdd(ctrl + MoeCtrl::kSendCount + static_cast<uint32_t>(e), 1u);
+    // one rank sends an expert at most t_max rows (one per token); a token that names an expert twice must not
+    // write past this rank's part of the peer's table: the surplus pair is dropped (the count is capped to match)
+    if (j >= a.L.t_max) return;
     const uint32_t dest = static_cast<uint32_t>(e) / a.L.experts_local, el = static_cast<uint32_t>(e) % a.L.experts_local;
     uint32_t* idx = reinterpret_cast<uint32_t*>(a.base[dest] + a.L.off_src_idx);
     idx[(static_cast<uint64_t>(el) * a.L.ranks + a.rank) * a.L.t_max + j] = i;
@@ -156,7 +172,7 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const MoeArgs a) {
 // (`nthreads` of them).  With `fused` != nullptr it also writes the fused kernel's tile table, clears its
 // progress counters and finally publishes `layout_ready`.  Returns false if the barrier timed out.
 struct MoeFusedHooks {
-    uint32_t tile_table, pulled, l1_done, num_tiles_word, layout_ready_word;   // word offsets in the work area
+    uint32_t tile_table, pulled, l1_done;   // word offsets in the work area
 };
 // `scratch`: kMoeScanWords words of shared memory for the layout scan (nullptr: scan in global memory).
 constexpr uint32_t kMoeScanCap = 512, kMoeScanWords = 4 * kMoeScanCap + 1;
@@ -164,14 +180,15 @@ DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthrea
                                  uint32_t* scratch) {
     const MoeLayout& L = a.L;
     uint32_t* work = reinterpret_cast<uint32_t*>(a.base[a.rank] + L.off_work);
+    uint32_t* ctrl = reinterpret_cast<uint32_t*>(a.base[a.rank]);
     __shared__ uint32_t s_call, s_ok, s_tiles, s_rows;
     if (tid == 0) {
-        s_call = ++work[MoeWork::kCall];
+        s_call = ++ctrl[MoeCtrl::kCall];
         s_ok = 1;
     }
     for (uint32_t e = tid; e < L.experts; e += nthreads) {
-        const uint32_t cnt = work[MoeWork::kSendCount + e];
-        work[MoeWork::kSendCount + e] = 0;   // ready for the next call
+        const uint32_t cnt = min(ctrl[MoeCtrl::kSendCount + e], L.t_max);
+        ctrl[MoeCtrl::kSendCount + e] = 0;   // ready for the next call
         const uint32_t dest = e / L.experts_local, el = e % L.experts_local;
         reinterpret_cast<uint32_t*>(a.base[dest] + L.off_recv_count)[a.rank * L.experts_local + el] = cnt;
     }
@@ -197,6 +214,7 @@ DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthrea
     }
     if (tid == 0) {
         uint32_t prev_end = 0, flat = 0, tiles = 0;
+        bool overflow = false;
         for (uint32_t el = 0; el < L.experts_local; ++el) {
             const uint32_t start = (prev_end + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
             uint32_t row = start;
@@ -206,8 +224,8 @@ DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthrea
                 if (staged) {
                     s_off[i] = row, s_pre[i] = flat;
                 } else {
-                    work[MoeWork::seg_off(L.experts, L.experts_local) + i] = row;
-                    work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + i] = flat;
+                    work[MoeWork::seg_off(L.experts_local) + i] = row;
+                    work[MoeWork::seg_prefix(L.experts_local, L.ranks) + i] = flat;
                 }
                 row += cnt, flat += cnt;
             }
@@ -215,8 +233,13 @@ DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthrea
                 s_end[el] = row;
                 s_cnt[el] = row - start;   // the expert's row count, for the statistics (entry el is consumed by now)
             } else {
-                work[MoeWork::psum_end(L.experts) + el] = row;
+                work[MoeWork::psum_end() + el] = row;
                 if (a.stats != nullptr) a.stats[el] += static_cast<int32_t>(row - start);
+            }
+            if (row > L.pool_rows) {
+                // more rows arrived than the pool was sized for (a capacity below the worst case was asked for)
+                overflow = true;
+                break;
             }
             if (fused != nullptr) {
                 // 256-token tiles over the expert's aligned extent
@@ -231,22 +254,35 @@ DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthrea
             }
             prev_end = row;
         }
+        if (overflow) {
+            // Nothing may be written past the pool: the call is reported and goes on as a call without rows (no
+            // pulls, no tiles), so that the barriers the peers wait at are still reached; y is not meaningful.
+            if (atomicCAS(a.status, 0u, static_cast<uint32_t>(kStatusPoolOverflow)) == 0u) {
+                a.status[1] = 110, a.status[2] = a.rank, a.status[3] = flat, a.status[4] = L.pool_rows;
+                __threadfence_system();
+            }
+            prev_end = flat = tiles = 0;
+            for (uint32_t el = 0; el < L.experts_local; ++el) {
+                if (staged) s_end[el] = 0, s_cnt[el] = 0;
+                else        work[MoeWork::psum_end() + el] = 0;
+            }
+        }
         if (staged) s_pre[segs] = flat;
-        else        work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + segs] = flat;
+        else        work[MoeWork::seg_prefix(L.experts_local, L.ranks) + segs] = flat;
         s_rows = (prev_end + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
-        work[MoeWork::kTotalRows] = s_rows;
+        ctrl[MoeCtrl::kTotalRows] = s_rows;
         s_tiles = tiles;
-        if (fused != nullptr) work[fused->num_tiles_word] = tiles;
+        if (fused != nullptr) ctrl[MoeCtrl::kNumTiles] = tiles;
     }
     __syncthreads();
     if (staged) {
         for (uint32_t i = tid; i < segs; i += nthreads) {
-            work[MoeWork::seg_off(L.experts, L.experts_local) + i] = s_off[i];
-            work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + i] = s_pre[i];
+            work[MoeWork::seg_off(L.experts_local) + i] = s_off[i];
+            work[MoeWork::seg_prefix(L.experts_local, L.ranks) + i] = s_pre[i];
         }
-        if (tid == 0) work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + segs] = s_pre[segs];
+        if (tid == 0) work[MoeWork::seg_prefix(L.experts_local, L.ranks) + segs] = s_pre[segs];
         for (uint32_t el = tid; el < L.experts_local; el += nthreads) {
-            work[MoeWork::psum_end(L.experts) + el] = s_end[el];
+            work[MoeWork::psum_end() + el] = s_end[el];
             // one thread per expert: a serial read-modify-write per expert costs a memory round trip each
             if (a.stats != nullptr) a.stats[el] += static_cast<int32_t>(s_cnt[el]);
         }
@@ -255,7 +291,7 @@ DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthrea
     __syncthreads();
     // Rows between an expert's end and the next boundary carry no token: mark them
     for (uint32_t el = 0; el < L.experts_local; ++el) {
-        const uint32_t end = staged ? s_end[el] : work[MoeWork::psum_end(L.experts) + el];
+        const uint32_t end = staged ? s_end[el] : work[MoeWork::psum_end() + el];
         const uint32_t stop = (end + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
         for (uint32_t r = end + tid; r < stop; r += nthreads) meta[r * 3] = -1;
     }
@@ -264,7 +300,7 @@ DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthrea
         for (uint32_t i = tid; i < s_tiles; i += nthreads) work[fused->l1_done + i] = 0;
         __threadfence();
         __syncthreads();
-        if (tid == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(work + fused->layout_ready_word), "r"(s_call) : "memory");
+        if (tid == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ctrl + MoeCtrl::kLayoutReady), "r"(s_call) : "memory");
     }
     return true;
 }
@@ -298,7 +334,7 @@ DG_DEVICE void moe_pull_rows(const MoeArgs& a, const uint32_t* s_prefix, uint32_
         const uint32_t el = lo / L.ranks, src = lo % L.ranks, j = r - s_prefix[lo];
         const uint32_t pair = src_idx[(static_cast<uint64_t>(el) * L.ranks + src) * L.t_max + j];
         const uint32_t token = pair / L.topk, slot = pair % L.topk;
-        const uint32_t dst = work[MoeWork::seg_off(L.experts, L.experts_local) + lo] + j;
+        const uint32_t dst = work[MoeWork::seg_off(L.experts_local) + lo] + j;
         const uint8_t* peer = a.base[src];
         const uint4* from = reinterpret_cast<const uint4*>(peer + L.off_x + static_cast<uint64_t>(token) * L.hidden);
         uint4* to = reinterpret_cast<uint4*>(l1 + static_cast<uint64_t>(dst) * L.hidden);
@@ -343,15 +379,15 @@ __global__ void __launch_bounds__(256) moe_pull_kernel(const MoeArgs a) {
     extern __shared__ uint32_t s_prefix[];   // [segments + 1]
     const uint32_t segments = L.experts_local * L.ranks;
     for (uint32_t i = threadIdx.x; i <= segments; i += 256)
-        s_prefix[i] = work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + i];
+        s_prefix[i] = work[MoeWork::seg_prefix(L.experts_local, L.ranks) + i];
     __syncthreads();
     moe_pull_rows(a, s_prefix, blockIdx.x * 8 + threadIdx.x / 32, gridDim.x * 8, threadIdx.x & 31, nullptr);
 }
 
 // ---- cross-rank barrier on its own (after the experts' ranks have pushed their results).  One CTA.
 __global__ void __launch_bounds__(32) moe_barrier_kernel(const MoeArgs a) {
-    const uint32_t* work = reinterpret_cast<const uint32_t*>(a.base[a.rank] + a.L.off_work);
-    if (threadIdx.x < a.L.ranks) moe_cross_rank_barrier(a, 1, 2 * work[MoeWork::kCall], threadIdx.x);
+    const uint32_t* ctrl = reinterpret_cast<const uint32_t*>(a.base[a.rank]);
+    if (threadIdx.x < a.L.ranks) moe_cross_rank_barrier(a, 1, 2 * ctrl[MoeCtrl::kCall], threadIdx.x);
 }
 
 // ---- last step: y[t] = bf16(sum over the token's valid slots, in slot order, of its combine rows).

@@ -97,15 +97,30 @@ DG_DEVICE bool fused_slot_to_tile(const uint32_t* table, uint32_t num_tiles, uin
     return true;
 }
 
-// Grid-wide barrier on a monotonic counter (all CTAs co-resident: one per SM).  Whole CTA calls it.
-DG_DEVICE bool fused_grid_barrier(uint32_t* counter, uint32_t target, volatile uint32_t* abort_flag, const MoeArgs& a,
+// Grid-wide barrier (all CTAs co-resident: at most one per SM).  Whole CTA calls it.  Self-contained: the last of
+// the `num_ctas` arrivers puts the arrival count back to zero and bumps the generation word the others wait on, so
+// the barrier does not depend on how many CTAs earlier launches had or on how many barriers they passed.  (A launch
+// that gives up on a wait leaves the count behind: the buffer's control block must then be cleared, see
+// SymmBuffer.reset.)
+DG_DEVICE bool fused_grid_barrier(uint32_t* ctrl, uint32_t num_ctas, volatile uint32_t* abort_flag, const MoeArgs& a,
                                   uint32_t site) {
     __shared__ uint32_t s_ok;
     __threadfence_system();   // also covers this CTA's stores to peer buffers
     __syncthreads();
     if (threadIdx.x == 0) {
-        atomicAdd(counter, 1u);
-        s_ok = fused_wait_counter(counter, target, abort_flag, a, site, target) ? 1u : 0u;
+        uint32_t* count = ctrl + MoeCtrl::kGridCount;
+        uint32_t* gen = ctrl + MoeCtrl::kGridGen;
+        uint32_t my_gen;   // read before arriving: the generation cannot move until this CTA has arrived
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(my_gen) : "l"(gen) : "memory");
+        const uint32_t prev = atomicAdd(count, 1u);
+        if (prev + 1 == num_ctas) {
+            atomicExch(count, 0u);
+            __threadfence();
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(gen), "r"(my_gen + 1) : "memory");
+            s_ok = 1u;
+        } else {
+            s_ok = fused_wait_counter(gen, my_gen + 1, abort_flag, a, site, prev) ? 1u : 0u;
+        }
     }
     __syncthreads();
     return s_ok != 0;
@@ -250,6 +265,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     __shared__ __align__(8) uint64_t s_epi_bar[2][2];   // per epilogue group: staging buffer written / read
     const uint32_t peer_abort = map_to_cta(smem_u32(&bars->abort), cta_rank ^ 1);
     uint32_t* work = reinterpret_cast<uint32_t*>(p.a.base[p.a.rank] + L.off_work);
+    uint32_t* ctrl = reinterpret_cast<uint32_t*>(p.a.base[p.a.rank]);
     GemmParams wp;   // only the fields wait_barrier reports through
     wp.timeout_ms = p.a.timeout_ms, wp.status = p.a.status;
 
@@ -283,33 +299,29 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
 
     DG_FUSED_STAMP(0);
     // ---------------------------------------------------------------- dispatch, step 1: count and scatter indices
-    const uint32_t call_old = *reinterpret_cast<volatile uint32_t*>(work + MoeWork::kCall);
+    const uint32_t call_old = *reinterpret_cast<volatile uint32_t*>(ctrl + MoeCtrl::kCall);   // CTA 0 bumps it after barrier 1
     const uint32_t call_new = call_old + 1;
-    // the grid barrier's counter only advances in launches of this kernel: its targets follow their own count
-    const uint32_t fused_calls = *reinterpret_cast<volatile uint32_t*>(work + MoeFusedWork::kFusedCalls);
     for (uint32_t i = blockIdx.x * kFusedThreads + threadIdx.x; i < p.a.num_tokens * L.topk; i += p.num_ctas * kFusedThreads)
         moe_scatter_pair(p.a, i);
-    bool ok = fused_grid_barrier(work + MoeFusedWork::kGridSync, (2 * fused_calls + 1) * p.num_ctas, abort_flag, p.a, 201);
+    bool ok = fused_grid_barrier(ctrl, p.num_ctas, abort_flag, p.a, 201);
     // step 2 (CTA 0): publish counts, cross-rank barrier, pool layout, tile table, counters, layout_ready
     if (ok && blockIdx.x == 0) {
-        if (threadIdx.x == 0) work[MoeFusedWork::kFusedCalls] = fused_calls + 1;   // every CTA has read it before the barrier
         MoeFusedHooks hooks;
         hooks.tile_table = MoeFusedWork::tile_table(L), hooks.pulled = MoeFusedWork::pulled(L);
-        hooks.l1_done = MoeFusedWork::l1_done(L), hooks.num_tiles_word = MoeFusedWork::kNumTiles;
-        hooks.layout_ready_word = MoeFusedWork::kLayoutReady;
+        hooks.l1_done = MoeFusedWork::l1_done(L);
         // the operand stages are idle until the roles start: their first words serve the layout scan
         moe_exchange_body(p.a, threadIdx.x, kFusedThreads, &hooks, reinterpret_cast<uint32_t*>(smem_gen));
     }
     if (ok) {
         if (threadIdx.x == 0)
-            ok = fused_wait_counter(work + MoeFusedWork::kLayoutReady, call_new, abort_flag, p.a, 202, call_new);
+            ok = fused_wait_counter(ctrl + MoeCtrl::kLayoutReady, call_new, abort_flag, p.a, 202, call_new);
         // every thread needs the outcome and the layout
         __shared__ uint32_t s_layout_ok;
         if (threadIdx.x == 0) s_layout_ok = ok ? 1u : 0u;
         __syncthreads();
         ok = s_layout_ok != 0;
     }
-    const uint32_t num_tiles = ok ? work[MoeFusedWork::kNumTiles] : 0;
+    const uint32_t num_tiles = ok ? ctrl[MoeCtrl::kNumTiles] : 0;
     const uint32_t* table = work + MoeFusedWork::tile_table(L);
     uint32_t* pulled = work + MoeFusedWork::pulled(L);
     uint32_t* l1_done = work + MoeFusedWork::l1_done(L);
@@ -318,7 +330,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     const uint32_t segments = L.experts_local * L.ranks;
     if (ok) {
         for (uint32_t i = threadIdx.x; i <= segments; i += kFusedThreads)
-            s_prefix[i] = work[MoeWork::seg_prefix(L.experts, L.experts_local, L.ranks) + i];
+            s_prefix[i] = work[MoeWork::seg_prefix(L.experts_local, L.ranks) + i];
     }
     __syncthreads();
 
@@ -543,7 +555,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     DG_FUSED_FLUSH();
     DG_FUSED_STAMP(2);
     // ---------------------------------------------------------------- combine: everyone has pushed, then reduce
-    bool ok2 = fused_grid_barrier(work + MoeFusedWork::kGridSync, (2 * fused_calls + 2) * p.num_ctas, abort_flag, p.a, 205);
+    bool ok2 = fused_grid_barrier(ctrl, p.num_ctas, abort_flag, p.a, 205);
     if (ok2 && blockIdx.x == 0) {
         __shared__ uint32_t s_bar_ok;
         if (threadIdx.x == 0) s_bar_ok = 1;
@@ -552,12 +564,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             if (!moe_cross_rank_barrier(p.a, 1, 2 * call_new, threadIdx.x)) s_bar_ok = 0;
         __syncthreads();
         if (threadIdx.x == 0 && s_bar_ok)
-            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(work + MoeFusedWork::kCombineReady), "r"(call_new) : "memory");
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ctrl + MoeCtrl::kCombineReady), "r"(call_new) : "memory");
     }
     if (ok2) {
         __shared__ uint32_t s_comb_ok;
         if (threadIdx.x == 0)
-            s_comb_ok = fused_wait_counter(work + MoeFusedWork::kCombineReady, call_new, abort_flag, p.a, 206, call_new) ? 1u : 0u;
+            s_comb_ok = fused_wait_counter(ctrl + MoeCtrl::kCombineReady, call_new, abort_flag, p.a, 206, call_new) ? 1u : 0u;
         __syncthreads();
         DG_FUSED_STAMP(3);
         if (s_comb_ok) {

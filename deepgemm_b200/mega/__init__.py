@@ -64,8 +64,11 @@ class SymmBuffer:
         self.num_experts, self.num_max_tokens_per_rank, self.num_topk = num_experts, num_max_tokens_per_rank, num_topk
         self.hidden, self.intermediate_hidden = hidden, intermediate_hidden
         self.num_shared_experts, self.mma_type, self.activation = 0, mma_type, activation
+        # `num_ring_tokens` bounds the rows of the expert-sorted pool (None / 0: the worst case, every token of every
+        # rank routed here); a call that receives more is abandoned and reported by check_status()
+        _require(num_ring_tokens is None or num_ring_tokens >= 0, "num_ring_tokens >= 0")
         self.config = _lib.MoeConfig(self.num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden,
-                                     intermediate_hidden)
+                                     intermediate_hidden, int(num_ring_tokens or 0), 0)
         lay = _lib.MoeLayout()
         _lib.check(_lib.lib().dg_mega_moe_buffer_layout(C.byref(self.config), C.byref(lay)))
         self.layout = lay
@@ -83,6 +86,9 @@ class SymmBuffer:
                 group.barrier()
             torch.cuda.synchronize()
         else:
+            # Another configuration on the memory of `base` (deep_gemm/mega/__init__.py:80-92).  Legal between calls:
+            # the words that live across calls (barrier epochs, grid barrier, send counters) sit in a control block
+            # whose place does not depend on the configuration, everything else is rewritten by each call.
             _require(base.buffer is not None and base.group is group, "cannot reuse an invalid symmetric buffer")
             _require(lay.num_bytes <= base.buffer.nbytes, "the reused buffer is too small for this configuration")
             self.buffer, self.handle = base.buffer, base.handle
@@ -119,6 +125,23 @@ class SymmBuffer:
         self.topk_idx[:n].copy_(topk_idx)
         self.topk_weights[:n].copy_(topk_weights)
         return n
+
+    def reset(self) -> None:
+        """Make the buffer usable again after a call that gave up on a wait (check_status() raised): such a call
+        leaves barrier arrivals and epochs behind that the next call would trip over.  Every rank of the group must
+        call this, with no forward in flight on any of them: the ranks meet, each clears its whole buffer (control
+        block included), and they meet again.  The inputs (x, x_sf, topk_idx, topk_weights) must be refilled."""
+        torch.cuda.synchronize()
+        if self.group is not None:
+            self.group.barrier()
+        self.buffer.zero_()
+        torch.cuda.synchronize()
+        if self.group is not None:
+            self.group.barrier()
+        try:
+            _lib.check_status()      # drop a stale record of the abandoned wait
+        except RuntimeError:
+            pass
 
     def destroy(self):
         self.handle = self.buffer = self.group = None

@@ -18,10 +18,6 @@ from .layout import (_require, _stream, get_k_grouped_mn_major_tma_aligned_packe
 PACKED_FP4 = torch.int8   # two E2M1 codes per byte (csrc/utils/math.hpp:11)
 _K, _MN = 0, 1
 
-# Tile override for tests / tuning: dict with any of cta_group, block_n, swap (1 plain, 2 swapped).
-_force_tile = {}
-
-
 class _Epilogue:
     pass
 
@@ -101,9 +97,6 @@ def _launch(gemm_type, m, n, k, a, sfa, major_a, gran_a, b, sfb, major_b, gran_b
     args.expected_m = int(expected_m or 0)
     args.grouped_layout = grouped_layout.data_ptr() if grouped_layout is not None else None
     args.stream = _stream(d)
-    args.force_cta_group = _force_tile.get("cta_group", 0)
-    args.force_block_n = _force_tile.get("block_n", 0)
-    args.force_swap = _force_tile.get("swap", 0)
     _lib.check(_lib.lib().dg_gemm_bs(args))
 
 

@@ -76,11 +76,6 @@ typedef struct dg_gemm_args {
     int32_t expected_m;       /* heuristic hint for grouped layouts; 0 = none */
     const int32_t* grouped_layout;
     void* stream;             /* cudaStream_t */
-    /* Tile selection override for tests and tuning; 0 = choose automatically. */
-    int32_t force_cta_group;  /* 1 or 2 */
-    int32_t force_block_n;    /* UMMA N: 32, 64, 128, 256 */
-    int32_t force_swap;       /* 1 = plain, 2 = swapped operands */
-    int32_t reserved;
 } dg_gemm_args;
 
 /* Block-scaled GEMM, all layouts.  Takes the role of sm100_fp8_fp4_gemm_1d1d and its grouped
@@ -121,6 +116,12 @@ int dg_sf_pack_ue8m0_k_grouped(const float* sf, int32_t* out, const int32_t* gro
  * the calling process (peer access over NVLink; with one rank, the buffer itself). */
 typedef struct dg_moe_config {
     int32_t num_ranks, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden;
+    /* Rows (token, expert pairs) the expert-sorted pool of one rank must hold, the role of the reference's
+     * `num_ring_tokens` (csrc/apis/mega_moe.hpp:49-96): 0 = the worst case num_max_tokens_per_rank * num_ranks *
+     * min(num_topk, experts per rank); a smaller value saves memory, and a call that receives more rows than fit
+     * is abandoned and reported by dg_check_status (code 3). */
+    int32_t num_ring_tokens;
+    int32_t reserved;
 } dg_moe_config;
 
 /* Byte offsets of the views inside one rank's buffer (shapes as in csrc/apis/mega_moe.hpp:137-226 of the
@@ -141,6 +142,11 @@ int dg_mega_moe_buffer_layout(const dg_moe_config* cfg, dg_moe_layout* out);
 
 /* Row granularity of num_max_tokens_per_rank (csrc/apis/mega_moe.hpp:34-36). */
 int dg_get_token_alignment_for_mega_moe(void);
+
+/* SMs the Mega MoE grid takes: dg_get_num_sms() (capped at the device's count) minus the environment variable
+ * DG_MEGA_MOE_SM_HEADROOM rounded up to an even number; -1 with dg_last_error() set when the headroom is negative,
+ * leaves no SM, or the result is odd (get_mega_moe_num_sms, csrc/jit_kernels/impls/runtime_utils.hpp:35-82). */
+int dg_get_mega_moe_num_sms(void);
 
 enum { DG_ACT_SWIGLU = 0, DG_ACT_GEGLU = 1, DG_ACT_SITU = 2 };
 
@@ -258,6 +264,17 @@ int dg_set_mk_alignment_for_contiguous_layout(int32_t alignment);
 int dg_get_mk_alignment_for_contiguous_layout(void);
 int dg_get_theoretical_mk_alignment_for_contiguous_layout(int32_t expected_m);
 int dg_set_wait_timeout_ms(int32_t ms);  /* budget of every device-side wait; default 2000 */
+
+/* Test and tuning aid, not part of the operator surface (the reference's counterpart is its heuristics'
+ * candidate enumeration, csrc/jit_kernels/heuristics/sm100.hpp:30-163): pins the tile that later dg_gemm_bs calls
+ * of this process use.  cta_group 1 / 2, block_n = UMMA N (32 .. 256), swap 1 = tokens on the UMMA M axis,
+ * 2 = weights on the UMMA M axis; 0 in any field = choose automatically. */
+int dg_debug_set_tile_override(int32_t cta_group, int32_t block_n, int32_t swap);
+
+/* Measurement aid (no counterpart in the reference): copies `bytes` (a multiple of 16, both addresses 16-byte
+ * aligned) with plain 16-byte loads and stores by all SMs, the way the Mega MoE forward pulls token rows.  Given a
+ * peer GPU's mapped address as `src` it measures the NVLink bandwidth that path can reach. */
+int dg_debug_copy(void* dst, const void* src, int64_t bytes, void* stream);
 
 /* Synchronises the device and reports whether any kernel of this library abandoned a wait
  * since the last call.  Returns DG_OK, or DG_ERR_DEVICE with the record in info[0..7]

@@ -24,7 +24,7 @@ int main(int argc, char** argv) {
         (int (*)(const dg_moe_config*, dg_moe_layout*))dlsym(lib, "dg_mega_moe_buffer_layout");
     int (*alignment)(void) = (int (*)(void))dlsym(lib, "dg_get_token_alignment_for_mega_moe");
     const char* (*last_error)(void) = (const char* (*)(void))dlsym(lib, "dg_last_error");
-    dg_moe_config cfg = {8, 256, 4096, 8, 7168, 2048};
+    dg_moe_config cfg = {8, 256, 4096, 8, 7168, 2048, 0, 0};
     dg_moe_layout lay;
     memset(&lay, 0, sizeof(lay));
     if (layout(&cfg, &lay) != DG_OK) {
@@ -32,7 +32,7 @@ int main(int argc, char** argv) {
         return 5;
     }
     /* a bad configuration is refused with a message, not a crash */
-    dg_moe_config bad = {3, 256, 4096, 8, 7168, 2048};
+    dg_moe_config bad = {3, 256, 4096, 8, 7168, 2048, 0, 0};
     dg_moe_layout unused;
     const int rc_bad = layout(&bad, &unused);
     printf("%s align=%d bytes=%lld pool_rows=%lld bad_rc=%d bad_msg=%s\n", version(), alignment(),

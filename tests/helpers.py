@@ -97,15 +97,14 @@ class force_tile:
         self.kw = kw
 
     def __enter__(self):
-        from deepgemm_b200 import ops
-        self.old = dict(ops._force_tile)
-        ops._force_tile.clear()
-        ops._force_tile.update({k: v for k, v in self.kw.items() if v})
+        from deepgemm_b200 import _lib
+        kw = self.kw
+        _lib.check(_lib.lib().dg_debug_set_tile_override(kw.get("cta_group") or 0, kw.get("block_n") or 0,
+                                                         kw.get("swap") or 0))
 
     def __exit__(self, *exc):
-        from deepgemm_b200 import ops
-        ops._force_tile.clear()
-        ops._force_tile.update(self.old)
+        from deepgemm_b200 import _lib
+        _lib.check(_lib.lib().dg_debug_set_tile_override(0, 0, 0))
 
 
 # --------------------------------------------------------------------------- grouped generators

@@ -78,7 +78,9 @@ def test_knobs_roundtrip():
     dg.set_tc_util(80)
     assert dg.get_tc_util() == 80
     dg.set_tc_util(100)
-    assert dg.get_theoretical_mk_alignment_for_contiguous_layout() in (128, 256)
+    # 256 on sm_100 whatever the expected group size (csrc/jit_kernels/heuristics/runtime.hpp:57-64 of the reference)
+    assert dg.get_theoretical_mk_alignment_for_contiguous_layout() == 256
+    assert dg.get_theoretical_mk_alignment_for_contiguous_layout(64) == 256
     assert dg.utils.get_m_alignment_for_contiguous_layout() == old
 
 
@@ -136,6 +138,44 @@ def test_mega_moe_buffer_layout_and_checks():
     assert _lib.lib().dg_mega_moe_buffer_layout(ctypes.byref(bad), ctypes.byref(lay)) != 0
     assert b"num_experts" in _lib.lib().dg_last_error()
     assert dg.get_token_alignment_for_mega_moe() == 128
+
+
+def test_mega_moe_sm_headroom_policy(monkeypatch):
+    """The table of the reference's tests/test_mega_moe_headroom.py: the grid is num_sms minus the headroom rounded up to
+    even; negative, all-consuming and odd results are refused."""
+    lib = _lib.lib()
+    try:
+        for sms, env, want in ((148, None, 148), (148, "0", 148), (148, "2", 146), (148, "3", 144), (148, "8", 140),
+                               (132, "1", 130), (148, "-1", -1), (148, "148", -1), (148, "147", -1), (147, "0", -1)):
+            dg.set_num_sms(sms)
+            if env is None:
+                monkeypatch.delenv("DG_MEGA_MOE_SM_HEADROOM", raising=False)
+            else:
+                monkeypatch.setenv("DG_MEGA_MOE_SM_HEADROOM", env)
+            assert lib.dg_get_mega_moe_num_sms() == want, (sms, env)
+    finally:
+        dg.set_num_sms(0)
+
+
+def test_mega_moe_pool_capacity_and_control_block():
+    """num_ring_tokens bounds the pool (and with it the buffer); the first view starts after the fixed 16 KiB control
+    block whatever the configuration, which is what makes reusing a buffer for another configuration legal."""
+    lay = _lib.MoeLayout()
+    sizes = {}
+    for cap in (0, 40000):
+        cfg = _lib.MoeConfig(8, 256, 4096, 8, 7168, 2048, cap, 0)
+        assert _lib.lib().dg_mega_moe_buffer_layout(ctypes.byref(cfg), ctypes.byref(lay)) == 0
+        sizes[cap] = (lay.num_bytes, lay.pool_rows)
+    assert sizes[0][1] >= 4096 * 8 * 8 and 40000 <= sizes[40000][1] < 40000 + 32 * 128 + 256
+    assert sizes[40000][0] < sizes[0][0] / 2
+    firsts = set()
+    for experts, tokens, hidden in ((256, 4096, 7168), (8, 128, 1024), (64, 512, 2048)):
+        cfg = _lib.MoeConfig(8, experts, tokens, 4, hidden, 512, 0, 0)
+        assert _lib.lib().dg_mega_moe_buffer_layout(ctypes.byref(cfg), ctypes.byref(lay)) == 0
+        firsts.add(min(lay.off_x, lay.off_x_sf, lay.off_topk_idx, lay.off_l1_acts, lay.off_combine) >= 16384)
+    assert firsts == {True}
+    too_many = _lib.MoeConfig(1, 8192, 128, 4, 1024, 512, 0, 0)
+    assert _lib.lib().dg_mega_moe_buffer_layout(ctypes.byref(too_many), ctypes.byref(lay)) != 0
 
 
 def test_header_is_plain_c_and_library_answers_without_gpu(tmp_path):
