@@ -377,6 +377,10 @@ int dg_check_status(uint32_t info[8]) {
     if (host[0] == dg::kStatusOk) return DG_OK;
     uint32_t zero[16] = {0};
     DG_CUDA(cudaMemcpyToSymbol(g_status, zero, sizeof(zero)));
+    if (host[0] == dg::kStatusPoolOverflow)
+        return fail(DG_ERR_DEVICE,
+                    "Mega MoE: rank %u received %u rows but its pool holds %u (num_ring_tokens is too small); the call "
+                    "was abandoned, y is not meaningful", host[2], host[3], host[4]);
     return fail(DG_ERR_DEVICE,
                 "a kernel abandoned a bounded wait: code %u site %u block %u tile-iteration %u k-block %u stage %u",
                 host[0], host[1], host[2], host[3], host[4], host[5]);

@@ -233,8 +233,10 @@ int dg_per_token_cast_to_fp8(const dg_cast_args* args);
  *   d : BF16 or FP32 [m, n], ldd bytes between rows
  *
  * Limits and rules:
- *   - (align(m,4) + align(n,4)) * ceil(k / (4 * gran_k)) * 4 bytes must fit dg_noalloc_scratch_bytes();
- *     larger problems are rejected with DG_ERR_INVALID and a message naming the sizes.
+ *   - with w = ceil(k / (4 * gran_k)) packed words per row:
+ *         round_up(align(m,4) * w * 4, 256) + align(n,4) * w * 4  bytes  <=  dg_noalloc_scratch_bytes()
+ *     (the scales of a, rounded up to a 256-byte boundary, then those of b); larger problems are rejected with
+ *     DG_ERR_INVALID and a message naming the sizes.
  *   - The first call on a device looks up the scratch array's device address (no allocation); make that
  *     first call before starting any stream capture.
  *   - All calls on one GPU share the one array, which keeps the last call's contents: each call rewrites

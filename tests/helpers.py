@@ -217,3 +217,43 @@ def make_k_grouped(num_groups, m, n, ks, *, gran_k=128, seed=0, device="cuda"):
         bounds.append((off, off + kk))
         off += kk
     return dict(a=qa, b=qb, ref_a=deq(*qa), ref_b=deq(*qb), bounds=bounds)
+
+
+def make_k_grouped_psum(m, n, real_ks, k_alignment, *, gran_k=128, seed=0, device="cuda"):
+    """tests/generators.py:540-608 of the reference with use_psum_layout: group g owns the K rows
+    [align(end[g-1], k_alignment), end[g]); the rows up to the next boundary are zero; every group is quantised over
+    its aligned extent, so its scale rows cover align(k_g, k_alignment) / gran_k rows.  Returns the quantised operands,
+    the cumulative ends, the aligned sizes and dequantised copies with the groups' real K ranges."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    aligned = [align_up(k, k_alignment) for k in real_ks]
+    ends, prev = [], 0
+    for k in real_ks:
+        prev = align_up(prev, k_alignment) + k
+        ends.append(prev)
+    total = sum(aligned)
+    a = torch.zeros((total, m), dtype=torch.bfloat16)
+    b = torch.zeros((total, n), dtype=torch.bfloat16)
+    bounds = []
+    for k, end in zip(real_ks, ends):
+        a[end - k:end] = torch.randn((k, m), generator=g).to(torch.bfloat16)
+        b[end - k:end] = torch.randn((k, n), generator=g).to(torch.bfloat16)
+        bounds.append((end - k, end))
+    a, b = a.to(device), b.to(device)
+
+    def cast(x):
+        data = torch.zeros(x.shape, dtype=torch.float8_e4m3fn, device=device)
+        sfs = []
+        for (k0, k1), al in zip(bounds, aligned):
+            if al == 0:
+                continue
+            q, sf = M.per_channel_cast_to_fp8(x[k0:k0 + al], True, gran_k)    # rows past k1 are the zero padding
+            data[k0:k0 + al] = q
+            sfs.append(sf)
+        return data, torch.cat(sfs)
+
+    qa, qb = cast(a), cast(b)
+
+    def deq(d, s):
+        return OQ.e4m3_bits_to_f32(to_np(d)) * np.repeat(to_np(s), gran_k, axis=0)
+
+    return dict(a=qa, b=qb, ref_a=deq(*qa), ref_b=deq(*qb), bounds=bounds, ends=ends, aligned=aligned)

@@ -68,3 +68,34 @@ def test_missing_peer_times_out_and_context_survives(fused):
     torch.cuda.synchronize()
     dg.check_status()
     assert torch.equal(d, torch.full_like(d, k))
+
+
+def test_buffer_reset_after_an_abandoned_call():
+    """A call that gives up on a wait leaves barrier arrivals behind; SymmBuffer.reset() makes the buffer usable again.
+    The failure is made on the host: stale arrivals are written into the grid barrier's count (what an abandoned call
+    leaves behind, exaggerated), so the count never equals the number of CTAs, nobody opens the barrier and every CTA
+    waits for a generation that never comes; with the limit at 200 ms the call returns with a status record."""
+    import test_mega_moe_gpu as T
+    hidden, inter, experts, topk, tokens = 1024, 512, 8, 4, 96
+    forward, ref = T._single_rank_case(hidden, inter, experts, topk, tokens)
+    buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter)
+    lib = _lib.lib()
+    dg.check_status()
+    try:
+        y_good = forward(buf)
+        torch.cuda.synchronize()
+        dg.check_status()
+        buf.buffer.view(torch.int32)[34] = 100000       # control word: arrivals of the grid barrier's generation
+        _lib.check(lib.dg_set_wait_timeout_ms(200))
+        forward(buf)
+        with pytest.raises(RuntimeError, match="abandoned a bounded wait"):
+            dg.check_status()
+        _lib.check(lib.dg_set_wait_timeout_ms(2000))
+        buf.reset()
+        y = forward(buf)
+        torch.cuda.synchronize()
+        dg.check_status()
+        assert torch.equal(y, y_good)
+    finally:
+        _lib.check(lib.dg_set_wait_timeout_ms(2000))
+        buf.destroy()

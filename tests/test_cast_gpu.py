@@ -1,12 +1,14 @@
-"""GPU parity of the fused BF16 -> E4M3 + UE8M0 cast kernel: bit for bit against the torch restatement of the
-reference helper (deep_gemm/utils/math.py:26-49), which tests/test_package_cpu.py pins to the reference's golden
-vectors, and against the packed MN-major layout the SF transform produces."""
+"""GPU parity of the fused BF16 -> E4M3 + UE8M0 cast kernel: bit for bit against the CPU oracle (oracle/quant.py,
+which tests/test_oracle_golden.py pins to outputs of the reference's deep_gemm/utils/math.py:26-49), against the shipped
+torch helper, and against the packed MN-major layout the SF transform produces."""
+import numpy as np
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
 
 import deepgemm_b200 as dg
+from oracle import quant as OQ
 
 
 def make_x(rows, cols, seed):
@@ -30,9 +32,15 @@ def test_cast_matches_reference_helper(shape, gran_k):
     q_ref, sf_ref = dg.utils.per_token_cast_to_fp8(x, True, gran_k)
     _, packed_ref = dg.utils.per_token_cast_to_fp8(x, True, gran_k, use_packed_ue8m0=True)
     q, sf = dg.per_token_cast_to_fp8_fused(x, gran_k, "float")
+    # the CPU oracle on the same BF16 values: E4M3 bytes, scale bits and packed words, bit for bit
+    o_q, o_sf = OQ.per_token_cast_to_fp8(x.float().cpu().numpy(), True, gran_k)
+    _, o_packed = OQ.per_token_cast_to_fp8(x.float().cpu().numpy(), True, gran_k, use_packed_ue8m0=True)
+    assert np.array_equal(q.view(torch.uint8).cpu().numpy(), o_q)
+    assert np.array_equal(sf.cpu().numpy().view(np.uint32), o_sf.view(np.uint32))
     assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
     assert torch.equal(sf, sf_ref)
     q2, packed = dg.per_token_cast_to_fp8_fused(x, gran_k, "packed")
+    assert np.array_equal(packed.cpu().numpy(), o_packed)
     assert torch.equal(q2.view(torch.uint8), q_ref.view(torch.uint8))
     assert torch.equal(packed, packed_ref)
     # GEMM-ready layout == what the SF transform makes of the FP32 scales, strides included

@@ -102,6 +102,31 @@ def test_sf_pack_k_grouped(gran_k, k_alignment):
     assert out.shape == ref.shape and np.array_equal(out.cpu().numpy(), ref)
 
 
+@pytest.mark.parametrize("gran_k,k_alignment", [(128, 128), (32, 128), (128, 256), (32, 384)])
+def test_sf_pack_k_grouped_psum(gran_k, k_alignment):
+    """The PSUM form (tests/test_layout.py:268-304 of the reference): the layout holds cumulative un-aligned K ends,
+    every group's scale rows cover its aligned extent; with and without the host-side list of aligned sizes."""
+    mn = 1024
+    real_ks = [200, 0, 1000, 128, 513, 0, 77, 640]
+    aligned = [H.align_up(k, k_alignment) for k in real_ks]
+    ends, prev = [], 0
+    for k in real_ks:
+        prev = H.align_up(prev, k_alignment) + k
+        ends.append(prev)
+    rows = sum(al // gran_k for al in aligned)
+    g = torch.Generator().manual_seed(rows)
+    sf = (torch.randint(1, 254, (rows, mn), generator=g, dtype=torch.int32) << 23).view(torch.float32)
+    layout = torch.tensor(ends, dtype=torch.int32, device="cuda")
+    ref = OL.k_grouped_packed_ue8m0(sf.numpy(), aligned, gran_k)
+    out = dg.get_k_grouped_mn_major_tma_aligned_packed_ue8m0_tensor(sf.cuda(), layout, aligned, gran_k, k_alignment,
+                                                                    use_psum_layout=True)
+    assert out.shape == ref.shape and np.array_equal(out.cpu().numpy(), ref)
+    for ks_cpu in (None, []):                      # sizes not known on the host: a safe upper bound of rows
+        out2 = dg.get_k_grouped_mn_major_tma_aligned_packed_ue8m0_tensor(sf.cuda(), layout, ks_cpu, gran_k,
+                                                                         k_alignment, use_psum_layout=True)
+        assert out2.size(0) >= ref.shape[0] and np.array_equal(out2[:ref.shape[0]].cpu().numpy(), ref)
+
+
 # --------------------------------------------------------------------------- dense GEMM
 def run_dense(m, n, k, *, gran_a=128, b_kind="fp8_block", tile=None, out_dtype=torch.bfloat16, packed=False,
               accumulate=False, alpha=None, mn_major=(False, False), alias=False, scale_b=1.0):
@@ -348,6 +373,41 @@ def test_k_grouped_tn_empty_groups(ks, accumulate, out_dtype):
         for g, kk in enumerate(ks):
             if kk == 0:
                 assert np.array_equal(got[g], ref[g]), f"empty group {g}"
+        assert H.calc_diff(got, ref) < FP8_TOL
+    finally:
+        dg.set_mk_alignment_for_contiguous_layout(old)
+
+
+@pytest.mark.parametrize("gran_k", [128, 32])
+@pytest.mark.parametrize("accumulate,out_dtype", [(True, torch.float32), (False, torch.bfloat16)])
+@pytest.mark.parametrize("synced", [True, False])
+def test_k_grouped_tn_psum(gran_k, accumulate, out_dtype, synced):
+    """K-grouped GEMM over the PSUM layout (tests/generators.py:540-608 of the reference): un-aligned K ends, a group's
+    last K block stops inside the zero padding before the next group; empty groups first, last and in between; with the
+    aligned sizes known on the host and without."""
+    old = dg.get_mk_alignment_for_contiguous_layout()
+    try:
+        dg.set_mk_alignment_for_contiguous_layout(128)
+        real_ks = [0, 200, 0, 1000, 128, 513, 0]
+        m, n = 256, 512
+        case = H.make_k_grouped_psum(m, n, real_ks, 128, gran_k=gran_k, seed=gran_k + 1)
+        g = len(real_ks)
+        d = torch.randn((g, m, n), dtype=out_dtype, device="cuda") * 32 if accumulate else \
+            torch.full((g, m, n), float("nan"), dtype=out_dtype, device="cuda")
+        c = d if accumulate else None
+        cref = H.to_np(d).astype(np.float32) if accumulate else None
+        layout = torch.tensor(case["ends"], dtype=torch.int32, device="cuda")
+        dg.k_grouped_fp8_gemm_tn_contiguous(case["a"], case["b"], d, case["aligned"] if synced else None, layout, c=c,
+                                            recipe=(1, 1, gran_k), use_psum_layout=True)
+        torch.cuda.synchronize()
+        dg.check_status()
+        ref = OG.k_grouped_tn(case["ref_a"], case["ref_b"], case["bounds"], c=cref,
+                              cd_dtype="f32" if out_dtype == torch.float32 else "bf16")
+        got = H.to_np(d)
+        assert not np.isnan(got).any()
+        for i, kk in enumerate(real_ks):
+            if kk == 0:
+                assert np.array_equal(got[i], ref[i]), f"empty group {i}"
         assert H.calc_diff(got, ref) < FP8_TOL
     finally:
         dg.set_mk_alignment_for_contiguous_layout(old)

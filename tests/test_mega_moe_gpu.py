@@ -191,6 +191,105 @@ def test_mega_moe_post_down_route_weights(fused):
         buf.destroy()
 
 
+def _single_rank_case(hidden, inter, experts, topk, tokens, seed=100):
+    (q1, sf1, deq1), (q2, sf2, deq2) = make_weights(experts, hidden, inter)
+    l1 = (q1, dg.transform_sf_into_required_layout(sf1, 2 * inter, hidden, (1, 32), experts))
+    l2 = (q2, dg.transform_sf_into_required_layout(sf2, hidden, inter, (1, 32), experts))
+    l1, l2 = dg.transform_weights_for_mega_moe(l1, l2)
+    x_fp8, x_sf, idx, w, x_deq = make_inputs(tokens, hidden, experts, topk, seed)
+    ref = OM.mega_moe_reference(x_deq, idx.cpu().numpy(), w.cpu().numpy(), deq1, deq2)[0]
+
+    def fill(buf):
+        buf.x[:tokens].copy_(x_fp8), buf.x_sf[:tokens].copy_(x_sf)
+        buf.topk_idx[:tokens].copy_(idx), buf.topk_weights[:tokens].copy_(w)
+
+    def forward(buf):
+        fill(buf)
+        y = torch.full((tokens, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+        dg.fp8_fp4_mega_moe(y, l1, l2, buf)
+        return y
+
+    return forward, ref
+
+
+def test_mega_moe_with_fewer_sms():
+    """The persistent grid follows set_num_sms and DG_MEGA_MOE_SM_HEADROOM between calls on one buffer (its grid barrier
+    does not remember earlier grids); a grouped GEMM runs under the same knob.  Results equal the full-grid ones bit
+    for bit (the tiles' arithmetic does not depend on which CTA runs them)."""
+    hidden, inter, experts, topk, tokens = 2048, 1024, 16, 4, 700
+    forward, ref = _single_rank_case(hidden, inter, experts, topk, tokens)
+    buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter)
+    full = dg.get_num_sms()
+    try:
+        y_full = forward(buf)
+        torch.cuda.synchronize()
+        dg.check_status()
+        assert H.calc_diff(H.to_np(y_full), ref) < MOE_TOL
+        for sms, headroom in ((full - 2, None), (100, None), (full, "3"), (full + 40, None), (full, None)):
+            dg.set_num_sms(sms)
+            if headroom is None:
+                os.environ.pop("DG_MEGA_MOE_SM_HEADROOM", None)
+            else:
+                os.environ["DG_MEGA_MOE_SM_HEADROOM"] = headroom
+            y = forward(buf)
+            torch.cuda.synchronize()
+            dg.check_status()
+            assert torch.equal(y, y_full), (sms, headroom)
+        dg.set_num_sms(full - 2)
+        case = H.make_m_grouped_contiguous(4, 300, 512, 1024, seed=9)
+        d = torch.full((case["m"], 512), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ga, gmb, gb = case["grans"]
+        dg.m_grouped_fp8_fp4_gemm_nt_contiguous(case["a"], case["b"], d, case["layout"], recipe_a=(1, ga), recipe_b=(gmb, gb))
+        torch.cuda.synchronize()
+        dg.check_status()
+        from oracle import gemm as OG
+        assert H.calc_diff(H.to_np(d)[case["valid"]], H.ref_m_grouped(case)[case["valid"]]) < 1e-3
+    finally:
+        os.environ.pop("DG_MEGA_MOE_SM_HEADROOM", None)
+        dg.set_num_sms(0)
+        buf.destroy()
+
+
+def test_mega_moe_buffer_reused_for_another_configuration():
+    """SymmBuffer(base=...) runs a second configuration on the first one's memory (deep_gemm/mega/__init__.py:80-92),
+    then the first again: the words that live across calls keep their place, everything else is rewritten."""
+    big = (2048, 1024, 16, 4, 700)
+    small = (1024, 512, 8, 4, 96)
+    fwd_big, ref_big = _single_rank_case(*big)
+    fwd_small, ref_small = _single_rank_case(*small, seed=7)
+    buf = dg.get_symm_buffer_for_mega_moe(None, big[2], big[4], big[3], big[0], big[1])
+    assert H.calc_diff(H.to_np(fwd_big(buf)), ref_big) < MOE_TOL
+    view = dg.SymmBuffer(None, small[2], small[4], small[3], small[0], small[1], base=buf)
+    assert view.buffer.data_ptr() == buf.buffer.data_ptr()
+    for fused in (True, False, True):
+        dg.mega.set_fused(fused)
+        assert H.calc_diff(H.to_np(fwd_small(view)), ref_small) < MOE_TOL
+        assert H.calc_diff(H.to_np(fwd_big(buf)), ref_big) < MOE_TOL
+        torch.cuda.synchronize()
+        dg.check_status()
+    dg.mega.set_fused(True)
+    buf.destroy()
+
+
+def test_mega_moe_pool_smaller_than_the_rows_is_reported():
+    """num_ring_tokens below what arrives: the call is abandoned and reported (no write past the pool, no hang), and a
+    later call that fits runs normally on the same buffer."""
+    hidden, inter, experts, topk, tokens = 1024, 512, 8, 4, 512
+    forward, ref = _single_rank_case(hidden, inter, experts, topk, tokens)
+    buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter, num_ring_tokens=1024)
+    assert buf.layout.pool_rows < tokens * topk
+    for fused in (True, False):
+        dg.mega.set_fused(fused)
+        forward(buf)
+        with pytest.raises(RuntimeError, match="pool"):
+            dg.check_status()
+    dg.mega.set_fused(True)
+    roomy = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter, num_ring_tokens=tokens * topk)
+    assert H.calc_diff(H.to_np(forward(roomy)), ref) < MOE_TOL
+    dg.check_status()
+    buf.destroy(), roomy.destroy()
+
+
 def _worker(local_rank, ranks, cfg, port, results):
     import torch.distributed as dist
     torch.cuda.set_device(local_rank)

@@ -44,6 +44,7 @@ def call_noalloc(qa, qb, d, m, n, k, gran_k, out_dtype):
 def test_noalloc_gemm_matches_ordinary_entry_point_twice_in_a_row():
     torch.manual_seed(0)
     cases = [(512, 768, 2048, 128, "block", torch.bfloat16), (300, 256, 1024, 32, "row", torch.float32)]
+    prepared = []
     for m, n, k, gran_k, b_kind, out_dtype in cases:           # second call reuses the scratch with another shape
         x = torch.randn((m, k), device="cuda", dtype=torch.bfloat16)
         w = torch.randn((n, k), device="cuda", dtype=torch.bfloat16)
@@ -51,14 +52,26 @@ def test_noalloc_gemm_matches_ordinary_entry_point_twice_in_a_row():
         qb = dg.utils.per_block_cast_to_fp8(w, True, 128) if b_kind == "block" else \
             dg.utils.per_token_cast_to_fp8(w, True, gran_k)
         got = torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda")
-        before = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
         call_noalloc(qa, qb, got, m, n, k, gran_k, out_dtype)
-        torch.cuda.synchronize()
-        assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == before   # nothing was allocated
         want = reference_path(qa, qb, m, n, k, gran_k, out_dtype)
         torch.cuda.synchronize()
         dg.check_status()
         dg.testing.assert_bitwise_equal(got, want, f"noalloc vs ordinary ({m}x{n}x{k})")
+        prepared.append((qa, qb, got, want, m, n, k, gran_k, out_dtype))
+    # Nothing is allocated: with both kernels loaded by the calls above (the driver loads a kernel's code on first use),
+    # the free device memory the DRIVER reports - which sees every cudaMalloc, not only torch's caching allocator -
+    # must not move across further calls, and the results stay right.
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    torch_before = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
+    for qa, qb, got, want, m, n, k, gran_k, out_dtype in prepared + prepared[::-1]:
+        got.fill_(float("nan"))
+        call_noalloc(qa, qb, got, m, n, k, gran_k, out_dtype)
+        torch.cuda.synchronize()
+        dg.testing.assert_bitwise_equal(got, want, f"noalloc, repeated ({m}x{n}x{k})")
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, f"device memory moved by {free_before - free_after} bytes"
+    assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == torch_before
 
 
 def test_noalloc_gemm_rejects_problems_beyond_the_scratch():
