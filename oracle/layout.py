@@ -9,6 +9,11 @@ TEST INFRASTRUCTURE ONLY (see oracle/quant.py).  Integer-exact restatements of
 * PSUM gap-row zeroing (tests/test_layout.py:110-179);
 * the K-grouped packed layout (tests/test_layout.py:233-265);
 * the Mega MoE weight / scale permutations (deep_gemm/mega/__init__.py:167-220).
+
+Pinned: tests/golden/layout_golden.npz holds outputs of the reference's own Python for the packed layout
+(tests/test_layout.py:24-46) and for both permutations (deep_gemm/mega/__init__.py:167-198), produced by running those
+functions from the reference's text (tests/golden/make_layout_golden.py); tests/test_oracle_golden.py requires bit
+equality, strides included.
 """
 from __future__ import annotations
 

@@ -276,7 +276,7 @@ def test_mega_moe_pool_smaller_than_the_rows_is_reported():
     later call that fits runs normally on the same buffer."""
     hidden, inter, experts, topk, tokens = 1024, 512, 8, 4, 512
     forward, ref = _single_rank_case(hidden, inter, experts, topk, tokens)
-    buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter, num_ring_tokens=1024)
+    buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter, num_ring_tokens=512)
     assert buf.layout.pool_rows < tokens * topk
     for fused in (True, False):
         dg.mega.set_fused(fused)

@@ -138,3 +138,42 @@ def test_mega_moe_oracle_matches_reference_baseline():
                     ("y_situ_2_3", dict(activation="situ", situ_beta=2.0, situ_linear_beta=3.0))):
         y, _ = OM.mega_moe_reference(g["x_deq"], g["topk_idx"], g["topk_weights"], g["l1_deq"], g["l2_deq"], **kw)
         assert np.array_equal(y, g[tag]), tag
+
+
+def test_layout_oracle_matches_reference_text():
+    """oracle/layout.py against outputs of the reference's own Python for the packed MN-major scale layout
+    (tests/test_layout.py:24-46) and for the Mega MoE weight permutations (deep_gemm/mega/__init__.py:167-198), both
+    run from the reference's text by tests/golden/make_layout_golden.py.  Values and strides, bit for bit."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layout_golden.npz"))
+    for tag in ("p2", "p2b", "p3", "p1row"):
+        got = L.packed_ue8m0_mn_major(g[f"{tag}_sf"])
+        assert np.array_equal(np.ascontiguousarray(got), g[f"{tag}_packed"]), tag
+        mn = g[f"{tag}_sf"].shape[-2]
+        if mn > 1:      # a one-row tensor's strides carry no information
+            assert L.element_strides(got) == tuple(g[f"{tag}_strides"]), tag
+    assert np.array_equal(L.interleave_gate_up(g["w"]), g["w_interleaved"])
+    assert np.array_equal(L.interleave_gate_up(g["w2d"][None])[0], g["w2d_interleaved"])
+    il = L.interleave_gate_up(g["wsf"])
+    assert np.array_equal(il, g["wsf_interleaved"])
+    assert np.array_equal(L.transpose_sf_for_utccp(il), g["wsf_utccp"])
+    # the reference keeps the packed scales' MN-major strides through both permutations
+    assert tuple(g["wsf_utccp_strides"]) == tuple(g["wsf_in_strides"])
+
+
+def test_shipped_weight_transform_matches_reference_text():
+    """transform_weights_for_mega_moe of the package (torch, CPU tensors) against the same reference outputs,
+    strides included."""
+    import os
+    import torch
+    import deepgemm_b200 as dg
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layout_golden.npz"))
+    w = torch.from_numpy(g["w"])
+    sf = torch.from_numpy(np.ascontiguousarray(g["wsf"].transpose(0, 2, 1))).transpose(1, 2)   # MN-major [G, 2I, pk]
+    assert tuple(sf.stride()) == tuple(g["wsf_in_strides"])
+    w2 = torch.zeros((2, 128, 8), dtype=torch.int8)
+    sf2 = torch.zeros((2, 1, 128), dtype=torch.int32).transpose(1, 2)
+    (t1, tsf1), _ = dg.transform_weights_for_mega_moe((w, sf), (w2, sf2))
+    assert np.array_equal(t1.numpy(), g["w_interleaved"])
+    assert np.array_equal(tsf1.numpy(), g["wsf_utccp"])
+    assert tuple(tsf1.stride()) == tuple(g["wsf_utccp_strides"])
