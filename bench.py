@@ -282,6 +282,8 @@ def config_c3(device, steps, warmup, flush):
     g, max_m, n, k = 16, 1024, 4096, 7168
     rnd = random.Random(0)
     masked = [min(max_m, int(256 * rnd.uniform(0.5, 1.5))) for _ in range(g)]
+    if MASKED_ROWS_OVERRIDE:
+        masked = [MASKED_ROWS_OVERRIDE] * g          # tuning aid: every group with the same number of rows
     a_q = torch.empty((g, max_m, k), dtype=torch.float8_e4m3fn, device=device)
     a_s = torch.empty((g, max_m, k // 128), dtype=torch.float32, device=device)
     b_q = torch.empty((g, n, k), dtype=torch.float8_e4m3fn, device=device)
@@ -377,6 +379,8 @@ def config_fp4(device, steps, warmup, flush):
     return dict(ms=ms, tflops=tf, frac_of_4x_measured_bf16=tf / peak, frac_of_nominal_9000=tf / 9000.0,
                 calc_diff=float(calc_diff(np_of(d[:rows]), ref)), tolerance=5e-3, parity_sample=f"rows 0..{rows - 1}")
 
+
+MASKED_ROWS_OVERRIDE = 0
 
 CONFIGS = {"c1": ("c1_dense_fp8_4096x4096x7168", config_c1), "c4": ("c4_fp8xfp4_8192x7168x2048", config_c4),
            "c3": ("c3_masked_16x(256 of 1024)x4096x7168", config_c3),
@@ -720,6 +724,9 @@ def main():
                     help="profiling aid: `gemm` runs the headline GEMM alone (no other configs, no Mega MoE, no CPU "
                          "baseline); `mega_moe` the Mega MoE forward alone; c1 / c3 / c4 / kg / fp4 one other config alone")
     ap.add_argument("--tile", default="", help="tuning aid: cta_group,block_n,swap (0 = automatic) pinned for every GEMM")
+    ap.add_argument("--masked-costs", default="", help="tuning aid: first,next_base,next_per_256_rows of the masked GEMM's "
+                                                     "tile cost estimate (first = 0: round-robin deal)")
+    ap.add_argument("--masked-rows", type=int, default=0, help="tuning aid: config c3 with this many rows in every group")
     ap.add_argument("--moe-tokens", type=int, default=4096, help="tokens per rank of the Mega MoE run")
     ap.add_argument("--moe-experts", type=int, default=32, help="experts per rank of the Mega MoE run")
     ap.add_argument("--sustained-s", type=float, default=1.0, help="length of the back-to-back loop of the headline kernel")
@@ -746,6 +753,10 @@ def main():
     if args.tile:
         cta, bn, swap = (int(v) for v in args.tile.split(","))
         _lib.check(_lib.lib().dg_debug_set_tile_override(cta, bn, swap))
+    if args.masked_costs:
+        _lib.check(_lib.lib().dg_debug_set_masked_costs(*(int(v) for v in args.masked_costs.split(","))))
+    global MASKED_ROWS_OVERRIDE
+    MASKED_ROWS_OVERRIDE = args.masked_rows
 
     if args.only == "mega_moe":
         moe = mega_moe_bench(device, dist.group.WORLD if world > 1 else None, rank, world, max(1, min(args.steps, 10)),
@@ -758,7 +769,8 @@ def main():
     if args.only in CONFIGS:
         out = other_configs(device, max(1, min(args.steps, 10)), args.warmup, which=(args.only,))
         if rank == 0:
-            emit({"other_configs": out, "tile": args.tile or "automatic"})
+            emit({"other_configs": out, "tile": args.tile or "automatic", "masked_costs": args.masked_costs or "default",
+                  "masked_rows": args.masked_rows or "config"})
         return
 
     w = make_c2(device, seed=0)

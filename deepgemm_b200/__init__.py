@@ -21,8 +21,9 @@ from .layout import (  # noqa: F401
 from .ops import (  # noqa: F401
     fp8_fp4_gemm_nt, fp8_fp4_gemm_nn, fp8_fp4_gemm_tn, fp8_fp4_gemm_tt,
     m_grouped_fp8_fp4_gemm_nt_contiguous, m_grouped_fp8_fp4_gemm_nn_contiguous,
-    m_grouped_fp8_fp4_gemm_nt_masked, k_grouped_fp8_gemm_tn_contiguous,
+    m_grouped_fp8_fp4_gemm_nt_masked, k_grouped_fp8_gemm_tn_contiguous, k_grouped_fp4_gemm_nt_contiguous,
 )
+from .einsum import fp8_einsum  # noqa: F401
 
 from . import mega  # noqa: F401,E402
 from . import cast  # noqa: F401,E402
@@ -52,9 +53,11 @@ def k_grouped_fp8_gemm_nt_contiguous(*args, **kwargs):
                        "sm_100 takes k_grouped_fp8_gemm_tn_contiguous")
 
 
-class epilogue:  # namespace, as deep_gemm.epilogue
+class epilogue:  # namespace, as deep_gemm.epilogue (csrc/apis/epilogue_class.hpp:13-31 of the reference)
     Identity = _ops.Identity
     Alpha = _ops.Alpha
+    FP8CastWithClamp = _ops.FP8CastWithClamp
+    BF16StochasticRounding = _ops.BF16StochasticRounding
 
 
 # Process-wide knobs (csrc/apis/config.hpp:8-48 of the reference)
@@ -74,18 +77,18 @@ def get_tc_util() -> int:
     return int(_lib.lib().dg_get_tc_util())
 
 
-_pdl = False
 _deterministic = False
 
 
 def set_pdl(enable: bool) -> None:
-    """Accepted for compatibility; launches do not use programmatic dependent launch."""
-    global _pdl
-    _pdl = bool(enable)
+    """Launch the GEMM, scale-packing and cast kernels with programmatic dependent launch: a kernel's set-up (barriers,
+    tensor-memory allocation, descriptor prefetch) overlaps the tail of the kernel before it in the stream, and it
+    waits in-kernel before reading anything that kernel wrote (csrc/apis/config.hpp:27-32 of the reference)."""
+    _lib.check(_lib.lib().dg_set_pdl(int(bool(enable))))
 
 
 def get_pdl() -> bool:
-    return _pdl
+    return bool(_lib.lib().dg_get_pdl())
 
 
 def use_deterministic_algorithms(enable: bool) -> None:

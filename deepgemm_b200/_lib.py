@@ -11,7 +11,8 @@ import os
 from .build import LIB_PATH
 
 DG_E4M3, DG_E2M1_PACKED, DG_BF16, DG_F32 = 0, 1, 2, 3
-GEMM_NORMAL, GEMM_M_CONTIGUOUS, GEMM_M_MASKED, GEMM_M_PSUM, GEMM_K_GROUPED, GEMM_K_GROUPED_PSUM = range(6)
+GEMM_NORMAL, GEMM_M_CONTIGUOUS, GEMM_M_MASKED, GEMM_M_PSUM, GEMM_K_GROUPED, GEMM_K_GROUPED_PSUM, GEMM_BATCHED = range(7)
+EPILOGUE_STORE, EPILOGUE_STOCHASTIC_BF16, EPILOGUE_FP8_CAST = range(3)
 
 EXPORTS = (
     "dg_gemm_bs", "dg_sf_pack_ue8m0", "dg_sf_pack_ue8m0_k_grouped", "dg_set_num_sms", "dg_get_num_sms",
@@ -19,13 +20,14 @@ EXPORTS = (
     "dg_get_mk_alignment_for_contiguous_layout", "dg_get_theoretical_mk_alignment_for_contiguous_layout",
     "dg_set_wait_timeout_ms", "dg_check_status", "dg_last_error", "dg_version",
     "dg_mega_moe_buffer_layout", "dg_get_token_alignment_for_mega_moe", "dg_mega_moe_forward", "dg_set_mega_moe_fused", "dg_gemm_fp8_fp32sf_noalloc", "dg_noalloc_scratch_bytes",
-    "dg_per_token_cast_to_fp8", "dg_debug_set_tile_override", "dg_get_mega_moe_num_sms", "dg_debug_copy",
+    "dg_per_token_cast_to_fp8", "dg_debug_set_tile_override", "dg_get_mega_moe_num_sms", "dg_debug_copy", "dg_set_pdl", "dg_get_pdl", "dg_debug_set_masked_costs",
 )
 
 
 class Operand(C.Structure):
     _fields_ = [("data", C.c_void_p), ("sf", C.c_void_p), ("ld", C.c_int64), ("sf_ld", C.c_int64),
-                ("dtype", C.c_int32), ("mn_major", C.c_int32), ("gran_k", C.c_int32), ("reserved", C.c_int32)]
+                ("dtype", C.c_int32), ("mn_major", C.c_int32), ("gran_k", C.c_int32), ("reserved", C.c_int32),
+                ("batch_stride", C.c_int64), ("sf_k_rows", C.c_int64)]
 
 
 class GemmArgs(C.Structure):
@@ -34,7 +36,9 @@ class GemmArgs(C.Structure):
                 ("a", Operand), ("b", Operand),
                 ("d", C.c_void_p), ("ldd", C.c_int64), ("d_dtype", C.c_int32), ("accumulate", C.c_int32),
                 ("alpha", C.c_float), ("expected_m", C.c_int32),
-                ("grouped_layout", C.c_void_p), ("stream", C.c_void_p)]
+                ("grouped_layout", C.c_void_p), ("stream", C.c_void_p),
+                ("d_batch_stride", C.c_int64), ("epilogue", C.c_int32), ("clamp_value", C.c_float),
+                ("sfd", C.c_void_p), ("sfd_ld", C.c_int64), ("clamped_count", C.c_void_p)]
 
 
 class MoeConfig(C.Structure):
@@ -98,11 +102,12 @@ def lib() -> C.CDLL:
         l.dg_mega_moe_forward.argtypes = [C.POINTER(MoeArgs)]
         l.dg_gemm_fp8_fp32sf_noalloc.argtypes = [C.POINTER(GemmNoAllocArgs)]
         l.dg_per_token_cast_to_fp8.argtypes = [C.POINTER(CastArgs)]
-        for name in ("dg_set_num_sms", "dg_set_tc_util", "dg_set_mk_alignment_for_contiguous_layout",
+        for name in ("dg_set_num_sms", "dg_set_tc_util", "dg_set_pdl", "dg_set_mk_alignment_for_contiguous_layout",
                      "dg_get_theoretical_mk_alignment_for_contiguous_layout", "dg_set_wait_timeout_ms",
                      "dg_set_mega_moe_fused"):
             getattr(l, name).argtypes = [C.c_int32]
         l.dg_debug_set_tile_override.argtypes = [C.c_int32, C.c_int32, C.c_int32]
+        l.dg_debug_set_masked_costs.argtypes = [C.c_int32, C.c_int32, C.c_int32]
         l.dg_debug_copy.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
         _lib = l
     return _lib

@@ -14,7 +14,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_DIR = os.path.join(PKG_DIR, "lib")
 LIB_PATH = os.environ.get("DEEPGEMM_B200_LIB") or os.path.join(LIB_DIR, "libdeepgemm_b200.so")
-SOURCES = ["lib.cu"]
+SOURCES = ["lib.cu", "gemm_inst_plain.cu", "gemm_inst_moe.cu", "gemm_inst_mxf4.cu", "gemm_inst_epi.cu"]
 PUBLIC_HEADER = os.path.join(PKG_DIR, "..", "include", "deepgemm_b200.h")
 
 
@@ -39,21 +39,35 @@ def needs_build() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile every CUDA source for sm_100a into one shared library; returns its path."""
+    """Compile every CUDA source for sm_100a (one nvcc per source, in parallel) and link one shared library; returns
+    its path."""
     if not force and not needs_build():
         return LIB_PATH
+    from concurrent.futures import ThreadPoolExecutor
     os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = [
-        nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-        "-shared", "-Xcompiler", "-fPIC", "-o", LIB_PATH,
-    ] + [os.path.join(CSRC, s) for s in SOURCES]
+    obj_dir = os.path.join(LIB_DIR, "obj")
+    os.makedirs(obj_dir, exist_ok=True)
+    nvcc = nvcc_path()
+    flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
     if verbose:
-        cmd += ["-Xptxas", "-v"]
-    res = subprocess.run(cmd, capture_output=True, text=True)
+        flags += ["-Xptxas", "-v"]
+
+    def compile_one(src):
+        obj = os.path.join(obj_dir, os.path.splitext(src)[0] + ".o")
+        res = subprocess.run([nvcc, *flags, "-c", os.path.join(CSRC, src), "-o", obj], capture_output=True, text=True)
+        return src, obj, res
+
+    with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
+        results = list(pool.map(compile_one, SOURCES))
+    for src, _, res in results:
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src}:\n" + res.stdout + res.stderr)
+        if verbose:
+            sys.stderr.write(res.stderr)
+    res = subprocess.run([nvcc, "-shared", "-o", LIB_PATH] + [obj for _, obj, _ in results],
+                         capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-    if verbose:
-        sys.stderr.write(res.stderr)
+        raise RuntimeError("linking failed:\n" + res.stdout + res.stderr)
     return LIB_PATH
 
 

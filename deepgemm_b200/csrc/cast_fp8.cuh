@@ -36,6 +36,8 @@ constexpr uint32_t kCastUnroll = 4;   // 16-byte loads in flight per lane
 
 // One warp per row at a time; a lane owns 8 consecutive elements of each of kCastUnroll 256-element spans.
 __global__ void __launch_bounds__(kCastThreads) cast_bf16_to_fp8_ue8m0_kernel(const CastParams p) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");                // x may come from the kernel before this one
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the consumer waits for this kernel's end itself
     const uint32_t lane = threadIdx.x % 32;
     const uint32_t warp = (blockIdx.x * kCastThreads + threadIdx.x) / 32, num_warps = gridDim.x * kCastThreads / 32;
     const uint32_t lanes_per_group = p.gran_k / 8;                    // 4 or 16

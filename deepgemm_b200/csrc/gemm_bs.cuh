@@ -14,8 +14,13 @@
 // kSwap = true : R = GEMM B (weights), C = GEMM A (tokens): the accumulator is D^T, which
 //                lets a CTA pair share one (possibly short) token block of any expert.
 //
-// Warp roles (256 threads):  0 TMA producer | 1 UMMA issuer (+TMEM owner) | 2 scale-factor
-// transposer | 3 idle | 4..7 epilogue (warp % 4 == TMEM lane quadrant).
+// Warp roles (288 threads):  0 TMA producer of the R tiles | 1 UMMA issuer (+TMEM owner) | 2 scale-factor
+// transposer | 3 TMA producer of the scale factors | 4..7 epilogue (warp % 4 == TMEM lane quadrant) |
+// 8 TMA producer of the C tiles.
+//
+// Two UMMA kinds: kind::mxf8f6f4 (E4M3 and unpacked E2M1 operands, 128 K elements per stage, UMMA K = 32) and, when
+// both operands are packed E2M1, kind::mxf4 (256 K elements per stage in the same 128 bytes per row, UMMA K = 64,
+// two scale words per row and stage: the 9 PFLOP/s path; sm100_fp8_fp4_gemm_1d1d.cuh:51-54 of the reference).
 //
 // Every wait is bounded: on expiry the waiting thread records where it gave up in the
 // status block, raises the CTA's (and its pair's) abort flag, all roles leave their
@@ -36,6 +41,16 @@ enum GemmType : uint32_t {
     kGemmMPsum = 3,         // grouped_layout: int32[G], cumulative unaligned row ends
     kGemmKGrouped = 4,      // grouped_layout: int32[G], padded K per group
     kGemmKGroupedPsum = 5,  // grouped_layout: int32[G], cumulative unaligned K ends
+    kGemmBatched = 6,       // num_groups independent m x n x k problems (no layout tensor)
+};
+
+// Epilogue kinds (GemmConfig::kEpi)
+enum EpilogueKind : int {
+    kEpiStore = 0,       // D = alpha * acc, or D += acc
+    kEpiMoeL1 = 1,       // Mega MoE: gated activation + requantisation
+    kEpiMoeL2 = 2,       // Mega MoE: BF16 rows pushed to the source ranks
+    kEpiStochastic = 3,  // BF16 D with stochastic rounding (epilogue/operators.cuh:53-114 of the reference)
+    kEpiFp8Cast = 4,     // E4M3 D with per-32 UE8M0 scales, optional clamp and clamp count (:116-220)
 };
 
 enum StatusCode : uint32_t {
@@ -53,6 +68,8 @@ enum WaitSite : uint32_t {
 };
 
 // One UMMA operand as the kernel sees it (all values computed on the host).
+constexpr uint32_t kMaxBalancedGroups = 256;   // masked layouts with more groups keep the round-robin deal
+
 struct OperandParams {
     uint32_t mn_major;    // 0: K is the contiguous axis in global memory
     uint32_t num_boxes;   // TMA boxes per stage per CTA
@@ -64,6 +81,16 @@ struct OperandParams {
     uint32_t desc_kstep;  // descriptor start-address advance per UMMA_K (32 elements), bytes
     uint32_t gran_k;      // 32 or 128 K elements per scale
     uint32_t fmt;         // kFmtE4M3 / kFmtE2M1
+    uint32_t batched;     // the tensor map's third coordinate is the tile's group (0: always 0)
+};
+
+// Arguments of the value epilogues (kEpiStochastic needs none; kEpiFp8Cast all).
+struct CastEpilogueParams {
+    uint32_t* sfd;            // packed UE8M0 words: scale of (row, column group g) in byte g % 4 of word
+                              // sfd[(g / 4) * sfd_ld + row], g = (batch * n + column) / 32
+    int64_t sfd_ld;
+    float clamp_bound;        // BF16-rounded clamp value; +inf = no clamp
+    uint32_t* clamped_count;  // optional: += elements whose BF16 magnitude exceeds the bound
 };
 
 // Arguments of the fused Mega MoE epilogues.
@@ -109,15 +136,16 @@ struct GemmParams {
     uint32_t raster;            // tiles along the rasterised axis per super-row
     uint32_t num_units;         // CTAs (kCtas == 1) or CTA pairs (kCtas == 2) in the grid
     uint32_t sf_groups_r, sf_groups_c;     // packed-K words per group in the SF tensors (0: not grouped)
-    uint32_t rows_per_group_r, rows_per_group_c;  // row stride between groups of a K-major operand (0: none)
-    uint32_t k_rows_per_group_r, k_rows_per_group_c;  // K-row stride between groups of an MN-major operand
     float alpha;
     uint32_t accumulate;        // D += result (TMA reduce-add) instead of D = result
     uint32_t d_grouped;         // D has a group axis (masked / K-grouped): third store coordinate = group
     uint32_t split_blocks;      // contiguous layout: a schedule slot spans two alignment units (may straddle experts)
     uint32_t r_sf_pretransposed;  // R's scale words already sit in the 32x4 order tcgen05.cp reads (Mega MoE weights)
     uint32_t c_sf_pretransposed;  // same for C (Mega MoE activations: the pool is written in that order)
-    MoeEpilogueParams moe;      // fused Mega MoE epilogues (GemmConfig::kEpi != 0)
+    MoeEpilogueParams moe;      // fused Mega MoE epilogues (GemmConfig::kEpi == 1, 2)
+    CastEpilogueParams cast;    // kEpiFp8Cast
+    uint32_t balance_masked;    // masked layout: cost-balanced runs of slots per unit instead of a round-robin deal
+    uint32_t cost_first, cost_next_base, cost_next_per_256_rows;   // tile cost estimates, see masked_balanced_run
     uint32_t timeout_ms;
     uint32_t* status;           // 16 words: [0] code, [1] site, [2] block, [3] tile iter, [4] k block, [5] stage
     unsigned long long* trace;  // optional clock samples of block 0's first tile (builds with DG_TRACE only)
@@ -204,6 +232,16 @@ struct TileWalker {
         c.k_start = 0, c.k_len = p.k, c.sfk_base = 0, c.group = 0, c.rows = bm;
         const uint32_t num_n = p.num_n_blocks;
         uint32_t m_blk;
+        if (p.gemm_type == kGemmBatched) {
+            // every batch owns a full m x n tile grid
+            const uint32_t per_group = p.num_m_blocks * num_n;
+            if (t >= per_group * p.num_groups) return 0;
+            const uint32_t g = t / per_group;
+            swizzle(t - g * per_group, p.num_m_blocks, num_n, m_blk, c.n_blk);
+            c.row0 = m_blk * bm, c.group = g;
+            if (swap) c.rows = min(bm, align16(p.m - c.row0));
+            return 1;
+        }
         if (p.gemm_type == kGemmNormal || p.gemm_type == kGemmMContiguous) {
             if (t >= p.num_m_blocks * num_n) return 0;
             swizzle(t, p.num_m_blocks, num_n, m_blk, c.n_blk);
@@ -268,10 +306,14 @@ struct TileWalker {
     }
 };
 
-template <int kCtas_, int BN_, bool kSwap_, bool kCdF32_, int kEpi_ = 0>
+template <int kCtas_, int BN_, bool kSwap_, bool kCdF32_, int kEpi_ = 0, bool kMxf4_ = false>
 struct GemmConfig {
-    static constexpr int kEpi = kEpi_;   // 0: store D; 1 / 2: fused Mega MoE epilogues (swapped tiles only)
-    static_assert(kEpi_ == 0 || kSwap_, "the fused epilogues work on D^T tiles");
+    static constexpr int kEpi = kEpi_;   // EpilogueKind
+    static constexpr bool kMoeEpi = kEpi_ == kEpiMoeL1 || kEpi_ == kEpiMoeL2;
+    static_assert(!kMoeEpi || kSwap_, "the fused Mega MoE epilogues work on D^T tiles");
+    static_assert(!(kEpi_ == kEpiStochastic || kEpi_ == kEpiFp8Cast) || (!kSwap_ && !kCdF32_),
+                  "the value epilogues work on D tiles with 16-bit or 8-bit output");
+    static constexpr bool kMxf4 = kMxf4_;   // both operands packed E2M1: kind::mxf4, 256 K elements per stage
     static constexpr int kCtas = kCtas_;
     static constexpr int BN = BN_;
     static constexpr bool kSwap = kSwap_;
@@ -280,26 +322,29 @@ struct GemmConfig {
     static_assert(BN % 16 == 0 && BN >= 32 && BN <= 256, "UMMA N");
 
     static constexpr uint32_t kThreads = 288;   // warps 0-3: R copies, UMMA, scale transposer, scale copies; 4-7: epilogue; 8: C copies
-    static constexpr uint32_t BLOCK_K = 128;
+    static constexpr uint32_t BLOCK_K = 128;          // bytes of K per row and stage
+    static constexpr uint32_t BLOCK_K_ELEMS = kMxf4 ? 256 : 128;
+    static constexpr uint32_t SF_WORDS = kMxf4 ? 2 : 1;   // packed scale words (128 K elements each) per row and stage
     static constexpr uint32_t R_ROWS = 128;
     static constexpr uint32_t C_ROWS_PER_CTA = BN / kCtas;
     static constexpr uint32_t R_STAGE = R_ROWS * BLOCK_K;
     static constexpr uint32_t C_STAGE = C_ROWS_PER_CTA * BLOCK_K;
     static constexpr uint32_t SFC_ROWS = (BN + 127) / 128 * 128;
-    static constexpr uint32_t SFR_STAGE = 128 * 4;
-    static constexpr uint32_t SFC_STAGE = SFC_ROWS * 4;
+    static constexpr uint32_t SFR_STAGE = 128 * 4 * SF_WORDS;
+    static constexpr uint32_t SFC_STAGE = SFC_ROWS * 4 * SF_WORDS;
     static constexpr uint32_t STAGE_BYTES = R_STAGE + C_STAGE + SFR_STAGE + SFC_STAGE;
 
     // Epilogue staging: each epilogue warp owns one slab per buffer and stores it by itself.
     //   D tile:   32 rows x 128 B (64 BF16 or 32 FP32 columns), 128 B swizzle
     //   D^T tile: 32 tokens x 32 BF16 (64 B rows), no swizzle
+    //   E4M3 D tile (kEpiFp8Cast): 32 rows x 64 B, no swizzle
     static constexpr uint32_t CHUNK_COLS = kSwap ? 32 : (kCdF32 ? 32 : 64);
-    static constexpr uint32_t SLAB_BYTES = kSwap ? 32 * 64 : 32 * 128;
+    static constexpr uint32_t SLAB_BYTES = (kSwap || kEpi == kEpiFp8Cast) ? 32 * 64 : 32 * 128;
     static constexpr uint32_t kStoreBufs = (kCtas == 1 && BN == 256) ? 1 : 2;
     // Fused epilogues stage 32 tokens x 128 rows of BF16 per buffer (row pitch padded for kEpi == 1)
     static constexpr uint32_t MOE_PITCH = kEpi == 1 ? 272 : 256;
-    static constexpr uint32_t CD_BYTES = kEpi == 0 ? kStoreBufs * 4 * SLAB_BYTES
-                                                   : (2 * 32 * MOE_PITCH + 2 * 256 * 8 + 1023) / 1024 * 1024;
+    static constexpr uint32_t CD_BYTES = !kMoeEpi ? kStoreBufs * 4 * SLAB_BYTES
+                                                  : (2 * 32 * MOE_PITCH + 2 * 256 * 8 + 1023) / 1024 * 1024;
     static constexpr uint32_t MOE_TABLE_OFF = 2 * 32 * MOE_PITCH;   // per-tile token tables, two copies
 
     static constexpr uint32_t kSmemLimit = 232448;
@@ -314,12 +359,14 @@ struct GemmConfig {
     // kOverlap columns: the last columns of stage 0 are the first columns of stage 1.  The epilogue
     // drains the shared columns first (stage 0 back to front, stage 1 front to back) and tells the
     // UMMA issuer, which only then lets the next tile write them.
-    static constexpr uint32_t SFC_COLS = SFC_ROWS / 32;
-    static constexpr uint32_t kOverlap = (2 * BN + 4 + SFC_COLS > 512) ? 16 : 0;
+    static constexpr uint32_t SFR_COLS = 4 * SF_WORDS;
+    static constexpr uint32_t SFC_COLS_PER_WORD = SFC_ROWS / 32;
+    static constexpr uint32_t SFC_COLS = SFC_COLS_PER_WORD * SF_WORDS;
+    static constexpr uint32_t kOverlap = (2 * BN + SFR_COLS + SFC_COLS > 512) ? (2 * BN + SFR_COLS + SFC_COLS - 512 + 15) / 16 * 16 : 0;
     static_assert(kOverlap <= CHUNK_COLS, "the shared columns must lie in one epilogue chunk");
     static constexpr uint32_t kAccStride = BN - kOverlap;
     static constexpr uint32_t kSfrCol = 2 * BN - kOverlap;
-    static constexpr uint32_t kSfcCol = kSfrCol + 4;
+    static constexpr uint32_t kSfcCol = kSfrCol + SFR_COLS;
     static constexpr uint32_t kUsedCols = kSfcCol + SFC_COLS;
     static constexpr uint32_t kTmemCols = kUsedCols <= 32 ? 32 : kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128
                                           : kUsedCols <= 256 ? 256 : 512;
@@ -340,10 +387,64 @@ struct alignas(8) GemmBarriers {
     uint64_t epi_sync[2];   // fused epilogues: the four epilogue warps meet here once per chunk
     uint32_t tmem_base;
     uint32_t abort;
+    uint32_t sched_first, sched_end;   // masked layout: this unit's run of consecutive schedule slots
+    uint16_t group_rows[kMaxBalancedGroups];   // masked layout: the groups' row counts, staged for the cost scan
 };
 static_assert(sizeof(GemmBarriers) <= 1024, "barrier block");
 
-__device__ __noinline__ void report_timeout(const GemmParams& p, uint32_t site, uint32_t iter, uint32_t kb,
+// Masked layout: schedule slots are not dealt round robin but cut into one run of consecutive slots per unit, the runs
+// balanced by an estimate of each tile's cost.  A group's weight tile (one n block) streams from HBM for the first
+// token block that uses it and comes from L2 for the following ones, which sit right behind it in the same unit's
+// run: tiles differ a lot in cost (first token block: the HBM-bound stream; others: a re-run over cached weights with
+// few tokens), and a round-robin deal leaves some units with only expensive tiles.  Costs are in 1/256 of a first tile.
+// All units evaluate the same integer arithmetic on the same masked_m values, so the runs partition the slots.
+// Called by one thread; rows[] holds the groups' row counts.
+struct MaskedCosts {
+    uint32_t first, next_base, next_per_256_rows;
+};
+DG_DEVICE void masked_balanced_run(const uint16_t* rows, uint32_t num_groups, uint32_t bm, uint32_t num_n,
+                                   const MaskedCosts& mc, uint32_t unit, uint32_t num_units, uint32_t& first_slot,
+                                   uint32_t& end_slot) {
+    auto column_cost = [&](uint32_t r, uint32_t mb) -> uint32_t {   // all token blocks of one n block of a group
+        if (mb == 0) return 0;
+        uint32_t c = mc.first;
+        for (uint32_t j = 1; j < mb; ++j) c += mc.next_base + min(bm, r - j * bm) * mc.next_per_256_rows / 256u;
+        return c;
+    };
+    uint64_t total = 0;
+    for (uint32_t g = 0; g < num_groups; ++g) {
+        const uint32_t r = rows[g], mb = (r + bm - 1) / bm;
+        total += static_cast<uint64_t>(column_cost(r, mb)) * num_n;
+    }
+    // first slot whose middle lies at or beyond `target` on the cost axis
+    auto slot_at = [&](uint64_t target) -> uint32_t {
+        uint64_t prefix = 0;
+        uint32_t slots = 0;
+        for (uint32_t g = 0; g < num_groups; ++g) {
+            const uint32_t r = rows[g], mb = (r + bm - 1) / bm;
+            const uint32_t cc = column_cost(r, mb);
+            const uint64_t gc = static_cast<uint64_t>(cc) * num_n;
+            if (cc != 0 && prefix + gc > target) {
+                const uint64_t into = target > prefix ? target - prefix : 0;
+                const uint32_t col = static_cast<uint32_t>(into / cc);
+                uint32_t rem = static_cast<uint32_t>(into - static_cast<uint64_t>(col) * cc), j = 0, start = 0;
+                // first tile of the column whose middle is >= rem (a tile goes to the unit that holds its middle)
+                while (j < mb) {
+                    const uint32_t c = j == 0 ? mc.first : mc.next_base + min(bm, r - j * bm) * mc.next_per_256_rows / 256u;
+                    if (start + c / 2 >= rem) break;
+                    start += c, ++j;
+                }
+                return slots + col * mb + j;   // j == mb: the next column's first tile
+            }
+            prefix += gc, slots += mb * num_n;
+        }
+        return slots;
+    };
+    first_slot = slot_at((total * unit + num_units - 1) / num_units);
+    end_slot = unit + 1 == num_units ? slot_at(total) : slot_at((total * (unit + 1) + num_units - 1) / num_units);
+}
+
+static __device__ __noinline__ void report_timeout(const GemmParams& p, uint32_t site, uint32_t iter, uint32_t kb,
                                             uint32_t stage) {
     if (atomicCAS(p.status, kStatusOk, kStatusTimeout) == kStatusOk) {
         p.status[1] = site;
@@ -566,11 +667,30 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
     if (warp == 1) {
         tmem_alloc<kCtas>(&bars->tmem_base, Cfg::kTmemCols);
         tmem_relinquish<kCtas>();
+    } else if (warp == 2 && p.balance_masked) {
+        // this unit's run of schedule slots (masked_m is read here: wait for the kernel that may have written it)
+        grid_dependency_wait();
+        for (uint32_t g = lane; g < p.num_groups; g += 32)
+            bars->group_rows[g] = static_cast<uint16_t>(min(static_cast<uint32_t>(max(__ldg(p.grouped_layout + g), 0)), p.m));
+        __syncwarp();
+        if (lane == 0) {
+            MaskedCosts mc{p.cost_first, p.cost_next_base, p.cost_next_per_256_rows};
+            uint32_t first_slot, end_slot;
+            masked_balanced_run(bars->group_rows, p.num_groups, Cfg::UNIT_M, p.num_n_blocks, mc,
+                                kPair ? blockIdx.x / 2 : blockIdx.x, p.num_units, first_slot, end_slot);
+            bars->sched_first = first_slot, bars->sched_end = end_slot;
+        }
     }
     tc_fence_before();
     if (kPair) cluster_sync(); else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+    // Everything above touched this CTA's own state only.  From here on global memory is read that an earlier kernel of
+    // the stream may have written (packed scales, a producer's activations): with programmatic dependent launch this
+    // is where that kernel's completion is awaited; the next kernel of the stream may start its own set-up already.
+    grid_dependency_wait();
+    grid_launch_dependents();
 
     // Barrier addresses in the leader CTA (own CTA when not paired)
     auto leader_addr = [&](uint64_t* bar) -> uint32_t {
@@ -589,6 +709,10 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
     };
     TileWalker walker(p, Cfg::UNIT_M, Cfg::UNIT_N, kSwap);
     TileCoord tiles[2];
+    // Schedule slots of this unit: unit, unit + num_units, ... or (balanced masked layout) one run of consecutive slots
+    const uint32_t slot_first = p.balance_masked ? bars->sched_first : unit;
+    const uint32_t slot_stride = p.balance_masked ? 1u : p.num_units;
+    const uint32_t slot_end = p.balance_masked ? bars->sched_end : 0xFFFFFFFFu;
     bool ok = true;
     uint32_t acc_iter = 0;   // accumulator tiles handled so far by this role
 
@@ -604,26 +728,28 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
         const uint32_t r_boxes = p.r.num_boxes, r_box_bytes = p.r.box_bytes, r_box_mn = p.r.box_mn;
         const uint32_t c_boxes = p.c.num_boxes, c_box_bytes = p.c.box_bytes, c_box_mn = p.c.box_mn;
         const bool r_mn_major = p.r.mn_major != 0, c_mn_major = p.c.mn_major != 0;
-        // Group strides of GEMM A / GEMM B (A is C when swapped)
-        const uint32_t rpg_a = kSwap ? p.rows_per_group_c : p.rows_per_group_r;
-        const uint32_t rpg_b = kSwap ? p.rows_per_group_r : p.rows_per_group_c;
-        const uint32_t kpg_a = kSwap ? p.k_rows_per_group_c : p.k_rows_per_group_r;
-        const uint32_t kpg_b = kSwap ? p.k_rows_per_group_r : p.k_rows_per_group_c;
         const uint32_t sfg_a = kSwap ? p.sf_groups_c : p.sf_groups_r;
         const uint32_t sfg_b = kSwap ? p.sf_groups_r : p.sf_groups_c;
+        const bool r_batched = p.r.batched != 0, c_batched = p.c.batched != 0;
         for (uint32_t iter = 0; ok; ++iter) {
-            const uint32_t num_sub = walker.next(iter * p.num_units + unit, tiles);
+            const uint32_t slot = slot_first + iter * slot_stride;
+            if (slot >= slot_end) break;
+            const uint32_t num_sub = walker.next(slot, tiles);
             if (num_sub == 0) break;
             for (uint32_t sub = 0; sub < num_sub && ok; ++sub, ++acc_iter) {
                 const TileCoord& tc = tiles[sub];
                 // Operand coordinates of this tile (GEMM A / B, then mapped to R / C)
-                const uint32_t a_mn = tc.row0 + tc.group * rpg_a, b_mn = tc.n_blk * Cfg::UNIT_N + tc.group * rpg_b;
-                const uint32_t a_k = tc.k_start + tc.group * kpg_a, b_k = tc.k_start + tc.group * kpg_b;
+                // Data: (K, row inside the group, group) through 3-D tensor maps; the K coordinate counts the map's
+                // elements (bytes for E4M3 and for packed E2M1 under kind::mxf4)
+                const uint32_t a_mn = tc.row0, b_mn = tc.n_blk * Cfg::UNIT_N;
+                const uint32_t k0 = Cfg::kMxf4 ? tc.k_start >> 1 : tc.k_start;
+                const int32_t r_batch = r_batched ? static_cast<int32_t>(tc.group) : 0;
+                const int32_t c_batch = c_batched ? static_cast<int32_t>(tc.group) : 0;
                 const uint32_t sfa_k = tc.sfk_base + tc.group * sfg_a, sfb_k = tc.sfk_base + tc.group * sfg_b;
                 // SF rows are addressed inside the group (the group offset is on the packed-K axis)
                 const uint32_t sfa_mn = tc.row0, sfb_mn = tc.n_blk * Cfg::UNIT_N;
                 uint32_t r_mn = kSwap ? b_mn : a_mn, c_mn = kSwap ? a_mn : b_mn;
-                const uint32_t r_k = kSwap ? b_k : a_k, c_k = kSwap ? a_k : b_k;
+                const uint32_t r_k = k0, c_k = k0;
                 uint32_t sfr_mn = kSwap ? sfb_mn : sfa_mn;
                 const uint32_t sfc_mn = kSwap ? sfa_mn : sfb_mn;
                 const uint32_t sfr_k = kSwap ? sfb_k : sfa_k, sfc_k = kSwap ? sfa_k : sfb_k;
@@ -640,7 +766,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                         else if (per_cta <= 64) tm_c_tile = &p.tm_c_small[1], tile_tx_bytes = p.r.tx_bytes + 64 * 128;
                     }
                 }
-                const uint32_t num_kb = max(1u, (tc.k_len + 127u) / 128u);
+                const uint32_t num_kb = max(1u, (tc.k_len + Cfg::BLOCK_K_ELEMS - 1) / Cfg::BLOCK_K_ELEMS);
                 for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
                     DG_TRACE_AT(0, kb);
                     ok = wait_barrier(&bars->empty[stage], phase ^ 1, abort_flag, peer_abort, p, kSiteProducerEmpty,
@@ -654,13 +780,13 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                         if ((kb & sf_mask_r) == 0) {
                             tma_load_2d<false>(smem_sfr + stage * Cfg::SFR_STAGE, &p.tm_sfr, sf_bar,
                                                static_cast<int32_t>(sfr_mn),
-                                               static_cast<int32_t>(sfr_k + (kb >> sf_shift_r)));
+                                               static_cast<int32_t>(sfr_k + (Cfg::kMxf4 ? kb * 2 : kb >> sf_shift_r)));
                             sf_bytes += Cfg::SFR_STAGE;
                         }
                         if ((kb & sf_mask_c) == 0) {
                             tma_load_2d<false>(smem_sfc + stage * Cfg::SFC_STAGE, &p.tm_sfc, sf_bar,
                                                static_cast<int32_t>(sfc_mn),
-                                               static_cast<int32_t>(sfc_k + (kb >> sf_shift_c)));
+                                               static_cast<int32_t>(sfc_k + (Cfg::kMxf4 ? kb * 2 : kb >> sf_shift_c)));
                             sf_bytes += Cfg::SFC_STAGE;
                         }
                         mbar_arrive_expect_tx(&bars->sf_full[stage], sf_bytes);
@@ -674,8 +800,8 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                         for (uint32_t b = 0; b < r_boxes; ++b) {
                             const uint32_t dst = smem_r + stage * Cfg::R_STAGE + b * r_box_bytes;
                             const uint32_t mn = r_mn + b * r_box_mn;
-                            if (r_mn_major) tma_load_2d<kPair>(dst, &p.tm_r, full_bar, mn, kr);
-                            else            tma_load_2d<kPair>(dst, &p.tm_r, full_bar, kr, mn);
+                            if (r_mn_major) tma_load_3d<kPair>(dst, &p.tm_r, full_bar, mn, kr, r_batch);
+                            else            tma_load_3d<kPair>(dst, &p.tm_r, full_bar, kr, mn, r_batch);
                         }
                       }
                     } else if (elect_one()) {
@@ -685,8 +811,8 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                         for (uint32_t b = 0; b < c_boxes; ++b) {
                             const uint32_t dst = smem_c + stage * Cfg::C_STAGE + b * c_box_bytes;
                             const uint32_t mn = c_mn + b * c_box_mn;
-                            if (c_mn_major) tma_load_2d<kPair>(dst, &p.tm_c, full_bar, mn, kc);
-                            else            tma_load_2d<kPair>(dst, tm_c_tile, full_bar, kc, mn);
+                            if (c_mn_major) tma_load_3d<kPair>(dst, &p.tm_c, full_bar, mn, kc, c_batch);
+                            else            tma_load_3d<kPair>(dst, tm_c_tile, full_bar, kc, mn, c_batch);
                         }
                     }
                     __syncwarp();
@@ -698,8 +824,9 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
         // Whole warp in the loop, one elected lane issues (always the same lane, so that
         // tcgen05.commit covers every UMMA issued before it).
         if (is_leader) {
-            const uint32_t idesc_base = make_idesc_mxf8f6f4(p.r.fmt, p.c.fmt, p.r.mn_major != 0, p.c.mn_major != 0,
-                                                            128 * kCtas, BN);
+            const uint32_t idesc_base = Cfg::kMxf4
+                ? make_idesc_mxf4(128 * kCtas, BN)
+                : make_idesc_mxf8f6f4(p.r.fmt, p.c.fmt, p.r.mn_major != 0, p.c.mn_major != 0, 128 * kCtas, BN);
             const uint64_t sf_desc_hi = make_smem_desc(0, 0, 128, kSwizzleNone);
             // Operand descriptors: constant high word; the low word carries (address >> 4) and the LBO field
             const uint32_t r_hi = static_cast<uint32_t>(make_smem_desc(0, p.r.desc_lbo, p.r.desc_sbo, kSwizzle128B) >> 32);
@@ -711,7 +838,9 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
             const uint32_t r_per32 = p.r.gran_k == 32 ? 1u : 0u, c_per32 = p.c.gran_k == 32 ? 1u : 0u;
             const uint32_t sfr_tmem = tmem_base + Cfg::kSfrCol, sfc_tmem = tmem_base + Cfg::kSfcCol;
             for (uint32_t iter = 0; ok; ++iter) {
-                const uint32_t num_sub = walker.next(iter * p.num_units + unit, tiles);
+                const uint32_t slot = slot_first + iter * slot_stride;
+                if (slot >= slot_end) break;
+                const uint32_t num_sub = walker.next(slot, tiles);
                 if (num_sub == 0) break;
                 for (uint32_t sub = 0; sub < num_sub && ok; ++sub, ++acc_iter) {
                     const TileCoord& tc = tiles[sub];
@@ -730,7 +859,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + acc * Cfg::kAccStride;
                     const uint32_t idesc_tile = kSwap ? idesc_with_n(idesc_base, tc.rows) : idesc_base;
-                    const uint32_t num_kb = max(1u, (tc.k_len + 127u) / 128u);
+                    const uint32_t num_kb = max(1u, (tc.k_len + Cfg::BLOCK_K_ELEMS - 1) / Cfg::BLOCK_K_ELEMS);
                     for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
                         DG_TRACE_AT(3, kb);
                         ok = wait_barrier(&bars->full[stage], phase, abort_flag, peer_abort, p, kSiteMmaFull, acc_iter,
@@ -740,15 +869,24 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                         tc_fence_after();
                         if (elect_one()) {
                             // Fresh scale factors: shared memory (already in 32x4 order) -> TMEM
+                            // (kind::mxf4: two scale words per row; word w of 128 rows i sits at
+                            // (w * rows + i * 128) * 4 in the stage and goes to columns w * rows / 32 + i * 4)
                             if ((kb & sf_mask_r) == 0) {
-                                const uint32_t a = smem_sfr + stage * Cfg::SFR_STAGE;
-                                utccp_32x128b_warpx4<kCtas>(sfr_tmem, sf_desc_hi | (a >> 4));
+#pragma unroll
+                                for (uint32_t w = 0; w < Cfg::SF_WORDS; ++w) {
+                                    const uint32_t a = smem_sfr + stage * Cfg::SFR_STAGE + w * 512;
+                                    utccp_32x128b_warpx4<kCtas>(sfr_tmem + w * 4, sf_desc_hi | (a >> 4));
+                                }
                             }
                             if ((kb & sf_mask_c) == 0) {
 #pragma unroll
-                                for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i) {
-                                    const uint32_t a = smem_sfc + stage * Cfg::SFC_STAGE + i * 512;
-                                    utccp_32x128b_warpx4<kCtas>(sfc_tmem + i * 4, sf_desc_hi | (a >> 4));
+                                for (uint32_t w = 0; w < Cfg::SF_WORDS; ++w) {
+#pragma unroll
+                                    for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i) {
+                                        const uint32_t a = smem_sfc + stage * Cfg::SFC_STAGE + (w * Cfg::SFC_ROWS + i * 128) * 4;
+                                        utccp_32x128b_warpx4<kCtas>(sfc_tmem + w * Cfg::SFC_COLS_PER_WORD + i * 4,
+                                                                    sf_desc_hi | (a >> 4));
+                                    }
                                 }
                             }
                             const uint32_t r_lo = r_lo0 + stage * (Cfg::R_STAGE >> 4);
@@ -761,8 +899,16 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                             for (uint32_t ks = 0; ks < 4; ++ks) {
                                 const uint64_t r_desc = (static_cast<uint64_t>(r_hi) << 32) | (r_lo + ks * r_kstep);
                                 const uint64_t c_desc = (static_cast<uint64_t>(c_hi) << 32) | (c_lo + ks * c_kstep);
-                                umma_mxf8f6f4<kCtas>(d_tmem, r_desc, c_desc, idesc_kb + ks * idesc_ks, sfr_tmem,
-                                                     sfc_tmem, (kb | ks) != 0);
+                                if constexpr (Cfg::kMxf4) {
+                                    // UMMA K = 64: scale bytes (ks % 2) * 2 and + 1 of word ks / 2, on both sides
+                                    const uint32_t id = (ks & 1u) * 2u;
+                                    umma_mxf4<kCtas>(d_tmem, r_desc, c_desc, idesc_tile | (id << 4) | (id << 29),
+                                                     sfr_tmem + (ks >> 1) * 4, sfc_tmem + (ks >> 1) * Cfg::SFC_COLS_PER_WORD,
+                                                     (kb | ks) != 0);
+                                } else {
+                                    umma_mxf8f6f4<kCtas>(d_tmem, r_desc, c_desc, idesc_kb + ks * idesc_ks, sfr_tmem,
+                                                         sfc_tmem, (kb | ks) != 0);
+                                }
                             }
                             umma_commit<kCtas>(&bars->empty[stage]);   // frees the stage (in both CTAs)
                             if (kb + 1 == num_kb) umma_commit<kCtas>(&bars->tmem_full[acc]);
@@ -778,10 +924,12 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
         // tcgen05.cp 32x128b.warpx4 wants, per 128 rows, row i's word at position (i % 32) * 4 + i / 32.
         const uint32_t full_bar = leader_addr(&bars->full[0]);
         for (uint32_t iter = 0; ok; ++iter) {
-            const uint32_t num_sub = walker.next(iter * p.num_units + unit, tiles);
+            const uint32_t slot = slot_first + iter * slot_stride;
+            if (slot >= slot_end) break;
+            const uint32_t num_sub = walker.next(slot, tiles);
             if (num_sub == 0) break;
             for (uint32_t sub = 0; sub < num_sub && ok; ++sub, ++acc_iter) {
-                const uint32_t num_kb = max(1u, (tiles[sub].k_len + 127u) / 128u);
+                const uint32_t num_kb = max(1u, (tiles[sub].k_len + Cfg::BLOCK_K_ELEMS - 1) / Cfg::BLOCK_K_ELEMS);
                 for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
                     ok = wait_barrier(&bars->sf_full[stage], phase, abort_flag, peer_abort, p, kSiteTransposerSfFull,
                                       acc_iter, kb, stage);
@@ -793,11 +941,14 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                         reinterpret_cast<uint4*>(w)[lane] = make_uint4(v0, v1, v2, v3);
                     };
                     const bool new_r = (kb & sf_mask_r) == 0, new_c = (kb & sf_mask_c) == 0;
-                    if (new_r && !p.r_sf_pretransposed) transpose_128(sf_words_r + stage * 128);
+                    if (new_r && !p.r_sf_pretransposed) {
+#pragma unroll
+                        for (uint32_t i = 0; i < Cfg::SF_WORDS; ++i) transpose_128(sf_words_r + stage * (Cfg::SFR_STAGE / 4) + i * 128);
+                    }
                     if (new_c && !p.c_sf_pretransposed) {
 #pragma unroll
-                        for (uint32_t i = 0; i < Cfg::SFC_ROWS / 128; ++i)
-                            transpose_128(sf_words_c + stage * Cfg::SFC_ROWS + i * 128);
+                        for (uint32_t i = 0; i < Cfg::SF_WORDS * Cfg::SFC_ROWS / 128; ++i)
+                            transpose_128(sf_words_c + stage * (Cfg::SFC_STAGE / 4) + i * 128);
                     }
                     if ((new_r && !p.r_sf_pretransposed) || (new_c && !p.c_sf_pretransposed)) {
                         fence_proxy_async_smem();   // generic-proxy writes -> visible to tcgen05.cp
@@ -814,16 +965,18 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
         const uint32_t overlap_bar = leader_addr(&bars->overlap[0]);
         const uint32_t slab0 = smem_cd + q * Cfg::SLAB_BYTES;
         uint8_t* slab0_gen = smem_gen + (slab0 - smem_base);
-        uint32_t buf = 0, moe_buf = 0, moe_chunks = 0;
-        (void)buf, (void)moe_buf, (void)moe_chunks;
+        uint32_t buf = 0, moe_buf = 0, moe_chunks = 0, clamp_count = 0;
+        (void)buf, (void)moe_buf, (void)moe_chunks, (void)clamp_count;
         for (uint32_t iter = 0; ok; ++iter) {
-            const uint32_t num_sub = walker.next(iter * p.num_units + unit, tiles);
+            const uint32_t slot = slot_first + iter * slot_stride;
+            if (slot >= slot_end) break;
+            const uint32_t num_sub = walker.next(slot, tiles);
             if (num_sub == 0) break;
             for (uint32_t sub = 0; sub < num_sub && ok; ++sub, ++acc_iter) {
                 const TileCoord& tc = tiles[sub];
                 const uint32_t acc = acc_iter & 1;
                 const uint32_t acc_phase = (acc_iter >> 1) & 1;
-                if constexpr (Cfg::kEpi != 0) {
+                if constexpr (Cfg::kMoeEpi) {
                     // Per-token data of this tile, fetched while the UMMAs still run: route weights (kEpi 1) or
                     // destination addresses in the source ranks' combine planes (kEpi 2; 0 = row carries no token)
                     uint64_t* table = reinterpret_cast<uint64_t*>(smem_gen + (smem_cd - smem_base) + Cfg::MOE_TABLE_OFF) +
@@ -877,7 +1030,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                             if (i + 1 == num_chunks) mbar_arrive_cluster(tmem_empty_bar + acc * 8);
                         }
                     }
-                    if constexpr (Cfg::kEpi == 0) {
+                    if constexpr (!Cfg::kMoeEpi) {
                     // A K group without rows (K-grouped layouts allow them) contributes nothing: its single K block
                     // ran on whatever follows it in memory, so the accumulator is replaced by zeros
                     // (D = 0, or D unchanged when accumulating).
@@ -893,7 +1046,82 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                     if constexpr (!kSwap) {
                         // Row `lane` of the slab: 128 B, 16 B chunks XOR-swizzled by (row % 8)
                         uint4* row = reinterpret_cast<uint4*>(slab_gen + lane * 128);
-                        if constexpr (Cfg::kCdF32) {
+                        if constexpr (Cfg::kEpi == kEpiFp8Cast) {
+                            // E4M3 output with one UE8M0 scale per row and 32 columns: BF16 rounding first, so that the
+                            // bytes equal a BF16 D followed by the per-token cast (deep_gemm/utils/math.py:26-49)
+                            const bool counted = m0 + q * 32 + lane < p.m && n0 + ch * 64 < p.n;
+                            const float bound = p.cast.clamp_bound;
+                            uint4* row64 = reinterpret_cast<uint4*>(slab_gen + lane * 64);
+                            uint32_t sf_bytes = 0;
+#pragma unroll
+                            for (uint32_t g = 0; g < 2; ++g) {
+                                float x[32];
+                                float amax = 0.f;
+                                uint32_t over = 0;
+#pragma unroll
+                                for (uint32_t j = 0; j < 32; ++j) {
+                                    x[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[g * 32 + j])));
+                                    const float ax = fabsf(x[j]);
+                                    over += ax > bound ? 1u : 0u;
+                                    amax = fmaxf(amax, ax);
+                                }
+                                if (counted) clamp_count += over;
+                                amax = fminf(amax, bound);
+                                // power-of-two scale 2^e >= amax / 448, floor 2^-22 (as in moe_l1_chunk_impl)
+                                uint32_t e = (__float_as_uint(amax) + 0x1FFFFFu) >> 23;
+                                e = max(e, 113u) - 8u;
+                                const float inv = __uint_as_float((254u - e) << 23);
+                                sf_bytes |= e << (8 * g);
+#pragma unroll
+                                for (uint32_t c16 = 0; c16 < 2; ++c16) {
+                                    uint32_t w[4];
+#pragma unroll
+                                    for (uint32_t j = 0; j < 4; ++j) {
+                                        float f[4];
+#pragma unroll
+                                        for (uint32_t l = 0; l < 4; ++l)
+                                            f[l] = fminf(fmaxf(x[c16 * 16 + j * 4 + l], -bound), bound) * inv;
+                                        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f[0], f[1]), __NV_SATFINITE, __NV_E4M3);
+                                        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f[2], f[3]), __NV_SATFINITE, __NV_E4M3);
+                                        w[j] = lo | (hi << 16);
+                                    }
+                                    row64[g * 2 + c16] = make_uint4(w[0], w[1], w[2], w[3]);
+                                }
+                            }
+                            if (counted) {
+                                const uint32_t sf_idx = (tc.group * p.n + n0 + ch * 64) >> 5;   // even: two scales of one word
+                                uint8_t* dst = reinterpret_cast<uint8_t*>(p.cast.sfd + static_cast<uint64_t>(sf_idx >> 2) * p.cast.sfd_ld +
+                                                                          (m0 + q * 32 + lane)) + (sf_idx & 3u);
+                                *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(sf_bytes);
+                            }
+                        } else if constexpr (Cfg::kEpi == kEpiStochastic) {
+                            // BF16 with stochastic rounding: the 16 dropped bits of each FP32 value plus 16 random bits,
+                            // carried into the kept half.  The random bits come from a hash of the four FP32 bit patterns
+                            // of the value's column quartet (columns 4i .. 4i+3 of D) and the quartet's index, so the
+                            // result is a function of the FP32 result alone (epilogue/operators.cuh:53-114 and
+                            // tests/utils.py:53-79 of the reference state the hash)
+#pragma unroll
+                            for (uint32_t c16 = 0; c16 < 8; ++c16) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (uint32_t h4 = 0; h4 < 2; ++h4) {
+                                    const uint32_t* a = v + c16 * 8 + h4 * 4;
+                                    uint32_t h = a[0] * 0x5671d42bu + a[1] * 0x9995e499u + a[2] * 0xace1b8a5u + a[3] * 0xe153538du +
+                                                 ((n0 + ch * 64 + c16 * 8 + h4 * 4) >> 2);
+                                    h = (h ^ (h >> 23)) * 0x7feb352du;
+                                    h ^= h >> 16;
+                                    uint32_t h1 = h * 0x846ca68bu, h2 = h * 0xd35a2d97u;
+                                    h1 ^= h1 >> 11, h2 ^= h2 >> 11;
+                                    const uint32_t r0 = (a[0] >> 16) + (((a[0] & 0xffffu) + (h1 & 0xffffu)) >> 16);
+                                    const uint32_t r1 = (a[1] >> 16) + (((a[1] & 0xffffu) + (h1 >> 16)) >> 16);
+                                    const uint32_t r2 = (a[2] >> 16) + (((a[2] & 0xffffu) + (h2 & 0xffffu)) >> 16);
+                                    const uint32_t r3 = (a[3] >> 16) + (((a[3] & 0xffffu) + (h2 >> 16)) >> 16);
+                                    w[h4 * 2] = (r0 & 0xffffu) | (r1 << 16);
+                                    w[h4 * 2 + 1] = (r2 & 0xffffu) | (r3 << 16);
+                                }
+                                row[c16 ^ (lane & 7)] = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        } else if constexpr (Cfg::kCdF32) {
 #pragma unroll
                             for (uint32_t c16 = 0; c16 < 8; ++c16) {
                                 float4 f;
@@ -970,7 +1198,13 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                 }
             }
         }
-        if (Cfg::kEpi == 0 && lane == 0) tma_store_wait<0>();
+        if (!Cfg::kMoeEpi && lane == 0) tma_store_wait<0>();
+        if constexpr (Cfg::kEpi == kEpiFp8Cast) {
+            if (p.cast.clamped_count != nullptr) {      // one atomic per warp
+                const uint32_t total = __reduce_add_sync(0xffffffffu, clamp_count);
+                if (lane == 0 && total != 0) atomicAdd(p.cast.clamped_count, total);
+            }
+        }
     }
 
     // ---------------------------------------------------------------- tear-down

@@ -1,0 +1,26 @@
+// gemm_bs_kernel instantiations: kind::mxf8f6f4 (FP8 x FP8, FP8 x FP4) with the store / accumulate epilogue.
+#include "gemm_launch.cuh"
+
+namespace dg {
+
+int dispatch_gemm_plain(const GemmLaunch& l) {
+    // tokens on the UMMA M axis (dense, K-grouped, batched): BF16 and FP32 output
+    DG_GEMM_CASE(1, 128, false, false, 0, false)
+    DG_GEMM_CASE(1, 256, false, false, 0, false)
+    DG_GEMM_CASE(2, 128, false, false, 0, false)
+    DG_GEMM_CASE(2, 256, false, false, 0, false)
+    DG_GEMM_CASE(1, 128, false, true, 0, false)
+    DG_GEMM_CASE(1, 256, false, true, 0, false)
+    DG_GEMM_CASE(2, 128, false, true, 0, false)
+    DG_GEMM_CASE(2, 256, false, true, 0, false)
+    // weights on the UMMA M axis (M-grouped layouts)
+    DG_GEMM_CASE(1, 64, true, false, 0, false)
+    DG_GEMM_CASE(1, 128, true, false, 0, false)
+    DG_GEMM_CASE(2, 64, true, false, 0, false)
+    DG_GEMM_CASE(2, 128, true, false, 0, false)
+    DG_GEMM_CASE(2, 256, true, false, 0, false)
+    DG_GEMM_CASE(1, 256, true, false, 0, false)
+    return kLaunchNoKernel;
+}
+
+}  // namespace dg

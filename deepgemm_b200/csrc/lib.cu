@@ -13,7 +13,7 @@
 #include <cuda_bf16.h>
 
 #include "../../include/deepgemm_b200.h"
-#include "gemm_bs.cuh"
+#include "gemm_launch.cuh"
 #include "sf_pack.cuh"
 #include "mega_moe.cuh"
 #include "mega_moe_fused.cuh"
@@ -59,6 +59,8 @@ struct Knobs {
     int moe_fused = 1;     // Mega MoE: one persistent kernel (1) or the kernel-per-phase path (0)
     int pdl = 0;           // launch with programmatic stream serialisation
     int force_cta_group = 0, force_block_n = 0, force_swap = 0;   // dg_debug_set_tile_override
+    // masked layout: tile cost estimates in 1/256 of a group's first token block (dg_debug_set_masked_costs)
+    int masked_cost_first = 256, masked_cost_next_base = 100, masked_cost_next_per_256 = 60;
 } g_knobs;
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -106,6 +108,27 @@ int encode_tmap(CUtensorMap* tm, CUtensorMapDataType dtype, uint32_t rank, const
     return DG_OK;
 }
 
+// Launch of a kernel that takes one parameter struct, with programmatic stream serialisation when the knob is on
+template <class Params>
+cudaError_t launch_with_pdl(void (*kernel)(const Params), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            const Params& params) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    int pdl;
+    {
+        std::lock_guard<std::mutex> lk(g_knobs.mu);
+        pdl = g_knobs.pdl;
+    }
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr, cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, params);
+}
+
 int device_sm_count(int* out) {
     static int cached[64] = {0};
     int dev = 0;
@@ -127,83 +150,62 @@ struct TileChoice {
     bool swap;
 };
 
-template <class Cfg>
-int launch_gemm(dg::GemmParams& p, const dg_gemm_args& a, uint32_t num_units) {
-    // The attribute is per device; set it on every call (cheap) so that multi-device processes work.
-    const cudaError_t attr_err = cudaFuncSetAttribute(dg::gemm_bs_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                      static_cast<int>(Cfg::kSmemBytes));
-    if (attr_err != cudaSuccess)
-        return fail(DG_ERR_CUDA, "CUDA error: %s setting %u bytes of dynamic shared memory",
-                    cudaGetErrorString(attr_err), Cfg::kSmemBytes);
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(num_units * Cfg::kCtas, 1, 1);
-    cfg.blockDim = dim3(Cfg::kThreads, 1, 1);
-    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-    cfg.stream = static_cast<cudaStream_t>(a.stream);
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = Cfg::kCtas;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    DG_CUDA(cudaLaunchKernelEx(&cfg, dg::gemm_bs_kernel<Cfg>, p));
-    return DG_OK;
-}
-
 struct OperandPlan {
     CUtensorMap tm, tm_sf;
     dg::OperandParams params;
-    uint32_t rows_per_group, k_rows_per_group, sf_groups;
+    uint32_t sf_groups;
 };
 
 // Build the tensor maps and kernel parameters of one GEMM operand in the role of R (128 rows per
-// CTA) or C (`box_rows` rows per CTA).
+// CTA) or C (`box_rows` rows per CTA).  Data maps are 3-D: (K, row inside the group, group) for a K-major operand,
+// (row, K row, group) for an MN-major one; an operand without a group axis has a third extent of 1.
 int plan_operand(const dg_gemm_args& a, const dg_operand& op, bool is_a, uint32_t box_rows, uint32_t sf_box_rows,
-                 OperandPlan* out) {
+                 bool mxf4, OperandPlan* out) {
     const uint32_t mn = is_a ? a.m : a.n;
     const bool fp4 = op.dtype == DG_E2M1_PACKED;
     const bool k_grouped = a.gemm_type == DG_GEMM_K_GROUPED || a.gemm_type == DG_GEMM_K_GROUPED_PSUM;
-    const bool m_grouped = a.gemm_type == DG_GEMM_M_CONTIGUOUS || a.gemm_type == DG_GEMM_M_PSUM ||
-                           a.gemm_type == DG_GEMM_M_MASKED;
     // Which operands carry a group axis
     uint32_t groups = 1;
-    if (a.gemm_type == DG_GEMM_M_MASKED) groups = a.num_groups;
+    if (a.gemm_type == DG_GEMM_M_MASKED || a.gemm_type == DG_GEMM_BATCHED) groups = a.num_groups;
     if ((a.gemm_type == DG_GEMM_M_CONTIGUOUS || a.gemm_type == DG_GEMM_M_PSUM) && !is_a) groups = a.num_groups;
-    (void)m_grouped;
     dg::OperandParams& q = out->params;
     memset(&q, 0, sizeof(q));
     q.gran_k = op.gran_k;
     q.fmt = fp4 ? dg::kFmtE2M1 : dg::kFmtE4M3;
     q.mn_major = op.mn_major ? 1 : 0;
-    out->rows_per_group = out->k_rows_per_group = out->sf_groups = 0;
+    q.batched = groups > 1 ? 1 : 0;
+    out->sf_groups = 0;
     const char* name = is_a ? "a" : "b";
     int rc;
     if (!op.mn_major) {
-        // [groups * mn, k] with K contiguous
-        const uint64_t dims[2] = {static_cast<uint64_t>(a.k), static_cast<uint64_t>(mn) * groups};
-        const uint64_t strides[1] = {static_cast<uint64_t>(op.ld)};
-        const uint32_t box[2] = {128, box_rows};
-        rc = encode_tmap(&out->tm, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+        // K contiguous.  Packed E2M1 is seen as bytes under kind::mxf4 (two codes per byte in shared memory too) and as
+        // 4-bit elements that TMA spreads to one per byte otherwise (kind::mxf8f6f4 reads 8-bit containers).
+        const bool unpack = fp4 && !mxf4;
+        const uint64_t k_extent = mxf4 ? static_cast<uint64_t>(a.k) / 2 : static_cast<uint64_t>(a.k);
+        const uint64_t batch_stride = op.batch_stride > 0 ? static_cast<uint64_t>(op.batch_stride)
+                                                          : static_cast<uint64_t>(op.ld) * mn;
+        const uint64_t dims[3] = {k_extent, static_cast<uint64_t>(mn), groups};
+        const uint64_t strides[2] = {static_cast<uint64_t>(op.ld), batch_stride};
+        const uint32_t box[3] = {128, box_rows, 1};
+        rc = encode_tmap(&out->tm, unpack ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
                          op.data, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, name);
         if (rc != DG_OK) return rc;
         q.num_boxes = 1;
         q.box_bytes = box_rows * 128;
         q.box_mn = box_rows;
-        q.tx_bytes = box_rows * 128 / (fp4 ? 2 : 1);
+        q.tx_bytes = box_rows * 128 / (unpack ? 2 : 1);
         q.desc_lbo = 0, q.desc_sbo = 1024, q.desc_kstep = 32;
-        if (groups > 1) out->rows_per_group = mn;
     } else {
-        // [groups * k, mn] with MN contiguous (E4M3 only)
+        // MN contiguous (E4M3 only): rows of the map are K rows; K-grouped layouts stack all groups' K rows on that axis
         if (fp4) return fail(DG_ERR_INVALID, "Assertion failed: packed FP4 operands are K-major (%s)", name);
         if (box_rows % 128 != 0)
             return fail(DG_ERR_INVALID, "Assertion failed: MN-major %s needs a tile of whole 128-row atoms", name);
-        const uint64_t k_rows = k_grouped ? static_cast<uint64_t>(a.k) : static_cast<uint64_t>(a.k) * groups;
-        const uint64_t dims[2] = {static_cast<uint64_t>(mn), k_rows};
-        const uint64_t strides[1] = {static_cast<uint64_t>(op.ld)};
-        const uint32_t box[2] = {128, 128};
-        rc = encode_tmap(&out->tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, op.data, dims, strides, box,
+        const uint64_t batch_stride = op.batch_stride > 0 ? static_cast<uint64_t>(op.batch_stride)
+                                                          : static_cast<uint64_t>(op.ld) * a.k;
+        const uint64_t dims[3] = {static_cast<uint64_t>(mn), static_cast<uint64_t>(a.k), groups};
+        const uint64_t strides[2] = {static_cast<uint64_t>(op.ld), batch_stride};
+        const uint32_t box[3] = {128, 128, 1};
+        rc = encode_tmap(&out->tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, op.data, dims, strides, box,
                          CU_TENSOR_MAP_SWIZZLE_128B, name);
         if (rc != DG_OK) return rc;
         q.num_boxes = box_rows / 128;
@@ -211,20 +213,21 @@ int plan_operand(const dg_gemm_args& a, const dg_operand& op, bool is_a, uint32_
         q.box_mn = 128;
         q.tx_bytes = box_rows * 128;
         q.desc_lbo = 128 * 128, q.desc_sbo = 1024, q.desc_kstep = 32 * 128;
-        if (groups > 1) out->k_rows_per_group = a.k;
     }
     // Scale factors: int32 [groups * packed_k, mn] seen with MN innermost
     uint64_t packed_k;
     if (k_grouped) {
-        // Upper bound of the packed rows actually present: every group may round up once
-        packed_k = (static_cast<uint64_t>(a.k) / op.gran_k + 3 * static_cast<uint64_t>(a.num_groups)) / 4 + 1;
+        // the real row count where the caller knows it (TMA then zero-fills what lies beyond, e.g. the scale row of a
+        // trailing group without K rows); else an upper bound: every group may round up once
+        packed_k = op.sf_k_rows > 0 ? static_cast<uint64_t>(op.sf_k_rows)
+                                    : (static_cast<uint64_t>(a.k) / op.gran_k + 3 * static_cast<uint64_t>(a.num_groups)) / 4 + 1;
     } else {
         packed_k = (static_cast<uint64_t>(a.k) + op.gran_k * 4 - 1) / (op.gran_k * 4);
     }
     {
         const uint64_t dims[2] = {static_cast<uint64_t>(mn), packed_k * groups};
         const uint64_t strides[1] = {static_cast<uint64_t>(op.sf_ld) * 4};
-        const uint32_t box[2] = {sf_box_rows, 1};
+        const uint32_t box[2] = {sf_box_rows, mxf4 ? 2u : 1u};   // kind::mxf4: two scale words per row and stage
         rc = encode_tmap(&out->tm_sf, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, op.sf, dims, strides, box,
                          CU_TENSOR_MAP_SWIZZLE_NONE, is_a ? "sfa" : "sfb");
         if (rc != DG_OK) return rc;
@@ -254,6 +257,7 @@ int choose_tile(const dg_gemm_args& a, int num_sms, TileChoice* t) {
         c.swap = false;
         c.bn = a.n % 256 == 0 ? 256 : 128;
         c.ctas = (a.m % 256 == 0 && c.bn == 256 && num_sms % 2 == 0) ? 2 : 1;
+        if (!a.b.mn_major && c.bn == 256 && a.m > 128 && num_sms % 2 == 0) c.ctas = 2;   // K-major operands (FP4 x FP4)
     } else {
         c.swap = false;
         const bool mn_major_b = a.b.mn_major != 0;
@@ -306,6 +310,15 @@ int dg_get_num_sms(void) {
     int n = 0;
     if (device_sm_count(&n) != DG_OK) return -1;
     return n;
+}
+int dg_set_pdl(int32_t enable) {
+    std::lock_guard<std::mutex> lk(g_knobs.mu);
+    g_knobs.pdl = enable ? 1 : 0;
+    return DG_OK;
+}
+int dg_get_pdl(void) {
+    std::lock_guard<std::mutex> lk(g_knobs.mu);
+    return g_knobs.pdl;
 }
 int dg_set_tc_util(int32_t v) {
     DG_REQUIRE(v >= 0 && v <= 100, "tc_util");
@@ -362,6 +375,14 @@ int dg_debug_copy(void* dst, const void* src, int64_t bytes, void* stream) {
     return DG_OK;
 }
 
+int dg_debug_set_masked_costs(int32_t first, int32_t next_base, int32_t next_per_256_rows) {
+    DG_REQUIRE(first >= 0 && next_base >= 0 && next_per_256_rows >= 0 && first <= 65536 && next_base <= 65536 &&
+               next_per_256_rows <= 65536, "costs");
+    std::lock_guard<std::mutex> lk(g_knobs.mu);
+    g_knobs.masked_cost_first = first, g_knobs.masked_cost_next_base = next_base;
+    g_knobs.masked_cost_next_per_256 = next_per_256_rows;
+    return DG_OK;
+}
 int dg_set_wait_timeout_ms(int32_t ms) {
     DG_REQUIRE(ms > 0, "timeout");
     std::lock_guard<std::mutex> lk(g_knobs.mu);
@@ -402,8 +423,7 @@ int dg_sf_pack_ue8m0(const float* sf, int32_t* out, int32_t num_batches, int32_t
     p.psum_layout = psum_layout, p.num_psum_groups = num_psum_groups, p.psum_alignment = psum_alignment;
     DG_REQUIRE(num_batches <= 65535 && (p.packed_k + 31) / 32 <= 65535, "grid");
     dim3 grid((mn + 31) / 32, (p.packed_k + 31) / 32, num_batches);
-    dg::sf_pack_ue8m0_kernel<<<grid, dim3(32, 8, 1), 0, static_cast<cudaStream_t>(stream)>>>(p);
-    DG_CUDA(cudaGetLastError());
+    DG_CUDA(launch_with_pdl(dg::sf_pack_ue8m0_kernel, grid, dim3(32, 8, 1), 0, static_cast<cudaStream_t>(stream), p));
     return DG_OK;
 }
 
@@ -439,8 +459,8 @@ int dg_per_token_cast_to_fp8(const dg_cast_args* args) {
     }
     const uint32_t want = (p.rows + warps_per_cta - 1) / warps_per_cta;
     const uint32_t grid = want < static_cast<uint32_t>(num_sms) * 8u ? want : static_cast<uint32_t>(num_sms) * 8u;
-    dg::cast_bf16_to_fp8_ue8m0_kernel<<<grid, dg::kCastThreads, 0, static_cast<cudaStream_t>(a.stream)>>>(p);
-    DG_CUDA(cudaGetLastError());
+    DG_CUDA(launch_with_pdl(dg::cast_bf16_to_fp8_ue8m0_kernel, dim3(grid, 1, 1), dim3(dg::kCastThreads, 1, 1), 0,
+                            static_cast<cudaStream_t>(a.stream), p));
     return DG_OK;
 }
 
@@ -457,43 +477,64 @@ int dg_sf_pack_ue8m0_k_grouped(const float* sf, int32_t* out, const int32_t* gro
     p.sf_k_rows = sf_k_rows, p.packed_rows = packed_rows, p.gran_k = gran_k, p.k_alignment = k_alignment;
     p.use_psum = use_psum;
     dim3 grid((mn + 255) / 256, packed_rows, 1);
-    dg::sf_pack_ue8m0_k_grouped_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    DG_CUDA(cudaGetLastError());
+    DG_CUDA(launch_with_pdl(dg::sf_pack_ue8m0_k_grouped_kernel, grid, dim3(256, 1, 1), 0, static_cast<cudaStream_t>(stream), p));
     return DG_OK;
 }
 
-// Shared by dg_gemm_bs (epi == 0) and the two expert GEMMs of dg_mega_moe_forward (epi == 1, 2).
-static int run_gemm(const dg_gemm_args& a, int epi, const dg::MoeEpilogueParams* moe) {
-    DG_REQUIRE(a.gemm_type >= DG_GEMM_NORMAL && a.gemm_type <= DG_GEMM_K_GROUPED_PSUM, "gemm_type");
+// Shared by dg_gemm_bs and the two expert GEMMs of dg_mega_moe_forward (moe_epi == 1, 2).
+static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpilogueParams* moe) {
+    DG_REQUIRE(a.gemm_type >= DG_GEMM_NORMAL && a.gemm_type <= DG_GEMM_BATCHED, "gemm_type");
     DG_REQUIRE(a.m >= 0 && a.n >= 0 && a.k >= 0, "shape");
     if (a.m == 0 || a.n == 0) return DG_OK;
     DG_REQUIRE(a.k > 0, "k == 0 is handled by the caller");
-    DG_REQUIRE(a.a.data && a.b.data && a.a.sf && a.b.sf && (a.d || epi != 0), "null tensor");
+    DG_REQUIRE(a.a.data && a.b.data && a.a.sf && a.b.sf && (a.d || moe_epi != 0), "null tensor");
     DG_REQUIRE(a.a.dtype == DG_E4M3 || a.a.dtype == DG_E2M1_PACKED, "a dtype");
     DG_REQUIRE(a.b.dtype == DG_E4M3 || a.b.dtype == DG_E2M1_PACKED, "b dtype");
-    DG_REQUIRE(!(a.a.dtype == DG_E2M1_PACKED && a.b.dtype == DG_E2M1_PACKED),
-               "FP4 x FP4 (kind::mxf4) is not built yet");
-    DG_REQUIRE(a.d_dtype == DG_BF16 || a.d_dtype == DG_F32, "d dtype");
+    DG_REQUIRE(a.epilogue >= DG_EPILOGUE_STORE && a.epilogue <= DG_EPILOGUE_FP8_CAST, "epilogue");
+    const bool fp8_out = a.epilogue == DG_EPILOGUE_FP8_CAST;
+    DG_REQUIRE(fp8_out ? a.d_dtype == DG_E4M3 : (a.d_dtype == DG_BF16 || a.d_dtype == DG_F32), "d dtype");
     DG_REQUIRE(a.a.gran_k == 32 || a.a.gran_k == 128, "gran_k of a");
     DG_REQUIRE(a.b.gran_k == 32 || a.b.gran_k == 128, "gran_k of b");
+    // Both operands packed E2M1: the dedicated kind::mxf4 path (K-major, one scale per 32 elements)
+    const bool mxf4 = a.a.dtype == DG_E2M1_PACKED && a.b.dtype == DG_E2M1_PACKED;
+    if (mxf4) {
+        DG_REQUIRE(!a.a.mn_major && !a.b.mn_major, "major_a == cute::UMMA::Major::K and major_b == cute::UMMA::Major::K");
+        DG_REQUIRE(a.a.gran_k == 32 && a.b.gran_k == 32, "FP4 x FP4 takes 1 x 32 scales on both sides");
+        DG_REQUIRE(moe_epi == 0 && a.epilogue == DG_EPILOGUE_STORE, "FP4 x FP4 has the plain epilogue only");
+    }
     const bool grouped = a.gemm_type != DG_GEMM_NORMAL;
-    DG_REQUIRE(!grouped || (a.grouped_layout != nullptr && a.num_groups > 0), "grouped_layout");
+    const bool batched = a.gemm_type == DG_GEMM_BATCHED;
+    DG_REQUIRE(!grouped || a.num_groups > 0, "num_groups");
+    DG_REQUIRE(!grouped || batched || a.grouped_layout != nullptr, "grouped_layout");
     const bool k_grouped = a.gemm_type == DG_GEMM_K_GROUPED || a.gemm_type == DG_GEMM_K_GROUPED_PSUM;
-    const bool m_grouped = grouped && !k_grouped;
-    DG_REQUIRE(!k_grouped || (a.a.mn_major && a.b.mn_major && a.a.gran_k == a.b.gran_k), "k-grouped layout");
+    const bool m_grouped = grouped && !k_grouped && !batched;
+    // K-grouped: A^T B over MN-major E4M3 operands, or (FP4 x FP4) A B^T over K-major ones whose K axis holds the groups
+    DG_REQUIRE(!k_grouped || a.a.gran_k == a.b.gran_k, "k-grouped scale granularities match");
+    DG_REQUIRE(!k_grouped || mxf4 || (a.a.mn_major && a.b.mn_major), "k-grouped FP8 operands are MN-major");
     DG_REQUIRE(!m_grouped || !a.a.mn_major, "m-grouped A is K-major");
     DG_REQUIRE(!m_grouped || a.d_dtype == DG_BF16, "m-grouped D is BF16");
     DG_REQUIRE(a.a.dtype == DG_E4M3 || a.k % 128 == 0, "FP4 K is a multiple of 128");
     DG_REQUIRE(a.b.dtype == DG_E4M3 || a.k % 128 == 0, "FP4 K is a multiple of 128");
+    if (a.epilogue != DG_EPILOGUE_STORE) {
+        DG_REQUIRE(a.gemm_type == DG_GEMM_NORMAL || batched, "value epilogues belong to the dense and batched GEMMs");
+        DG_REQUIRE(!a.accumulate && a.alpha == 1.0f, "value epilogues write D directly");
+        DG_REQUIRE(a.epilogue != DG_EPILOGUE_STOCHASTIC_BF16 || a.d_dtype == DG_BF16, "stochastic rounding writes BF16");
+    }
+    if (fp8_out) {
+        DG_REQUIRE(a.sfd != nullptr && a.sfd_ld > 0, "sfd");
+        DG_REQUIRE(a.n % 128 == 0, "n % 128 == 0");
+        DG_REQUIRE(a.clamp_value >= 0.0f, "clamp_value > 0");
+    }
 
     int num_sms = dg_get_num_sms();
     DG_REQUIRE(num_sms > 0, "num_sms");
     TileChoice t;
     choose_tile(a, num_sms, &t);
-    if (epi != 0) {
+    if (moe_epi != 0) {
         std::lock_guard<std::mutex> lk(g_knobs.mu);
         t.swap = true, t.bn = g_knobs.force_block_n ? g_knobs.force_block_n : 256;
     }
+    if (a.epilogue != DG_EPILOGUE_STORE) t.swap = false;
     DG_REQUIRE(t.ctas == 1 || t.ctas == 2, "cta group");
     DG_REQUIRE(!(t.swap && a.d_dtype == DG_F32), "swapped tiles write BF16 only");
     DG_REQUIRE(!(t.swap && a.accumulate), "swapped tiles do not accumulate");
@@ -515,7 +556,7 @@ static int run_gemm(const dg_gemm_args& a, int epi, const dg::MoeEpilogueParams*
     if (a.gemm_type == DG_GEMM_M_PSUM) DG_REQUIRE(a.alignment > 0 && a.alignment % 32 == 0, "psum alignment");
     if (a.gemm_type == DG_GEMM_M_PSUM || a.gemm_type == DG_GEMM_M_MASKED)
         DG_REQUIRE(t.swap, "psum / masked layouts run with swapped operands");
-    if (k_grouped) DG_REQUIRE(a.alignment > 0 && a.alignment % 128 == 0, "k alignment");
+    if (k_grouped) DG_REQUIRE(a.alignment > 0 && a.alignment % (mxf4 ? 256 : 128) == 0, "k alignment");
 
     // Operand roles
     const dg_operand& op_r = t.swap ? a.b : a.a;
@@ -523,27 +564,26 @@ static int run_gemm(const dg_gemm_args& a, int epi, const dg::MoeEpilogueParams*
     const uint32_t c_rows_per_cta = t.bn / t.ctas;
     const uint32_t sfc_rows = (t.bn + 127) / 128 * 128;
     OperandPlan plan_r, plan_c;
-    int rc = plan_operand(a, op_r, /*is_a=*/!t.swap, 128, 128, &plan_r);
+    int rc = plan_operand(a, op_r, /*is_a=*/!t.swap, 128, 128, mxf4, &plan_r);
     if (rc != DG_OK) return rc;
-    rc = plan_operand(a, op_c, /*is_a=*/t.swap, c_rows_per_cta, sfc_rows, &plan_c);
+    rc = plan_operand(a, op_c, /*is_a=*/t.swap, c_rows_per_cta, sfc_rows, mxf4, &plan_c);
     if (rc != DG_OK) return rc;
 
-    dg::GemmParams p;
-    memset(&p, 0, sizeof(p));
+    dg::GemmLaunch launch;
+    memset(&launch, 0, sizeof(launch));
+    dg::GemmParams& p = launch.p;
     p.tm_r = plan_r.tm, p.tm_c = plan_c.tm, p.tm_sfr = plan_r.tm_sf, p.tm_sfc = plan_c.tm_sf;
-    if (t.swap && grouped && !op_c.mn_major && op_c.dtype == DG_E4M3 && c_rows_per_cta == 128) {
+    if (t.swap && grouped && !op_c.mn_major && (op_c.dtype == DG_E4M3 || mxf4) && c_rows_per_cta == 128) {
         // narrower views of the token operand for ragged tiles
         for (int i = 0; i < 2; ++i) {
             OperandPlan small;
-            rc = plan_operand(a, op_c, /*is_a=*/true, i == 0 ? 32 : 64, sfc_rows, &small);
+            rc = plan_operand(a, op_c, /*is_a=*/true, i == 0 ? 32 : 64, sfc_rows, mxf4, &small);
             if (rc != DG_OK) return rc;
             p.tm_c_small[i] = small.tm;
         }
         p.c_small = 1;
     }
     p.r = plan_r.params, p.c = plan_c.params;
-    p.rows_per_group_r = plan_r.rows_per_group, p.rows_per_group_c = plan_c.rows_per_group;
-    p.k_rows_per_group_r = plan_r.k_rows_per_group, p.k_rows_per_group_c = plan_c.k_rows_per_group;
     p.sf_groups_r = plan_r.sf_groups, p.sf_groups_c = plan_c.sf_groups;
     p.gemm_type = a.gemm_type;
     p.m = a.m, p.n = a.n, p.k = a.k;
@@ -554,83 +594,91 @@ static int run_gemm(const dg_gemm_args& a, int epi, const dg::MoeEpilogueParams*
     p.num_n_blocks = (a.n + unit_n - 1) / unit_n;
     p.alpha = a.alpha;
     p.accumulate = a.accumulate ? 1 : 0;
-    p.d_grouped = (a.gemm_type == DG_GEMM_M_MASKED || k_grouped) ? 1 : 0;
+    p.d_grouped = (a.gemm_type == DG_GEMM_M_MASKED || k_grouped || batched) ? 1 : 0;
     p.split_blocks = split_blocks;
     {
         std::lock_guard<std::mutex> lk(g_knobs.mu);
         p.timeout_ms = g_knobs.timeout_ms;
+        launch.pdl = g_knobs.pdl;
     }
     void* status_ptr = nullptr;
     DG_CUDA(cudaGetSymbolAddress(&status_ptr, g_status));
     p.status = static_cast<uint32_t*>(status_ptr);
     p.trace = g_trace;
 
-    if (epi != 0) {
+    if (moe_epi != 0) {
         p.moe = *moe;
         p.r_sf_pretransposed = 1;
         p.c_sf_pretransposed = 1;
     }
+    cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
+    if (fp8_out) {
+        p.cast.sfd = reinterpret_cast<uint32_t*>(a.sfd);
+        p.cast.sfd_ld = a.sfd_ld;
+        // the kernel compares BF16 values with the BF16-rounded bound (torch compares a BF16 tensor with a scalar so)
+        p.cast.clamp_bound = a.clamp_value > 0.0f ? __bfloat162float(__float2bfloat16_rn(a.clamp_value)) : INFINITY;
+        p.cast.clamped_count = a.clamp_value > 0.0f ? a.clamped_count : nullptr;
+        // the count replaces the word's previous contents: cleared in stream order before the launch
+        if (a.clamped_count != nullptr) DG_CUDA(cudaMemsetAsync(a.clamped_count, 0, sizeof(uint32_t), stream));
+    }
     // D: [groups, m, n] row-major
-    if (epi == 0) {
-        const uint32_t es = a.d_dtype == DG_F32 ? 4 : 2;
+    if (moe_epi == 0) {
+        const uint32_t es = a.d_dtype == DG_F32 ? 4 : (fp8_out ? 1 : 2);
         const uint64_t d_groups = p.d_grouped ? a.num_groups : 1;
+        const uint64_t d_batch = a.d_batch_stride > 0 ? static_cast<uint64_t>(a.d_batch_stride) : static_cast<uint64_t>(a.ldd) * a.m;
         const uint64_t dims[3] = {static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.m), d_groups};
-        const uint64_t strides[2] = {static_cast<uint64_t>(a.ldd), static_cast<uint64_t>(a.ldd) * a.m};
+        const uint64_t strides[2] = {static_cast<uint64_t>(a.ldd), d_batch};
         uint32_t box[3];
         CUtensorMapSwizzle sw;
         if (t.swap) {
             box[0] = 32, box[1] = 32, box[2] = 1, sw = CU_TENSOR_MAP_SWIZZLE_NONE;
+        } else if (fp8_out) {
+            box[0] = 64, box[1] = 32, box[2] = 1, sw = CU_TENSOR_MAP_SWIZZLE_NONE;
         } else {
             box[0] = 128 / es, box[1] = 32, box[2] = 1, sw = CU_TENSOR_MAP_SWIZZLE_128B;
         }
-        rc = encode_tmap(&p.tm_d, a.d_dtype == DG_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                         3, a.d, dims, strides, box, sw, "d");
+        const CUtensorMapDataType dt = a.d_dtype == DG_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                       : fp8_out            ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                                            : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        rc = encode_tmap(&p.tm_d, dt, 3, a.d, dims, strides, box, sw, "d");
         if (rc != DG_OK) return rc;
     }
 
     // Grid: persistent units, never more than there are tiles (when the host can know)
     uint32_t units = static_cast<uint32_t>(num_sms) / t.ctas;
     uint64_t tiles = static_cast<uint64_t>(p.num_m_blocks) * p.num_n_blocks;
-    if (k_grouped) tiles *= a.num_groups;
+    if (k_grouped || batched) tiles *= a.num_groups;
     if (a.gemm_type == DG_GEMM_M_MASKED) tiles *= a.num_groups;   // upper bound: m = max rows per group
     if (a.gemm_type != DG_GEMM_M_PSUM && tiles < units) units = static_cast<uint32_t>(tiles);
     DG_REQUIRE(units > 0, "empty grid");
     p.num_units = units;
     p.raster = choose_raster(p.num_m_blocks, unit_m, unit_n, units);
+    if (a.gemm_type == DG_GEMM_M_MASKED && a.num_groups <= static_cast<int>(dg::kMaxBalancedGroups) && a.m <= 65535) {
+        std::lock_guard<std::mutex> lk(g_knobs.mu);
+        if (g_knobs.masked_cost_first > 0) {
+            p.balance_masked = 1;
+            p.cost_first = g_knobs.masked_cost_first, p.cost_next_base = g_knobs.masked_cost_next_base;
+            p.cost_next_per_256_rows = g_knobs.masked_cost_next_per_256;
+            p.raster = p.num_m_blocks;   // a group's token blocks of one n block are consecutive slots
+        }
+    }
 
-#define DG_TRY_MOE(CT, BNV, EPI)                                                           \
-    if (epi == EPI && t.ctas == CT && t.bn == BNV)                                         \
-        return launch_gemm<dg::GemmConfig<CT, BNV, true, false, EPI>>(p, a, units);
-    DG_TRY_MOE(2, 256, 1)
-    DG_TRY_MOE(2, 128, 1)
-    DG_TRY_MOE(1, 256, 1)
-    DG_TRY_MOE(1, 128, 1)
-    DG_TRY_MOE(2, 256, 2)
-    DG_TRY_MOE(2, 128, 2)
-    DG_TRY_MOE(1, 256, 2)
-    DG_TRY_MOE(1, 128, 2)
-#undef DG_TRY_MOE
-    if (epi != 0) return fail(DG_ERR_INVALID, "no fused-epilogue kernel for cta_group %d, block_n %d", t.ctas, t.bn);
-#define DG_TRY(CT, BNV, SW, F32)                                                           \
-    if (t.ctas == CT && t.bn == BNV && t.swap == SW && (a.d_dtype == DG_F32) == F32)       \
-        return launch_gemm<dg::GemmConfig<CT, BNV, SW, F32>>(p, a, units);
-    DG_TRY(1, 128, false, false)
-    DG_TRY(1, 256, false, false)
-    DG_TRY(2, 128, false, false)
-    DG_TRY(2, 256, false, false)
-    DG_TRY(1, 128, false, true)
-    DG_TRY(1, 256, false, true)
-    DG_TRY(2, 128, false, true)
-    DG_TRY(2, 256, false, true)
-    DG_TRY(1, 64, true, false)
-    DG_TRY(1, 128, true, false)
-    DG_TRY(2, 64, true, false)
-    DG_TRY(2, 128, true, false)
-    DG_TRY(2, 256, true, false)
-    DG_TRY(1, 256, true, false)
-#undef DG_TRY
-    return fail(DG_ERR_INVALID, "no kernel built for cta_group %d, block_n %d, swap %d, f32 %d", t.ctas, t.bn,
-                static_cast<int>(t.swap), static_cast<int>(a.d_dtype == DG_F32));
+    launch.stream = stream, launch.units = units;
+    launch.ctas = t.ctas, launch.bn = t.bn, launch.swap = t.swap, launch.f32 = a.d_dtype == DG_F32;
+    launch.epi = moe_epi != 0 ? moe_epi : a.epilogue == DG_EPILOGUE_STOCHASTIC_BF16 ? dg::kEpiStochastic
+                 : fp8_out                                                          ? dg::kEpiFp8Cast
+                                                                                    : dg::kEpiStore;
+    launch.mxf4 = mxf4;
+    int lrc = mxf4 ? dg::dispatch_gemm_mxf4(launch)
+              : moe_epi != 0 ? dg::dispatch_gemm_moe(launch)
+              : launch.epi != dg::kEpiStore ? dg::dispatch_gemm_epi(launch)
+                                            : dg::dispatch_gemm_plain(launch);
+    if (lrc == dg::kLaunchNoKernel)
+        return fail(DG_ERR_INVALID, "no kernel built for cta_group %d, block_n %d, swap %d, f32 %d, epilogue %d, mxf4 %d",
+                    t.ctas, t.bn, static_cast<int>(t.swap), static_cast<int>(launch.f32), launch.epi, static_cast<int>(mxf4));
+    if (lrc != 0)
+        return fail(DG_ERR_CUDA, "CUDA error: %s launching the GEMM kernel", cudaGetErrorString(static_cast<cudaError_t>(lrc)));
+    return DG_OK;
 }
 
 
@@ -714,14 +762,14 @@ static int launch_moe_fused(const dg_moe_args& m, const dg::MoeArgs& a, int num_
     for (int i = 0; i < 2; ++i) {
         // weights are the UMMA row operand (128 rows per CTA), tokens the column operand (half of 256 per CTA)
         OperandPlan w, act;
-        int rc = plan_operand(g[i], g[i].b, /*is_a=*/false, 128, 128, &w);
+        int rc = plan_operand(g[i], g[i].b, /*is_a=*/false, 128, 128, false, &w);
         if (rc != DG_OK) return rc;
-        rc = plan_operand(g[i], g[i].a, /*is_a=*/true, 128, 256, &act);
+        rc = plan_operand(g[i], g[i].a, /*is_a=*/true, 128, 256, false, &act);
         if (rc != DG_OK) return rc;
         p.tm_w[i] = w.tm, p.tm_wsf[i] = w.tm_sf, p.tm_act[i] = act.tm, p.tm_actsf[i] = act.tm_sf;
         for (int j = 0; j < 2; ++j) {
             OperandPlan small;
-            rc = plan_operand(g[i], g[i].a, /*is_a=*/true, j == 0 ? 32 : 64, 256, &small);
+            rc = plan_operand(g[i], g[i].a, /*is_a=*/true, j == 0 ? 32 : 64, 256, false, &small);
             if (rc != DG_OK) return rc;
             p.tm_act_small[i][j] = small.tm;
         }

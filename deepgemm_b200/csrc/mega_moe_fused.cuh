@@ -363,9 +363,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             if (!ok) break;
             asm volatile("fence.proxy.async;" ::: "memory");   // the rows were written through the generic proxy
             const uint32_t k = tc.kind;
-            const uint32_t w_rows = k == 0 ? 2 * L.inter : L.hidden;          // weight rows per expert
             const uint32_t pk = (k == 0 ? L.hidden : L.inter) / 128;          // packed scale words per row
-            const uint32_t r_mn = tc.group * w_rows + tc.n_blk * 256 + cta_rank * 128;
+            const uint32_t r_mn = tc.n_blk * 256 + cta_rank * 128;   // row inside the expert; the expert is the map's third coordinate
             const uint32_t sfr_mn = tc.n_blk * 256 + cta_rank * 128, sfr_k = tc.group * pk;
             const uint32_t c_mn = tc.row0 + cta_rank * (tc.rows / 2);
             const uint32_t sfc_mn = tc.row0;
@@ -384,10 +383,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                         tma_load_2d<true>(smem_sfc + stage * Cfg::SFC_STAGE, &p.tm_actsf[k], full_bar, sfc_mn, kb);
                     } else if (w_role) {
                         mbar_arrive_expect_tx_cluster(full_bar, Cfg::R_STAGE / 2);   // FP4 weights count packed bytes
-                        tma_load_2d<true>(smem_r + stage * Cfg::R_STAGE, &p.tm_w[k], full_bar, kb * 128, r_mn);
+                        tma_load_3d<true>(smem_r + stage * Cfg::R_STAGE, &p.tm_w[k], full_bar, kb * 128, r_mn, tc.group);
                     } else {
                         mbar_arrive_expect_tx_cluster(full_bar, tx_bytes);
-                        tma_load_2d<true>(smem_c + stage * Cfg::C_STAGE, tm_act, full_bar, kb * 128, c_mn);
+                        tma_load_3d<true>(smem_c + stage * Cfg::C_STAGE, tm_act, full_bar, kb * 128, c_mn, 0);
                     }
                 }
                 __syncwarp();

@@ -37,6 +37,11 @@ DG_DEVICE bool elect_one() {
     return pred != 0;
 }
 
+// Programmatic dependent launch: wait until the kernels this launch depends on have completed and flushed (returns at
+// once when the launch carries no such dependency); let the next kernel in the stream start its prologue.
+DG_DEVICE void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+DG_DEVICE void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // --------------------------------------------------------------------------- cluster
 DG_DEVICE uint32_t cluster_ctarank() {
     uint32_t r;
@@ -240,6 +245,27 @@ DG_DEVICE void umma_mxf8f6f4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, 
             : "memory");
 }
 
+// The same with both operands packed E2M1 (two values per byte in shared memory), UMMA K = 64 and one UE8M0 scale
+// per 32 K elements: two scale bytes per row and instruction (scale_vec::2X), byte ids 0 or 2 of the TMEM word.
+template <int kCtas>
+DG_DEVICE void umma_mxf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem,
+                         uint32_t sfb_tmem, uint32_t accumulate) {
+    if constexpr (kCtas == 1)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+            : "memory");
+}
+
 // Arrive on mbarrier(s) once every tcgen05 op issued so far by this thread has completed.
 // kCtas == 2: the arrive is multicast to the same barrier offset in both CTAs of the pair.
 template <int kCtas>
@@ -310,6 +336,16 @@ __host__ __device__ inline uint32_t make_idesc_mxf8f6f4(uint32_t fmt_a, uint32_t
     d |= (fmt_b & 7) << 10;
     d |= (a_mn_major ? 1u : 0u) << 15;
     d |= (b_mn_major ? 1u : 0u) << 16;
+    d |= ((umma_n >> 3) & 0x3F) << 17;
+    d |= 1u << 23;
+    d |= ((umma_m >> 4) & 0x1F) << 24;
+    return d;
+}
+// kind::mxf4: the same fields; the only operand format is E2M1 (code 1), both operands K-major.
+__host__ __device__ inline uint32_t make_idesc_mxf4(uint32_t umma_m, uint32_t umma_n) {
+    uint32_t d = 0;
+    d |= 1u << 7;
+    d |= 1u << 10;
     d |= ((umma_n >> 3) & 0x3F) << 17;
     d |= 1u << 23;
     d |= ((umma_m >> 4) & 0x1F) << 24;

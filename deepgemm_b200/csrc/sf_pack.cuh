@@ -7,6 +7,8 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 
+#include "ptx.cuh"
+
 namespace dg {
 
 struct SfPackParams {
@@ -24,6 +26,8 @@ __device__ __forceinline__ uint32_t ue8m0_byte(float v) { return (__float_as_uin
 __global__ void __launch_bounds__(256) sf_pack_ue8m0_kernel(const SfPackParams p) {
     __shared__ uint32_t tile[32][33];
     __shared__ uint32_t row_valid[32];
+    grid_dependency_wait();      // the scales may come from the kernel before this one in the stream
+    grid_launch_dependents();    // the GEMM that follows may start its set-up; it waits for this kernel's end itself
     const int lane = threadIdx.x, wy = threadIdx.y;
     const int m0 = blockIdx.x * 32, kw0 = blockIdx.y * 32, b = blockIdx.z;
 
@@ -85,6 +89,8 @@ struct SfPackKGroupedParams {
 // One thread per output word (packed row, mn).  grid: (ceil(mn / 256), packed_rows); block: 256
 __global__ void __launch_bounds__(256) sf_pack_ue8m0_k_grouped_kernel(const SfPackKGroupedParams p) {
     __shared__ int s_src_row, s_rows_left;
+    grid_dependency_wait();
+    grid_launch_dependents();
     if (threadIdx.x == 0) {
         // Find the group owning packed row blockIdx.y
         int packed = 0, src = 0, prev_end = 0;

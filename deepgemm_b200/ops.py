@@ -33,6 +33,34 @@ class Alpha(_Epilogue):
         self.alpha = float(alpha)
 
 
+class FP8CastWithClamp(_Epilogue):
+    """D as E4M3 with one UE8M0 scale per row and 32 columns, packed four to an int32 in the MN-major TMA-aligned
+    layout (the layout accepted for SFA).  The accumulator is rounded to BF16 first, so the bytes equal a BF16 D
+    followed by per_token_cast_to_fp8(gran_k=32, use_packed_ue8m0=True).  `clamp_value` clamps the BF16 values before
+    scaling; `clamped_count` (a one-element CUDA uint32 tensor) receives how many exceeded it
+    (csrc/jit_kernels/impls/epilogue_class.hpp:69-118 of the reference)."""
+
+    def __init__(self, sfd: torch.Tensor, clamp_value: Optional[float] = None, clamped_count: Optional[torch.Tensor] = None):
+        _require(clamp_value is None or clamp_value > 0.0, "not clamp_value.has_value() or clamp_value.value() > 0.0f")
+        if clamped_count is not None:
+            _require(clamped_count.dtype == torch.uint32 and clamped_count.numel() == 1,
+                     "clamped_count->scalar_type() == torch::kUInt32 and clamped_count->numel() == 1")
+        self.sfd, self.clamp_value, self.clamped_count = sfd, clamp_value, clamped_count
+
+    def check(self, c, d):
+        _require(c is None and d.dtype == torch.float8_e4m3fn,
+                 "not c.has_value() and d.scalar_type() == torch::kFloat8_e4m3fn and \"FP8 quantization requires a direct E4M3 output\"")
+
+
+class BF16StochasticRounding(_Epilogue):
+    """BF16 D rounded stochastically; the random bits are a hash of the FP32 results themselves, so the output is a
+    function of the FP32-accumulated result (csrc/jit_kernels/impls/epilogue_class.hpp:120-136 of the reference)."""
+
+    def check(self, c, d):
+        _require(c is None and d.dtype == torch.bfloat16,
+                 "not c.has_value() and d.scalar_type() == torch::kBFloat16 and \"Stochastic rounding requires a direct BF16 output\"")
+
+
 def _major(t: torch.Tensor) -> int:
     """K-major if the last axis is contiguous, else MN-major (csrc/utils/layout.hpp:18-33)."""
     _require(t.dim() in (2, 3), "dim == 2 or dim == 3")
@@ -61,11 +89,13 @@ def _logical_mn_k(t: torch.Tensor, major: int) -> Tuple[int, int]:
     return mn, k
 
 
-def _operand(data: torch.Tensor, sf: torch.Tensor, major: int, gran_k: int) -> _lib.Operand:
+def _operand(data: torch.Tensor, sf: torch.Tensor, major: int, gran_k: int, batched: bool = False) -> _lib.Operand:
     op = _lib.Operand()
     op.data = data.data_ptr()
     op.sf = sf.data_ptr()
     op.ld = (data.stride(-2) if major == _K else data.stride(-1)) * data.element_size()
+    op.batch_stride = data.stride(0) * data.element_size() if batched else 0
+    op.sf_k_rows = getattr(sf, "k_rows", 0)
     op.sf_ld = sf.stride(-1)
     op.dtype = _lib.DG_E2M1_PACKED if data.dtype == PACKED_FP4 else _lib.DG_E4M3
     op.mn_major = int(major == _MN)
@@ -73,25 +103,43 @@ def _operand(data: torch.Tensor, sf: torch.Tensor, major: int, gran_k: int) -> _
     return op
 
 
-def _resolve_alpha(alpha: Optional[float], epilogue) -> float:
+def _resolve_alpha(alpha: Optional[float], epilogue, c=None, d=None, value_epilogues: bool = False) -> float:
+    """The epilogue class, `alpha` and (einsum only) the FP8 output pair are exclusive
+    (resolve_epilogue_class, csrc/jit_kernels/impls/epilogue_class.hpp:138-157 of the reference)."""
+    _require(not (epilogue is not None and alpha is not None),
+             "The epilogue class, `alpha` and the FP8 output pair are exclusive")
     if epilogue is None or isinstance(epilogue, Identity):
         return 1.0 if alpha is None else float(alpha)
     if isinstance(epilogue, Alpha):
-        _require(alpha is None, "alpha and an Alpha epilogue are exclusive")
         return epilogue.alpha
-    raise NotImplementedError(f"epilogue {type(epilogue).__name__} is not part of this build")
+    if value_epilogues and isinstance(epilogue, (BF16StochasticRounding, FP8CastWithClamp)):
+        epilogue.check(c, d)
+        return 1.0
+    raise RuntimeError(f"epilogue {type(epilogue).__name__} is not supported by this operator")
+
+
+_D_DTYPES = {torch.float32: _lib.DG_F32, torch.bfloat16: _lib.DG_BF16, torch.float8_e4m3fn: _lib.DG_E4M3}
 
 
 def _launch(gemm_type, m, n, k, a, sfa, major_a, gran_a, b, sfb, major_b, gran_b, d, *, num_groups=1, alignment=0,
-            accumulate=False, alpha=1.0, expected_m=0, grouped_layout=None) -> None:
+            accumulate=False, alpha=1.0, expected_m=0, grouped_layout=None, epilogue=None, batched=False) -> None:
     args = _lib.GemmArgs()
     args.gemm_type, args.m, args.n, args.k = gemm_type, m, n, k
     args.num_groups, args.alignment = num_groups, alignment
-    args.a = _operand(a, sfa, major_a, gran_a)
-    args.b = _operand(b, sfb, major_b, gran_b)
+    args.a = _operand(a, sfa, major_a, gran_a, batched)
+    args.b = _operand(b, sfb, major_b, gran_b, batched)
     args.d = d.data_ptr()
     args.ldd = d.stride(-2) * d.element_size()
-    args.d_dtype = _lib.DG_F32 if d.dtype == torch.float32 else _lib.DG_BF16
+    args.d_batch_stride = d.stride(0) * d.element_size() if batched else 0
+    args.d_dtype = _D_DTYPES[d.dtype]
+    args.epilogue = _lib.EPILOGUE_STORE
+    if isinstance(epilogue, BF16StochasticRounding):
+        args.epilogue = _lib.EPILOGUE_STOCHASTIC_BF16
+    elif isinstance(epilogue, FP8CastWithClamp):
+        args.epilogue = _lib.EPILOGUE_FP8_CAST
+        args.sfd, args.sfd_ld = epilogue.sfd.data_ptr(), epilogue.sfd.stride(-1)
+        args.clamp_value = float(epilogue.clamp_value or 0.0)
+        args.clamped_count = epilogue.clamped_count.data_ptr() if epilogue.clamped_count is not None else None
     args.accumulate = int(accumulate)
     args.alpha = alpha
     args.expected_m = int(expected_m or 0)
@@ -134,13 +182,13 @@ def fp8_fp4_gemm_nt(a, b, d, c=None, recipe=None, recipe_a=None, recipe_b=None, 
     _require(d.dim() == 2 and d.is_cuda, "t.dim() == N")
     _require(m == d.size(0) and n == d.size(1) and k == k_, "m == m_ and n == n_ and k == k_")
     _require(d.dtype in (torch.bfloat16, torch.float32), "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat")
-    scale = _resolve_alpha(alpha, epilogue)
+    scale = _resolve_alpha(alpha, epilogue, c, d, value_epilogues=True)
     if _early_return(m, n, k, d, c):
         return
     sfa, sfb, gran_a, gran_b = transform_sf_pair_into_required_layout(
         a_sf, b_sf, m, n, k, recipe, recipe_a, recipe_b, None, None, disable_ue8m0_cast)
     _launch(_lib.GEMM_NORMAL, m, n, k, a_data, sfa, major_a, gran_a, b_data, sfb, major_b, gran_b, d,
-            accumulate=c is not None, alpha=scale)
+            accumulate=c is not None, alpha=scale, epilogue=epilogue)
 
 
 def _t(pair):
@@ -299,11 +347,62 @@ def k_grouped_fp8_gemm_tn_contiguous(a, b, d, ks_cpu: Optional[Sequence[int]], g
             num_groups=g, alignment=k_alignment, accumulate=c is not None, grouped_layout=grouped_layout)
 
 
+def k_grouped_fp4_gemm_nt_contiguous(a, b, d, ks_cpu: Optional[Sequence[int]], grouped_layout, c=None,
+                                     recipe=(1, 1, 32), compiled_dims: str = "mn", use_psum_layout: bool = False,
+                                     epilogue=None) -> None:
+    """D[g] (+= C[g]) = A[:, k_g] @ B[:, k_g]^T over packed-FP4 operands a [m, sum_k / 2], b [n, sum_k / 2] (K-major,
+    the groups laid along K), scales [sum_k / 32, mn] FP32 or packed int32 [., mn]; runs on kind::mxf4
+    (csrc/apis/gemm.hpp:433-491).  The K alignment (get_mk_alignment_for_contiguous_layout) must be a multiple of 256;
+    padding codes must be zero."""
+    (a_data, a_sf), (b_data, b_sf) = a, b
+    _require(tuple(recipe) == (1, 1, 32), "recipe == std::make_tuple(1, 1, 32)")
+    _require(a_data.dtype == PACKED_FP4 and b_data.dtype == PACKED_FP4,
+             "a.first.scalar_type() == kPackedFP4 and b.first.scalar_type() == kPackedFP4")
+    _require(a_data.dim() == 2 and b_data.dim() == 2 and d.dim() == 3, "t.dim() == N")
+    major_a, major_b = _major(a_data), _major(b_data)
+    _require(major_a == _K and major_b == _K, "major_a == cute::UMMA::Major::K and major_b == cute::UMMA::Major::K")
+    k_alignment = get_mk_alignment_for_contiguous_layout()
+    _require(k_alignment % 256 == 0, "k_alignment % 256 == 0")
+    g, m, n = d.shape
+    m_, sum_k_ = _logical_mn_k(a_data, major_a)
+    n_, sum_k__ = _logical_mn_k(b_data, major_b)
+    _require(grouped_layout.is_contiguous() and grouped_layout.dtype == torch.int32 and grouped_layout.numel() == g,
+             "static_cast<int>(grouped_layout.numel()) == num_groups")
+    if ks_cpu is not None and len(ks_cpu) > 0:
+        _require(len(ks_cpu) == g, "ks_cpu.value().size() == num_groups")
+        for kk in ks_cpu:
+            _require(kk % k_alignment == 0, "k % k_alignment == 0")
+        total = sum(ks_cpu)
+    else:
+        _require(use_psum_layout, "use_psum_layout")
+        total = sum_k_
+    _require(m == m_ and n == n_ and total == sum_k_ and total == sum_k__, "m == m_ and n == n_ and sum_k == sum_k_ and sum_k == sum_k__")
+    _require(a_data.is_contiguous() and b_data.is_contiguous() and d.is_contiguous(), "is_contiguous()")
+    _require(c is None or c.is_contiguous(), "not c.has_value() or c.value().is_contiguous()")
+    _resolve_alpha(None, epilogue)
+    if _early_return(m, n, total, d, c):
+        return
+
+    def sf_of(sf):
+        if sf.dtype == torch.float32:
+            return get_k_grouped_mn_major_tma_aligned_packed_ue8m0_tensor(sf, grouped_layout, ks_cpu, 32, k_alignment,
+                                                                          use_psum_layout)
+        _require(sf.dtype == torch.int32 and sf.dim() == 2 and sf.stride(1) == 1 and sf.stride(0) % 4 == 0,
+                 "sf.stride(0) >= mn and sf.stride(1) == 1")
+        return sf
+
+    sfa, sfb = sf_of(a_sf), sf_of(b_sf)
+    _launch(_lib.GEMM_K_GROUPED_PSUM if use_psum_layout else _lib.GEMM_K_GROUPED, m, n, total,
+            a_data, _SfView(sfa), _K, 32, b_data, _SfView(sfb), _K, 32, d,
+            num_groups=g, alignment=k_alignment, accumulate=c is not None, grouped_layout=grouped_layout)
+
+
 class _SfView:
     """Adapter: a [packed_k, mn] scale tensor seen through the (.., mn, packed_k) stride convention."""
 
     def __init__(self, t: torch.Tensor):
         self._t = t
+        self.k_rows = t.size(0)      # the tensor map's real extent: reads past it are zero-filled, not made
 
     def data_ptr(self):
         return self._t.data_ptr()

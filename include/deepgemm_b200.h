@@ -32,9 +32,17 @@ enum dg_gemm_type {
     DG_GEMM_M_PSUM = 3,          /* grouped_layout: int32[G], cumulative un-aligned row ends */
     DG_GEMM_K_GROUPED = 4,       /* grouped_layout: int32[G], padded K per group */
     DG_GEMM_K_GROUPED_PSUM = 5,  /* grouped_layout: int32[G], cumulative un-aligned K ends */
+    DG_GEMM_BATCHED = 6,         /* num_groups independent problems of one shape; no layout tensor */
 };
 
-enum dg_dtype { DG_E4M3 = 0, DG_E2M1_PACKED = 1, DG_BF16 = 2, DG_F32 = 3 };
+/* What happens to the FP32 accumulator (deep_gemm/include/deep_gemm/epilogue/operators.cuh of the reference). */
+enum dg_epilogue {
+    DG_EPILOGUE_STORE = 0,            /* D = alpha * acc cast to d_dtype, or D += acc (Identity / ScaleByAlpha, :12-51) */
+    DG_EPILOGUE_STOCHASTIC_BF16 = 1,  /* BF16 D, stochastically rounded with bits hashed from the FP32 result (:53-114) */
+    DG_EPILOGUE_FP8_CAST = 2,         /* E4M3 D + per-row, per-32-column UE8M0 scales, optional clamp (:116-220) */
+};
+
+enum dg_dtype { DG_E4M3 = 0, DG_E2M1_PACKED = 1, DG_BF16 = 2, DG_F32 = 3 };   /* d_dtype: BF16, F32, or E4M3 (FP8_CAST) */
 
 /* One quantised operand: data plus packed UE8M0 scale factors.
  *   data : E4M3 bytes, or E2M1 codes two per byte (low nibble first).
@@ -53,6 +61,9 @@ typedef struct dg_operand {
     int32_t mn_major;   /* 0: K contiguous, 1: MN contiguous (E4M3 only) */
     int32_t gran_k;     /* K elements per scale: 32 or 128 */
     int32_t reserved;
+    int64_t batch_stride; /* bytes between the groups / batches of `data`; 0 = stacked without gaps
+                             (rows * ld for a K-major operand, k * ld for an MN-major one) */
+    int64_t sf_k_rows;    /* K-grouped GEMMs: rows (packed-K words) the sf tensor holds; 0 = not known */
 } dg_operand;
 
 /* Arguments of dg_gemm_bs.  Shapes are logical GEMM shapes: D[m, n] = A[m, k] * B[n, k]^T.
@@ -60,7 +71,11 @@ typedef struct dg_operand {
  *   M_CONTIGUOUS  : a [m,k] (m = all groups' rows), b [G,n,k], d [m,n]
  *   M_PSUM        : as M_CONTIGUOUS; group g owns rows [align(end[g-1], alignment), end[g])
  *   M_MASKED      : a [G,m,k], b [G,n,k], d [G,m,n] (m = max rows per group)
- *   K_GROUPED*    : a [sum_k, m], b [sum_k, n] (both MN-major), d [G,m,n], k = sum of padded K
+ *   K_GROUPED*    : a [sum_k, m], b [sum_k, n] (both MN-major), d [G,m,n], k = sum of padded K;
+ *                   FP4 x FP4: a [m, sum_k], b [n, sum_k] K-major with the groups along K
+ *   BATCHED       : a [G,m,k], b [G,n,k], d [G,m,n], every tensor with its own batch stride
+ * Both operands DG_E2M1_PACKED selects the FP4 x FP4 path (tcgen05 kind::mxf4, twice the FP8 rate): K-major
+ * operands, gran_k 32 on both sides, k % 128 == 0.
  */
 typedef struct dg_gemm_args {
     int32_t gemm_type;
@@ -76,12 +91,21 @@ typedef struct dg_gemm_args {
     int32_t expected_m;       /* heuristic hint for grouped layouts; 0 = none */
     const int32_t* grouped_layout;
     void* stream;             /* cudaStream_t */
+    int64_t d_batch_stride;   /* bytes between the groups / batches of d; 0 = m * ldd */
+    int32_t epilogue;         /* enum dg_epilogue; the value epilogues: NORMAL / BATCHED, alpha 1, no accumulate */
+    float clamp_value;        /* FP8_CAST: BF16 values are clamped to +-clamp_value before scaling; 0 = no clamp */
+    int32_t* sfd;             /* FP8_CAST: packed UE8M0 scales of d seen as [m, groups * n]: the scale of row r and
+                                 column group g = (batch * n + column) / 32 is byte g % 4 of word sfd[(g / 4) * sfd_ld + r] */
+    int64_t sfd_ld;
+    uint32_t* clamped_count;  /* FP8_CAST with a clamp, optional: receives the number of elements whose BF16 magnitude
+                                 exceeded clamp_value (overwritten, in stream order) */
 } dg_gemm_args;
 
-/* Block-scaled GEMM, all layouts.  Takes the role of sm100_fp8_fp4_gemm_1d1d and its grouped
+/* Block-scaled GEMM, all layouts.  Takes the role of sm100_fp8_fp4_gemm_1d1d and its grouped, batched and FP4 x FP4
  * variants (csrc/jit_kernels/impls/sm100_fp8_fp4_gemm_1d1d.hpp:101-561) as called from
- * fp8_fp4_gemm_nt, m_grouped_fp8_fp4_gemm_nt_contiguous, m_grouped_fp8_fp4_gemm_nt_masked and
- * k_grouped_fp8_gemm_tn_contiguous (csrc/apis/gemm.hpp:78-375). */
+ * fp8_fp4_gemm_nt, m_grouped_fp8_fp4_gemm_nt_contiguous, m_grouped_fp8_fp4_gemm_nt_masked,
+ * k_grouped_fp8_gemm_tn_contiguous, k_grouped_fp4_gemm_nt_contiguous (csrc/apis/gemm.hpp:78-491) and fp8_einsum
+ * (csrc/apis/einsum.hpp:182-304). */
 int dg_gemm_bs(const dg_gemm_args* args);
 
 /* FP32 power-of-two scales -> packed UE8M0, MN-major, 16-byte-aligned columns.
@@ -260,6 +284,8 @@ int dg_noalloc_scratch_bytes(void);
 /* Process-wide knobs (csrc/apis/config.hpp:8-48, csrc/apis/layout.hpp:138-146 of the reference). */
 int dg_set_num_sms(int32_t num_sms);
 int dg_get_num_sms(void);           /* device SM count unless overridden */
+int dg_set_pdl(int32_t enable);     /* launch the GEMM, scale-packing and cast kernels with programmatic dependent launch */
+int dg_get_pdl(void);
 int dg_set_tc_util(int32_t percent);
 int dg_get_tc_util(void);
 int dg_set_mk_alignment_for_contiguous_layout(int32_t alignment);
@@ -272,6 +298,11 @@ int dg_set_wait_timeout_ms(int32_t ms);  /* budget of every device-side wait; de
  * of this process use.  cta_group 1 / 2, block_n = UMMA N (32 .. 256), swap 1 = tokens on the UMMA M axis,
  * 2 = weights on the UMMA M axis; 0 in any field = choose automatically. */
 int dg_debug_set_tile_override(int32_t cta_group, int32_t block_n, int32_t swap);
+
+/* Tuning aid for the masked grouped GEMM's schedule: its tiles are cut into one run per CTA pair, balanced by estimated
+ * cost in 1/256 of the first token block of a (group, n block) - the one that streams the weights from HBM.  A later
+ * token block of `r` rows costs next_base + r * next_per_256_rows / 256.  first = 0 switches to a round-robin deal. */
+int dg_debug_set_masked_costs(int32_t first, int32_t next_base, int32_t next_per_256_rows);
 
 /* Measurement aid (no counterpart in the reference): copies `bytes` (a multiple of 16, both addresses 16-byte
  * aligned) with plain 16-byte loads and stores by all SMs, the way the Mega MoE forward pulls token rows.  Given a
