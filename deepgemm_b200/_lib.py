@@ -20,7 +20,7 @@ EXPORTS = (
     "dg_get_mk_alignment_for_contiguous_layout", "dg_get_theoretical_mk_alignment_for_contiguous_layout",
     "dg_set_wait_timeout_ms", "dg_check_status", "dg_last_error", "dg_version",
     "dg_mega_moe_buffer_layout", "dg_get_token_alignment_for_mega_moe", "dg_mega_moe_forward", "dg_set_mega_moe_fused", "dg_gemm_fp8_fp32sf_noalloc", "dg_noalloc_scratch_bytes",
-    "dg_per_token_cast_to_fp8", "dg_debug_set_tile_override", "dg_get_mega_moe_num_sms", "dg_debug_copy", "dg_set_pdl", "dg_get_pdl", "dg_debug_set_masked_costs",
+    "dg_per_token_cast_to_fp8", "dg_debug_set_tile_override", "dg_get_mega_moe_num_sms", "dg_debug_copy", "dg_set_pdl", "dg_get_pdl", "dg_debug_set_masked_costs", "dg_debug_set_weight_prefetch",
 )
 
 
@@ -38,18 +38,20 @@ class GemmArgs(C.Structure):
                 ("alpha", C.c_float), ("expected_m", C.c_int32),
                 ("grouped_layout", C.c_void_p), ("stream", C.c_void_p),
                 ("d_batch_stride", C.c_int64), ("epilogue", C.c_int32), ("clamp_value", C.c_float),
-                ("sfd", C.c_void_p), ("sfd_ld", C.c_int64), ("clamped_count", C.c_void_p)]
+                ("sfd", C.c_void_p), ("sfd_ld", C.c_int64), ("clamped_count", C.c_void_p),
+                ("skip_padding_rows", C.c_int32), ("reserved", C.c_int32)]
 
 
 class MoeConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("num_ranks", "num_experts", "num_max_tokens_per_rank", "num_topk", "hidden",
-                                          "intermediate_hidden", "num_ring_tokens", "reserved")]
+                                          "intermediate_hidden", "num_ring_tokens", "num_shared_experts")]
 
 
 class MoeLayout(C.Structure):
     _fields_ = [(n, C.c_int64) for n in ("num_bytes", "pool_rows", "off_x", "off_x_sf", "off_topk_idx",
                                           "off_topk_weights", "off_l1_acts", "off_l1_acts_sf", "off_l2_acts",
-                                          "off_l2_acts_sf", "off_token_src_metadata", "off_combine")]
+                                          "off_l2_acts_sf", "off_token_src_metadata", "off_combine",
+                                          "off_shared_l1_acts_sf", "off_shared_l2_acts", "off_shared_l2_acts_sf")]
 
 
 class MoeArgs(C.Structure):
@@ -59,7 +61,9 @@ class MoeArgs(C.Structure):
                 ("l1_sf_ld", C.c_int64), ("l2_sf_ld", C.c_int64), ("stats", C.c_void_p),
                 ("activation_clamp", C.c_float), ("fast_math", C.c_int32), ("stream", C.c_void_p),
                 ("activation", C.c_int32), ("situ_beta", C.c_float), ("situ_linear_beta", C.c_float),
-                ("post_down", C.c_int32)]
+                ("post_down", C.c_int32), ("weights_fp8", C.c_int32),
+                ("shared_l1_w", C.c_void_p), ("shared_l1_sf", C.c_void_p), ("shared_l2_w", C.c_void_p),
+                ("shared_l2_sf", C.c_void_p), ("shared_l1_sf_ld", C.c_int64), ("shared_l2_sf_ld", C.c_int64)]
 
 
 class GemmNoAllocArgs(C.Structure):
@@ -102,7 +106,7 @@ def lib() -> C.CDLL:
         l.dg_mega_moe_forward.argtypes = [C.POINTER(MoeArgs)]
         l.dg_gemm_fp8_fp32sf_noalloc.argtypes = [C.POINTER(GemmNoAllocArgs)]
         l.dg_per_token_cast_to_fp8.argtypes = [C.POINTER(CastArgs)]
-        for name in ("dg_set_num_sms", "dg_set_tc_util", "dg_set_pdl", "dg_set_mk_alignment_for_contiguous_layout",
+        for name in ("dg_set_num_sms", "dg_set_tc_util", "dg_set_pdl", "dg_debug_set_weight_prefetch", "dg_set_mk_alignment_for_contiguous_layout",
                      "dg_get_theoretical_mk_alignment_for_contiguous_layout", "dg_set_wait_timeout_ms",
                      "dg_set_mega_moe_fused"):
             getattr(l, name).argtypes = [C.c_int32]

@@ -122,6 +122,11 @@ __host__ __device__ inline uint32_t moe_sf_row(uint32_t row) {
 
 struct GemmParams {
     CUtensorMap tm_r, tm_c, tm_sfr, tm_sfc, tm_d;
+    CUtensorMap tm_d_half;   // swapped tiles: D seen through boxes of 16 token rows, for a tile's last 16 rows
+    // R seen as 8-byte elements through boxes of 128 rows x 2 KB: L2 prefetch of an operand that streams from HBM once
+    // (the weights of the masked layout).  prefetch_r = 0: not used
+    CUtensorMap tm_r_prefetch;
+    uint32_t prefetch_r;
     // Swapped tiles with few token rows: the same C operand seen through boxes of 32 and 64 rows per CTA, so a
     // ragged last tile of an expert does not fetch 128 rows per CTA and K block (c_small != 0 when encoded)
     CUtensorMap tm_c_small[2];
@@ -140,6 +145,10 @@ struct GemmParams {
     uint32_t accumulate;        // D += result (TMA reduce-add) instead of D = result
     uint32_t d_grouped;         // D has a group axis (masked / K-grouped): third store coordinate = group
     uint32_t split_blocks;      // contiguous layout: a schedule slot spans two alignment units (may straddle experts)
+    uint32_t skip_padding;      // psum layout: compute a group's valid rows only (rounded up to 16), not its aligned extent
+    // Dense layout, swapped tiles: the slots from tail_first on (the last, partly filled wave) are token tiles cut in
+    // tail_split parts of UNIT_M / tail_split rows, so that more units share the wave (0 / 1: no cut)
+    uint32_t tail_first, tail_split;
     uint32_t r_sf_pretransposed;  // R's scale words already sit in the 32x4 order tcgen05.cp reads (Mega MoE weights)
     uint32_t c_sf_pretransposed;  // same for C (Mega MoE activations: the pool is written in that order)
     MoeEpilogueParams moe;      // fused Mega MoE epilogues (GemmConfig::kEpi == 1, 2)
@@ -210,7 +219,7 @@ struct TileWalker {
             const uint32_t end = static_cast<uint32_t>(layout(group));
             row_start = (prev_end + p.alignment - 1) / p.alignment * p.alignment;
             const uint32_t end_aligned = (end + p.alignment - 1) / p.alignment * p.alignment;
-            group_rows = end > row_start ? end_aligned - row_start : 0;
+            group_rows = end > row_start ? (p.skip_padding ? end : end_aligned) - row_start : 0;
             prev_end = end;
         }
         group_m_blocks = (group_rows + bm - 1) / bm;
@@ -240,6 +249,15 @@ struct TileWalker {
             swizzle(t - g * per_group, p.num_m_blocks, num_n, m_blk, c.n_blk);
             c.row0 = m_blk * bm, c.group = g;
             if (swap) c.rows = min(bm, align16(p.m - c.row0));
+            return 1;
+        }
+        if (p.gemm_type == kGemmNormal && p.tail_split > 1 && t >= p.tail_first) {
+            const uint32_t sub = t - p.tail_first, idx = p.tail_first + sub / p.tail_split;
+            if (idx >= p.num_m_blocks * num_n) return 0;
+            swizzle(idx, p.num_m_blocks, num_n, m_blk, c.n_blk);
+            const uint32_t part_rows = bm / p.tail_split;
+            c.row0 = m_blk * bm + (sub % p.tail_split) * part_rows;   // m is a multiple of bm: every part is full
+            c.rows = part_rows;
             return 1;
         }
         if (p.gemm_type == kGemmNormal || p.gemm_type == kGemmMContiguous) {
@@ -793,6 +811,14 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                       }
                     } else if (r_role) {
                       if (elect_one()) {
+                        if (p.prefetch_r && (kb & 15u) == 0) {
+                            // 2 KB of K (16 K blocks) per row at a time, one chunk ahead of the tile loads; a tile's
+                            // first two chunks go out together
+                            const uint32_t kbyte = r_k + kb * 128;
+                            if (kb == 0) tma_prefetch_l2_3d(&p.tm_r_prefetch, static_cast<int32_t>(kbyte >> 3), static_cast<int32_t>(r_mn), r_batch);
+                            if (kb + 16 < num_kb)
+                                tma_prefetch_l2_3d(&p.tm_r_prefetch, static_cast<int32_t>((kbyte + 2048) >> 3), static_cast<int32_t>(r_mn), r_batch);
+                        }
                         // Operand tiles land on the leader's barrier (both CTAs of a pair feed one UMMA)
                         const uint32_t full_bar = full_bar0 + stage * 8;
                         mbar_arrive_expect_tx_cluster(full_bar, p.r.tx_bytes);
@@ -1164,8 +1190,11 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                             cm = static_cast<int32_t>(m0 + ch * 32);
                         }
                         const int32_t cg = p.d_grouped ? static_cast<int32_t>(tc.group) : 0;
-                        if (p.accumulate) tma_reduce_add_3d(&p.tm_d, slab, cn, cm, cg);
-                        else              tma_store_3d(&p.tm_d, slab, cn, cm, cg);
+                        // a swapped tile's rows are a multiple of 16: its last chunk may hold 16 token rows only, and
+                        // the rows after them belong to another tile
+                        const CUtensorMap* tm_out = (kSwap && tc.rows - ch * 32 == 16) ? &p.tm_d_half : &p.tm_d;
+                        if (p.accumulate) tma_reduce_add_3d(tm_out, slab, cn, cm, cg);
+                        else              tma_store_3d(tm_out, slab, cn, cm, cg);
                         tma_store_commit();
                     }
                     buf = buf + 1 == Cfg::kStoreBufs ? 0 : buf + 1;

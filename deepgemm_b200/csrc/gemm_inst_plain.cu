@@ -20,6 +20,9 @@ int dispatch_gemm_plain(const GemmLaunch& l) {
     DG_GEMM_CASE(2, 128, true, false, 0, false)
     DG_GEMM_CASE(2, 256, true, false, 0, false)
     DG_GEMM_CASE(1, 256, true, false, 0, false)
+    // 240-token tiles: two accumulator stages plus the scale columns fit the 512 columns of tensor memory without
+    // sharing any, so a tile's first UMMA need not wait for the tile before it to be drained
+    DG_GEMM_CASE(2, 240, true, false, 0, false)
     return kLaunchNoKernel;
 }
 

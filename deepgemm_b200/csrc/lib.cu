@@ -60,7 +60,10 @@ struct Knobs {
     int pdl = 0;           // launch with programmatic stream serialisation
     int force_cta_group = 0, force_block_n = 0, force_swap = 0;   // dg_debug_set_tile_override
     // masked layout: tile cost estimates in 1/256 of a group's first token block (dg_debug_set_masked_costs)
-    int masked_cost_first = 256, masked_cost_next_base = 100, masked_cost_next_per_256 = 60;
+    // 0 (default): round-robin deal.  Measured on config 3: cost-balanced runs were slower (183 vs 132 us): a unit's run
+    // stays inside one group, so the units read 16 groups' token blocks and weights at once instead of sharing one.
+    int masked_cost_first = 0, masked_cost_next_base = 80, masked_cost_next_per_256 = 30;
+    int prefetch_weights = 1;   // masked layout: L2 prefetch of the weight stream (dg_debug_set_weight_prefetch)
 } g_knobs;
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -264,6 +267,13 @@ int choose_tile(const dg_gemm_args& a, int num_sms, TileChoice* t) {
         c.ctas = (a.m > 128 && num_sms % 2 == 0) ? 2 : 1;
         c.bn = a.n >= 256 ? 256 : 128;
         if (c.ctas == 2 && c.bn == 128 && mn_major_b) c.ctas = 1;   // half tiles of an MN-major B need 128 rows
+        // Weights on the UMMA M axis for the plain BF16 case with K-major operands: measured 3-5 % faster at the dense
+        // configurations (4096 x 4096 x 7168: 82.9 vs 87.1 us; 8192 x 7168 x 2048: 82.9 vs 85.0 us), and the last wave's
+        // token tiles can then be cut to spread over more units.  FP4 x FP4 measured faster the other way round.
+        const bool both_fp4 = a.a.dtype == DG_E2M1_PACKED && a.b.dtype == DG_E2M1_PACKED;
+        if (a.gemm_type == DG_GEMM_NORMAL && a.d_dtype == DG_BF16 && !a.accumulate && a.epilogue == DG_EPILOGUE_STORE &&
+            !a.a.mn_major && !a.b.mn_major && a.n % 256 == 0 && a.m >= 256 && num_sms % 2 == 0 && !both_fp4)
+            c.swap = true, c.ctas = 2, c.bn = 256;
     }
     {
         std::lock_guard<std::mutex> lk(g_knobs.mu);
@@ -381,6 +391,11 @@ int dg_debug_set_masked_costs(int32_t first, int32_t next_base, int32_t next_per
     std::lock_guard<std::mutex> lk(g_knobs.mu);
     g_knobs.masked_cost_first = first, g_knobs.masked_cost_next_base = next_base;
     g_knobs.masked_cost_next_per_256 = next_per_256_rows;
+    return DG_OK;
+}
+int dg_debug_set_weight_prefetch(int32_t enable) {
+    std::lock_guard<std::mutex> lk(g_knobs.mu);
+    g_knobs.prefetch_weights = enable ? 1 : 0;
     return DG_OK;
 }
 int dg_set_wait_timeout_ms(int32_t ms) {
@@ -533,6 +548,7 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
     if (moe_epi != 0) {
         std::lock_guard<std::mutex> lk(g_knobs.mu);
         t.swap = true, t.bn = g_knobs.force_block_n ? g_knobs.force_block_n : 256;
+        if (!g_knobs.force_cta_group) t.ctas = (a.n % 256 == 0 && num_sms % 2 == 0) ? 2 : 1;   // a CTA pair splits the weight rows
     }
     if (a.epilogue != DG_EPILOGUE_STORE) t.swap = false;
     DG_REQUIRE(t.ctas == 1 || t.ctas == 2, "cta group");
@@ -573,7 +589,7 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
     memset(&launch, 0, sizeof(launch));
     dg::GemmParams& p = launch.p;
     p.tm_r = plan_r.tm, p.tm_c = plan_c.tm, p.tm_sfr = plan_r.tm_sf, p.tm_sfc = plan_c.tm_sf;
-    if (t.swap && grouped && !op_c.mn_major && (op_c.dtype == DG_E4M3 || mxf4) && c_rows_per_cta == 128) {
+    if (t.swap && !op_c.mn_major && (op_c.dtype == DG_E4M3 || mxf4) && c_rows_per_cta == 128) {
         // narrower views of the token operand for ragged tiles
         for (int i = 0; i < 2; ++i) {
             OperandPlan small;
@@ -582,6 +598,24 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
             p.tm_c_small[i] = small.tm;
         }
         p.c_small = 1;
+    }
+    {
+        // Masked layout: the weights stream from HBM once with little reuse; prefetch them into L2 in 2 KB runs per row
+        std::lock_guard<std::mutex> lk(g_knobs.mu);
+        const bool bytes_k_major = !op_r.mn_major && (op_r.dtype == DG_E4M3 || mxf4);
+        const int64_t k_bytes = mxf4 ? a.k / 2 : a.k;
+        if (g_knobs.prefetch_weights && a.gemm_type == DG_GEMM_M_MASKED && t.swap && bytes_k_major && k_bytes % 8 == 0) {
+            const uint64_t groups = a.num_groups;
+            const uint64_t dims[3] = {static_cast<uint64_t>(k_bytes / 8), static_cast<uint64_t>(a.n), groups};
+            const uint64_t batch_stride = op_r.batch_stride > 0 ? static_cast<uint64_t>(op_r.batch_stride)
+                                                                : static_cast<uint64_t>(op_r.ld) * a.n;
+            const uint64_t strides[2] = {static_cast<uint64_t>(op_r.ld), batch_stride};
+            const uint32_t box[3] = {256, 128, 1};
+            rc = encode_tmap(&p.tm_r_prefetch, CU_TENSOR_MAP_DATA_TYPE_INT64, 3, op_r.data, dims, strides, box,
+                             CU_TENSOR_MAP_SWIZZLE_NONE, "b (prefetch view)");
+            if (rc != DG_OK) return rc;
+            p.prefetch_r = 1;
+        }
     }
     p.r = plan_r.params, p.c = plan_c.params;
     p.sf_groups_r = plan_r.sf_groups, p.sf_groups_c = plan_c.sf_groups;
@@ -596,6 +630,7 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
     p.accumulate = a.accumulate ? 1 : 0;
     p.d_grouped = (a.gemm_type == DG_GEMM_M_MASKED || k_grouped || batched) ? 1 : 0;
     p.split_blocks = split_blocks;
+    p.skip_padding = a.skip_padding_rows ? 1 : 0;
     {
         std::lock_guard<std::mutex> lk(g_knobs.mu);
         p.timeout_ms = g_knobs.timeout_ms;
@@ -642,6 +677,11 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
                                                             : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
         rc = encode_tmap(&p.tm_d, dt, 3, a.d, dims, strides, box, sw, "d");
         if (rc != DG_OK) return rc;
+        if (t.swap) {
+            box[1] = 16;
+            rc = encode_tmap(&p.tm_d_half, dt, 3, a.d, dims, strides, box, sw, "d");
+            if (rc != DG_OK) return rc;
+        }
     }
 
     // Grid: persistent units, never more than there are tiles (when the host can know)
@@ -649,7 +689,20 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
     uint64_t tiles = static_cast<uint64_t>(p.num_m_blocks) * p.num_n_blocks;
     if (k_grouped || batched) tiles *= a.num_groups;
     if (a.gemm_type == DG_GEMM_M_MASKED) tiles *= a.num_groups;   // upper bound: m = max rows per group
-    if (a.gemm_type != DG_GEMM_M_PSUM && tiles < units) units = static_cast<uint32_t>(tiles);
+    uint64_t slots = tiles;
+    if (a.gemm_type == DG_GEMM_NORMAL && t.swap && moe_epi == 0 && a.m % static_cast<int>(unit_m) == 0 && unit_m == 256) {
+        // The last wave (or the only one): when fewer than half (a quarter) of the units would have a tile, its token
+        // tiles are cut in two (four) parts: a half tile costs more than half a tile, but the wave ends sooner.
+        const uint32_t tail = static_cast<uint32_t>(tiles % units);
+        if (tail != 0) {
+            const uint32_t split = tail * 4 <= units ? 4u : tail * 2 <= units ? 2u : 1u;
+            if (split > 1) {
+                p.tail_first = static_cast<uint32_t>(tiles) - tail, p.tail_split = split;
+                slots = tiles - tail + static_cast<uint64_t>(tail) * split;
+            }
+        }
+    }
+    if (a.gemm_type != DG_GEMM_M_PSUM && slots < units) units = static_cast<uint32_t>(slots);
     DG_REQUIRE(units > 0, "empty grid");
     p.num_units = units;
     p.raster = choose_raster(p.num_m_blocks, unit_m, unit_n, units);
@@ -695,6 +748,7 @@ static int check_moe_config(const dg_moe_config& c) {
     DG_REQUIRE(c.num_topk > 0 && c.num_topk <= c.num_experts, "num_topk");
     DG_REQUIRE(c.num_max_tokens_per_rank > 0, "num_max_tokens_per_rank");
     DG_REQUIRE(c.num_ring_tokens >= 0, "num_ring_tokens >= 0");
+    DG_REQUIRE(c.num_shared_experts >= 0 && c.num_shared_experts <= 64, "num_shared_experts >= 0");
     DG_REQUIRE(c.hidden > 0 && c.hidden % 128 == 0 && c.intermediate_hidden > 0 && c.intermediate_hidden % 128 == 0,
                "hidden % 128 == 0 and intermediate_hidden % 128 == 0");
     return DG_OK;
@@ -725,12 +779,14 @@ static void fill_moe_gemm_args(const dg_moe_args& m, const dg::MoeArgs& a, dg::M
     g.m = L.pool_rows, g.n = 2 * L.inter, g.k = L.hidden;
     g.a.data = mine + L.off_l1_acts, g.a.sf = reinterpret_cast<const int32_t*>(mine + L.off_l1_sf);
     g.a.ld = L.hidden, g.a.sf_ld = L.pool_rows, g.a.dtype = DG_E4M3, g.a.gran_k = 32;
-    g.b.data = m.l1_w, g.b.sf = m.l1_sf, g.b.ld = L.hidden / 2, g.b.sf_ld = m.l1_sf_ld, g.b.dtype = DG_E2M1_PACKED;
+    const int wdiv = m.weights_fp8 ? 1 : 2;   // weight bytes per row: K, or K / 2 for packed FP4
+    g.b.data = m.l1_w, g.b.sf = m.l1_sf, g.b.ld = L.hidden / wdiv, g.b.sf_ld = m.l1_sf_ld;
+    g.b.dtype = m.weights_fp8 ? DG_E4M3 : DG_E2M1_PACKED;
     g.b.gran_k = 32;
     *g1 = g;
     g.n = L.hidden, g.k = L.inter;
     g.a.data = mine + L.off_l2_acts, g.a.sf = reinterpret_cast<const int32_t*>(mine + L.off_l2_sf), g.a.ld = L.inter;
-    g.b.data = m.l2_w, g.b.sf = m.l2_sf, g.b.ld = L.inter / 2, g.b.sf_ld = m.l2_sf_ld;
+    g.b.data = m.l2_w, g.b.sf = m.l2_sf, g.b.ld = L.inter / wdiv, g.b.sf_ld = m.l2_sf_ld;
     *g2 = g;
 }
 
@@ -751,6 +807,46 @@ static int mega_moe_num_sms(int* out) {
     DG_REQUIRE(num_sms % 2 == 0, "num_sms % 2 == 0");
     *out = num_sms;
     return DG_OK;
+}
+
+// Shared experts: two dense GEMMs over this rank's own tokens with the fused epilogues of the routed path (gated
+// activation + requantisation without a route weight; BF16 rows written to plane `topk` of this rank's combine
+// buffer), enqueued ahead of the routed forward, whose reduction adds that plane first.
+static int run_shared_experts(const dg_moe_args& m, const dg::MoeArgs& a) {
+    const dg::MoeLayout& L = a.L;
+    DG_REQUIRE(m.shared_l1_w && m.shared_l1_sf && m.shared_l2_w && m.shared_l2_sf, "shared expert weights");
+    DG_REQUIRE(!m.post_down, "shared experts take route_weight_mode pre_down");
+    if (m.num_tokens == 0) return DG_OK;
+    cudaStream_t stream = static_cast<cudaStream_t>(m.stream);
+    uint8_t* mine = a.base[m.rank];
+    const uint32_t t_al = (L.t_max + 127) / 128 * 128, inter_s = L.shared * L.inter;
+    dg::moe_shared_meta_kernel<<<(t_al + 255) / 256, 256, 0, stream>>>(a);
+    DG_CUDA(cudaGetLastError());
+    dg::MoeEpilogueParams e;
+    dg_gemm_args unused1, unused2;
+    fill_moe_gemm_args(m, a, &e, &unused1, &unused2);
+    e.l2_acts = mine + L.off_shared_l2_acts, e.l2_sf = mine + L.off_shared_l2_sf;
+    e.pool_w = reinterpret_cast<const float*>(mine + L.off_topk_w);   // read into the per-tile table, never applied
+    e.pool_meta = reinterpret_cast<const int32_t*>(mine + L.off_shared_meta);
+    e.pool_rows = t_al, e.inter = inter_s;
+    dg_gemm_args g;
+    memset(&g, 0, sizeof(g));
+    g.gemm_type = DG_GEMM_NORMAL, g.num_groups = 1, g.stream = m.stream, g.alpha = 1.0f, g.d_dtype = DG_BF16;
+    g.m = m.num_tokens, g.n = 2 * static_cast<int32_t>(inter_s), g.k = L.hidden;
+    g.a.data = mine + L.off_x, g.a.sf = reinterpret_cast<const int32_t*>(mine + L.off_shared_sf);
+    g.a.ld = L.hidden, g.a.sf_ld = t_al, g.a.dtype = DG_E4M3, g.a.gran_k = 32;
+    g.b.data = m.shared_l1_w, g.b.sf = m.shared_l1_sf, g.b.ld = L.hidden, g.b.sf_ld = m.shared_l1_sf_ld;
+    g.b.dtype = DG_E4M3, g.b.gran_k = 32;
+    dg::MoeEpilogueParams e1 = e;
+    e1.post_down = 1;          // first GEMM: no route weight on the activation
+    int rc = run_gemm(g, 1, &e1);
+    if (rc != DG_OK) return rc;
+    g.n = L.hidden, g.k = static_cast<int32_t>(inter_s);
+    g.a.data = mine + L.off_shared_l2_acts, g.a.sf = reinterpret_cast<const int32_t*>(mine + L.off_shared_l2_sf), g.a.ld = inter_s;
+    g.b.data = m.shared_l2_w, g.b.sf = m.shared_l2_sf, g.b.ld = inter_s, g.b.sf_ld = m.shared_l2_sf_ld;
+    dg::MoeEpilogueParams e2 = e;
+    e2.post_down = 0;          // second GEMM: rows go to the combine plane as they are
+    return run_gemm(g, 2, &e2);
 }
 
 static int launch_moe_fused(const dg_moe_args& m, const dg::MoeArgs& a, int num_sms) {
@@ -775,6 +871,7 @@ static int launch_moe_fused(const dg_moe_args& m, const dg::MoeArgs& a, int num_
         }
     }
     p.y = static_cast<__nv_bfloat16*>(m.y), p.ldy = m.ldy;
+    p.w_fp8 = m.weights_fp8 ? 1u : 0u;
     p.num_ctas = static_cast<uint32_t>(num_sms) / 2 * 2;
     p.trace = g_trace;
     p.lag = 8;
@@ -811,13 +908,16 @@ int dg_mega_moe_buffer_layout(const dg_moe_config* cfg, dg_moe_layout* out) {
     if (rc != DG_OK) return rc;
     DG_REQUIRE(cfg->num_max_tokens_per_rank % dg_get_token_alignment_for_mega_moe() == 0, "token alignment");
     const dg::MoeLayout L = dg::make_moe_layout(cfg->num_ranks, cfg->num_experts, cfg->num_max_tokens_per_rank,
-                                                cfg->num_topk, cfg->hidden, cfg->intermediate_hidden, cfg->num_ring_tokens);
+                                                cfg->num_topk, cfg->hidden, cfg->intermediate_hidden, cfg->num_ring_tokens,
+                                                cfg->num_shared_experts);
     out->num_bytes = static_cast<int64_t>(L.total_bytes);
     out->pool_rows = static_cast<int64_t>(L.pool_rows);
     out->off_x = L.off_x, out->off_x_sf = L.off_x_sf, out->off_topk_idx = L.off_topk_idx;
     out->off_topk_weights = L.off_topk_w, out->off_l1_acts = L.off_l1_acts, out->off_l1_acts_sf = L.off_l1_sf;
     out->off_l2_acts = L.off_l2_acts, out->off_l2_acts_sf = L.off_l2_sf, out->off_token_src_metadata = L.off_pool_meta;
     out->off_combine = L.off_combine;
+    out->off_shared_l1_acts_sf = L.off_shared_sf, out->off_shared_l2_acts = L.off_shared_l2_acts;
+    out->off_shared_l2_acts_sf = L.off_shared_l2_sf;
     return DG_OK;
 }
 
@@ -832,7 +932,8 @@ int dg_mega_moe_forward(const dg_moe_args* args) {
     DG_REQUIRE(m.l1_w && m.l1_sf && m.l2_w && m.l2_sf, "null weights");
     DG_REQUIRE(m.activation >= DG_ACT_SWIGLU && m.activation <= DG_ACT_SITU, "activation");
     const dg::MoeLayout L = dg::make_moe_layout(m.cfg.num_ranks, m.cfg.num_experts, m.cfg.num_max_tokens_per_rank,
-                                                m.cfg.num_topk, m.cfg.hidden, m.cfg.intermediate_hidden, m.cfg.num_ring_tokens);
+                                                m.cfg.num_topk, m.cfg.hidden, m.cfg.intermediate_hidden, m.cfg.num_ring_tokens,
+                                                m.cfg.num_shared_experts);
     dg::MoeArgs a;
     memset(&a, 0, sizeof(a));
     a.L = L;
@@ -860,6 +961,10 @@ int dg_mega_moe_forward(const dg_moe_args* args) {
     }
     fused = fused && L.hidden % 256 == 0 && L.inter % 128 == 0 && L.experts_local * L.ranks <= dg::FusedCfg::kMaxSegments &&
             num_sms >= 2;
+    if (L.shared != 0) {
+        rc = run_shared_experts(m, a);
+        if (rc != DG_OK) return rc;
+    }
     if (fused) return launch_moe_fused(m, a, num_sms);
 
     // 1. count + index scatter, 2. count exchange + barrier + pool layout, 3. pull

@@ -38,13 +38,19 @@ constexpr uint32_t kMoeMaxExperts = kMoeCtrlBytes / 4 - MoeCtrl::kSendCount;
 // Byte offsets inside one rank's symmetric buffer (identical on every rank).
 struct MoeLayout {
     uint32_t ranks, experts, experts_local, t_max, topk, hidden, inter;
+    uint32_t shared;         // shared experts (0: none); they act as one expert of intermediate size shared * inter
+    uint32_t planes;         // combine planes: topk, plus one for the shared experts' result
     uint32_t pool_rows;      // capacity of the expert-sorted pool (multiple of 256)
     uint64_t off_ctrl;       // control block, always 0
     uint64_t off_recv_count; // u32 [ranks][experts_local]: rows each source rank sends to each local expert
     uint64_t off_src_idx;    // u32 [experts_local][ranks][t_max]: token * topk + slot, written by the source rank
     uint64_t off_x, off_x_sf, off_topk_idx, off_topk_w;   // inputs the caller fills
     uint64_t off_l1_acts, off_l1_sf, off_pool_w, off_pool_meta, off_l2_acts, off_l2_sf;
-    uint64_t off_combine;    // bf16 [topk][t_max][hidden]: written by the experts' ranks
+    uint64_t off_combine;    // bf16 [planes][t_max][hidden]: planes 0 .. topk-1 written by the experts' ranks, plane topk
+                             // by this rank's shared experts
+    // Shared experts (every token of this rank, no dispatch): x's scales once more, MN-major and in tcgen05.cp row
+    // order (filled by the caller like x_sf); the gated activation of all tokens; (rank, token, plane) per row
+    uint64_t off_shared_sf, off_shared_l2_acts, off_shared_l2_sf, off_shared_meta;
     uint64_t off_work;       // local scratch, see MoeWork
     uint64_t total_bytes;
 };
@@ -74,10 +80,10 @@ inline uint64_t moe_align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * 
 // pool_cap: rows the expert-sorted pool must hold; 0 = the worst case (every token of every rank picks this rank's
 // experts with all the slots it can).  A smaller pool makes a call whose rows do not fit fail with kStatusPoolOverflow.
 inline MoeLayout make_moe_layout(uint32_t ranks, uint32_t experts, uint32_t t_max, uint32_t topk, uint32_t hidden,
-                                 uint32_t inter, uint32_t pool_cap = 0) {
+                                 uint32_t inter, uint32_t pool_cap = 0, uint32_t shared = 0) {
     MoeLayout L{};
     L.ranks = ranks, L.experts = experts, L.experts_local = experts / ranks, L.t_max = t_max, L.topk = topk;
-    L.hidden = hidden, L.inter = inter;
+    L.hidden = hidden, L.inter = inter, L.shared = shared, L.planes = topk + (shared != 0 ? 1u : 0u);
     const uint64_t active_topk = topk < L.experts_local ? topk : L.experts_local;
     const uint64_t slack = static_cast<uint64_t>(L.experts_local) * kMoePoolAlign;   // every expert's rows start on a boundary
     uint64_t rows = static_cast<uint64_t>(t_max) * ranks * active_topk;
@@ -102,7 +108,14 @@ inline MoeLayout make_moe_layout(uint32_t ranks, uint32_t experts, uint32_t t_ma
     L.off_pool_meta = take(static_cast<uint64_t>(L.pool_rows) * 12);
     L.off_l2_acts = take(static_cast<uint64_t>(L.pool_rows) * inter);
     L.off_l2_sf = take(static_cast<uint64_t>(L.pool_rows) * (inter / 128) * 4);
-    L.off_combine = take(static_cast<uint64_t>(topk) * t_max * hidden * 2);
+    L.off_combine = take(static_cast<uint64_t>(L.planes) * t_max * hidden * 2);
+    if (shared != 0) {
+        const uint64_t t_al = moe_align_up(t_max, 128), inter_s = static_cast<uint64_t>(shared) * inter;
+        L.off_shared_sf = take(t_al * (hidden / 128) * 4);
+        L.off_shared_l2_acts = take(t_al * inter_s);
+        L.off_shared_l2_sf = take(t_al * (inter_s / 128) * 4);
+        L.off_shared_meta = take(t_al * 12);
+    }
     L.off_work = take(static_cast<uint64_t>(MoeFusedWork::words(L)) * 4);
     L.total_bytes = off;
     return L;
@@ -384,6 +397,16 @@ __global__ void __launch_bounds__(256) moe_pull_kernel(const MoeArgs a) {
     moe_pull_rows(a, s_prefix, blockIdx.x * 8 + threadIdx.x / 32, gridDim.x * 8, threadIdx.x & 31, nullptr);
 }
 
+// ---- shared experts: every row of the token buffer is its own pool row, bound for plane `topk` of this rank
+__global__ void __launch_bounds__(256) moe_shared_meta_kernel(const MoeArgs a) {
+    const uint32_t t = blockIdx.x * 256 + threadIdx.x;
+    const uint32_t t_al = (a.L.t_max + 127) / 128 * 128;
+    if (t >= t_al) return;
+    int32_t* meta = reinterpret_cast<int32_t*>(a.base[a.rank] + a.L.off_shared_meta) + t * 3;
+    meta[0] = t < a.num_tokens ? static_cast<int32_t>(a.rank) : -1;
+    meta[1] = static_cast<int32_t>(t), meta[2] = static_cast<int32_t>(a.L.topk);
+}
+
 // ---- cross-rank barrier on its own (after the experts' ranks have pushed their results).  One CTA.
 __global__ void __launch_bounds__(32) moe_barrier_kernel(const MoeArgs a) {
     const uint32_t* ctrl = reinterpret_cast<const uint32_t*>(a.base[a.rank]);
@@ -402,6 +425,17 @@ DG_DEVICE void moe_reduce_cols(const MoeArgs& a, __nv_bfloat16* y, int64_t ldy, 
     const int64_t delta = (static_cast<int64_t>(c2) - static_cast<int64_t>(c)) * 2;
     const uint64_t plane = static_cast<uint64_t>(L.t_max) * L.hidden * 2;
     float acc0[8] = {0, 0, 0, 0, 0, 0, 0, 0}, acc1[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (L.shared != 0) {   // the shared experts' row goes first, then the routed slots in slot order
+        const uint4 v0 = *reinterpret_cast<const uint4*>(col + L.topk * plane);
+        const uint4 v1 = kTwo ? *reinterpret_cast<const uint4*>(col + L.topk * plane + delta) : make_uint4(0, 0, 0, 0);
+        const __nv_bfloat162* b0 = reinterpret_cast<const __nv_bfloat162*>(&v0);
+        const __nv_bfloat162* b1 = reinterpret_cast<const __nv_bfloat162*>(&v1);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f0 = __bfloat1622float2(b0[i]), f1 = __bfloat1622float2(b1[i]);
+            acc0[2 * i] = f0.x, acc0[2 * i + 1] = f0.y, acc1[2 * i] = f1.x, acc1[2 * i + 1] = f1.y;
+        }
+    }
     for (uint32_t s0 = 0; s0 < L.topk; s0 += 8) {
         uint4 v0[8], v1[8];
         uint32_t mask = 0;

@@ -31,6 +31,7 @@ struct MoeFusedParams {
     uint32_t num_ctas;
     unsigned long long* trace;   // optional per-CTA time stamps (builds with DG_TRACE only)
     uint32_t lag;   // token tiles between a tile's first-GEMM slots and its second-GEMM slots in the schedule
+    uint32_t w_fp8; // expert weights are E4M3 bytes instead of packed E2M1 codes
 };
 
 struct FusedCfg {
@@ -45,8 +46,6 @@ struct FusedCfg {
     static constexpr uint32_t kSmemBytes = 1024 + kStages * STAGE_BYTES + CD_BYTES + 1024;
     static constexpr uint32_t kOverlap = 16, kAccStride = BN - kOverlap, kSfrCol = 2 * BN - kOverlap, kSfcCol = kSfrCol + 4;
     static constexpr uint32_t kTmemCols = 512;
-    // bytes one CTA's loads add to the stage barrier: FP4 weights count packed bytes
-    static constexpr uint32_t kTxBytes = R_STAGE / 2 + C_STAGE + SFR_STAGE + SFC_STAGE;
 };
 static_assert(FusedCfg::kStages >= 4 && FusedCfg::kStages <= 10, "stage count");
 
@@ -138,6 +137,7 @@ DG_DEVICE bool fused_grid_barrier(uint32_t* ctrl, uint32_t num_ctas, volatile ui
 constexpr uint32_t kReducePiece = DG_REDUCE_PIECE, kReduceStages = DG_REDUCE_STAGES, kReduceSlotBytes = kReducePiece * 2;
 static_assert(kReducePiece <= kFusedThreads * 8 && kReducePiece % 8 == 0, "one 8-column group per thread");
 static_assert(kReduceStages * 8 * kReduceSlotBytes <= FusedCfg::kStages * (FusedCfg::R_STAGE + FusedCfg::C_STAGE), "reduce stages");
+static_assert((kReduceStages - 1) * 9 * kReduceSlotBytes <= FusedCfg::kStages * (FusedCfg::R_STAGE + FusedCfg::C_STAGE), "reduce stages, nine rows");
 
 DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uint32_t smem_base,
                                  volatile uint32_t* abort_flag, const GemmParams& wp) {
@@ -148,6 +148,8 @@ DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uin
     __shared__ __align__(8) uint64_t s_full[kReduceStages];
     __shared__ uint32_t s_mask[kReduceStages];
     const MoeLayout& L = p.a.L;
+    // rows per item: the routed slots plus, with shared experts, their plane; nine rows leave room for three stages
+    const uint32_t np = L.planes, nst = np <= 8 ? kReduceStages : kReduceStages - 1;
     const uint32_t pieces = (L.hidden + kReducePiece - 1) / kReducePiece;
     const uint32_t num_items = my_tokens * pieces;
     const uint8_t* combine = p.a.base[p.a.rank] + L.off_combine;
@@ -166,6 +168,7 @@ DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uin
             const long long e = idx[u];
             if (e >= 0 && e < static_cast<long long>(L.experts)) mask |= 1u << u;
         }
+        if (L.shared != 0) mask |= 1u << L.topk;   // the shared experts' plane holds a row for every token
         return mask;
     };
     constexpr uint32_t kMaskCap = FusedCfg::CD_BYTES / 4;
@@ -175,8 +178,8 @@ DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uin
 
     // Lane 0 of warp u issues slot u's copy (eight issuing threads: one thread issuing all eight copies of an item
     // spends longer on that than the copies take); thread 0 also posts the expected byte count.
-    auto issue = [&](uint32_t it) {   // threads 0, 32, ..., 224
-        const uint32_t s = it % kReduceStages, i = it / pieces, u = threadIdx.x / 32;
+    auto issue = [&](uint32_t it) {   // threads 0, 32, ..., 32 * (np - 1)
+        const uint32_t s = it % nst, i = it / pieces, u = threadIdx.x / 32;
         const uint32_t t = first_token + i, c0 = (it % pieces) * kReducePiece;
         const uint32_t bytes = min(kReducePiece, L.hidden - c0) * 2;
         const uint32_t mask = i < kMaskCap ? s_token_mask[i] : token_mask(i);
@@ -186,24 +189,33 @@ DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uin
         }
         if (mask >> u & 1) {
             const uint8_t* src = combine + (static_cast<uint64_t>(t) * L.hidden + c0) * 2;
-            bulk_load(smem_base + (s * 8 + u) * kReduceSlotBytes, src + u * plane, bytes, smem_u32(&s_full[s]));
+            bulk_load(smem_base + (s * np + u) * kReduceSlotBytes, src + u * plane, bytes, smem_u32(&s_full[s]));
         }
     };
-    const bool issuer = threadIdx.x % 32 == 0 && threadIdx.x / 32 < 8;
+    const bool issuer = threadIdx.x % 32 == 0 && threadIdx.x / 32 < np;
 
     if (issuer)
-        for (uint32_t it = 0; it + 1 < kReduceStages && it < num_items; ++it) issue(it);
+        for (uint32_t it = 0; it + 1 < nst && it < num_items; ++it) issue(it);
     for (uint32_t it = 0; it < num_items; ++it) {
-        const uint32_t s = it % kReduceStages;
-        if (issuer && it + kReduceStages - 1 < num_items) issue(it + kReduceStages - 1);
-        const bool ok = wait_barrier(&s_full[s], (it / kReduceStages) & 1, abort_flag, 0, wp, 207, it, 0, s);
+        const uint32_t s = it % nst;
+        if (issuer && it + nst - 1 < num_items) issue(it + nst - 1);
+        const bool ok = wait_barrier(&s_full[s], (it / nst) & 1, abort_flag, 0, wp, 207, it, 0, s);
         if (ok) {
             const uint32_t t = first_token + it / pieces, c0 = (it % pieces) * kReducePiece;
             const uint32_t width = min(kReducePiece, L.hidden - c0), c = threadIdx.x * 8;
             if (c < width) {
-                const uint32_t mask = s_mask[s];
-                const uint8_t* src = smem_gen + s * 8 * kReduceSlotBytes + c * 2;
+                const uint32_t mask = s_mask[s] & ((1u << L.topk) - 1u);   // routed slots; the shared plane is added first
+                const uint8_t* src = smem_gen + s * np * kReduceSlotBytes + c * 2;
                 float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                if (L.shared != 0) {   // the shared experts' row first, then the routed slots in slot order
+                    const uint4 v = *reinterpret_cast<const uint4*>(src + L.topk * kReduceSlotBytes);
+                    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(b[i]);
+                        acc[2 * i] = f.x, acc[2 * i + 1] = f.y;
+                    }
+                }
 #pragma unroll
                 for (uint32_t u = 0; u < 8; ++u) {
                     if (mask >> u & 1) {
@@ -382,7 +394,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                         tma_load_2d<true>(smem_sfr + stage * Cfg::SFR_STAGE, &p.tm_wsf[k], full_bar, sfr_mn, sfr_k + kb);
                         tma_load_2d<true>(smem_sfc + stage * Cfg::SFC_STAGE, &p.tm_actsf[k], full_bar, sfc_mn, kb);
                     } else if (w_role) {
-                        mbar_arrive_expect_tx_cluster(full_bar, Cfg::R_STAGE / 2);   // FP4 weights count packed bytes
+                        mbar_arrive_expect_tx_cluster(full_bar, p.w_fp8 ? Cfg::R_STAGE : Cfg::R_STAGE / 2);   // FP4 weights count packed bytes
                         tma_load_3d<true>(smem_r + stage * Cfg::R_STAGE, &p.tm_w[k], full_bar, kb * 128, r_mn, tc.group);
                     } else {
                         mbar_arrive_expect_tx_cluster(full_bar, tx_bytes);
@@ -396,7 +408,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     } else if (warp == 1) {
         // ============================================================ UMMA issuer (leader CTA)
         if (is_leader) {
-            const uint32_t idesc_base = make_idesc_mxf8f6f4(kFmtE2M1, kFmtE4M3, false, false, 256, BN);
+            const uint32_t idesc_base = make_idesc_mxf8f6f4(p.w_fp8 ? kFmtE4M3 : kFmtE2M1, kFmtE4M3, false, false, 256, BN);
             const uint64_t sf_desc_hi = make_smem_desc(0, 0, 128, kSwizzleNone);
             const uint32_t op_hi = static_cast<uint32_t>(make_smem_desc(0, 0, 1024, kSwizzle128B) >> 32);
             const uint32_t r_lo0 = static_cast<uint32_t>(make_smem_desc(smem_r, 0, 1024, kSwizzle128B));

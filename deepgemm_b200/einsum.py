@@ -61,12 +61,9 @@ def fp8_bmm(a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor, sfb: torch.Tens
         _require(d.dtype in (torch.bfloat16, torch.float32), "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat")
     if batch == 0:
         return
-    if m == 0 or n == 0 or k == 0:
-        if sfd is not None:
-            sfd.zero_()
-        if _early_return(m, n, k, d, c):
-            return
-    if _early_return(m, n, k, d, c):
+    if (m == 0 or n == 0 or k == 0) and sfd is not None:
+        sfd.zero_()          # an empty problem zeroes the scales it would have produced
+    if _early_return(m, n, k, d, c, allow_fp8=sfd is not None):
         return
     ta, tb, gran_a, gran_b = transform_sf_pair_into_required_layout(sfa, sfb, m, n, k, recipe, None, None, batch, batch)
     alpha = epilogue.alpha if isinstance(epilogue, Alpha) else 1.0

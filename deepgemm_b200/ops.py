@@ -122,7 +122,8 @@ _D_DTYPES = {torch.float32: _lib.DG_F32, torch.bfloat16: _lib.DG_BF16, torch.flo
 
 
 def _launch(gemm_type, m, n, k, a, sfa, major_a, gran_a, b, sfb, major_b, gran_b, d, *, num_groups=1, alignment=0,
-            accumulate=False, alpha=1.0, expected_m=0, grouped_layout=None, epilogue=None, batched=False) -> None:
+            accumulate=False, alpha=1.0, expected_m=0, grouped_layout=None, epilogue=None, batched=False,
+            skip_padding_rows=False) -> None:
     args = _lib.GemmArgs()
     args.gemm_type, args.m, args.n, args.k = gemm_type, m, n, k
     args.num_groups, args.alignment = num_groups, alignment
@@ -132,6 +133,7 @@ def _launch(gemm_type, m, n, k, a, sfa, major_a, gran_a, b, sfb, major_b, gran_b
     args.ldd = d.stride(-2) * d.element_size()
     args.d_batch_stride = d.stride(0) * d.element_size() if batched else 0
     args.d_dtype = _D_DTYPES[d.dtype]
+    args.skip_padding_rows = int(skip_padding_rows)
     args.epilogue = _lib.EPILOGUE_STORE
     if isinstance(epilogue, BF16StochasticRounding):
         args.epilogue = _lib.EPILOGUE_STOCHASTIC_BF16
@@ -148,14 +150,15 @@ def _launch(gemm_type, m, n, k, a, sfa, major_a, gran_a, b, sfb, major_b, gran_b
     _lib.check(_lib.lib().dg_gemm_bs(args))
 
 
-def _early_return(m: int, n: int, k: int, d: torch.Tensor, c: Optional[torch.Tensor]) -> bool:
+def _early_return(m: int, n: int, k: int, d: torch.Tensor, c: Optional[torch.Tensor], allow_fp8: bool = False) -> bool:
     """Empty problems and the C != D copy (csrc/apis/gemm.hpp:17-53)."""
     if m == 0 or n == 0:
         return True
     same = c is not None and c.data_ptr() == d.data_ptr()
     if same:
         _require(c.shape == d.shape and c.stride() == d.stride(), "c->sizes() == d.sizes() and c->strides() == d.strides()")
-    _require(d.dtype in (torch.bfloat16, torch.float32), "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat")
+    _require(d.dtype in (torch.bfloat16, torch.float32) or (allow_fp8 and d.dtype == torch.float8_e4m3fn),
+             "d.scalar_type() == torch::kBFloat16 or d.scalar_type() == torch::kFloat")
     if c is not None:
         _check_cd(c)
         _require(d.dtype == c.dtype, "d.scalar_type() == c.value().scalar_type()")
@@ -254,7 +257,7 @@ def m_grouped_fp8_fp4_gemm_nt_contiguous(a, b, d, grouped_layout, recipe=None, r
     _launch(_lib.GEMM_M_PSUM if use_psum_layout else _lib.GEMM_M_CONTIGUOUS, m, n, k,
             a_data, sfa, major_a, gran_a, b_data, sfb, major_b, gran_b, d, num_groups=num_groups,
             alignment=get_mk_alignment_for_contiguous_layout(), expected_m=expected_m_for_psum_layout or 0,
-            grouped_layout=grouped_layout)
+            grouped_layout=grouped_layout, skip_padding_rows=use_psum_layout and not ensure_zero_padding)
 
 
 def m_grouped_fp8_fp4_gemm_nn_contiguous(a, b, d, grouped_layout, recipe=None, recipe_a=None, recipe_b=None,

@@ -99,6 +99,10 @@ typedef struct dg_gemm_args {
     int64_t sfd_ld;
     uint32_t* clamped_count;  /* FP8_CAST with a clamp, optional: receives the number of elements whose BF16 magnitude
                                  exceeded clamp_value (overwritten, in stream order) */
+    int32_t skip_padding_rows; /* M_PSUM: 0 = every group's whole aligned extent is computed, so zero padding rows of a
+                                  give zero rows of d; 1 = only the valid rows, rounded up to 16 (the reference's
+                                  ensure_zero_padding = false, deep_gemm/include/deep_gemm/scheduler/gemm.cuh:178-184) */
+    int32_t reserved;
 } dg_gemm_args;
 
 /* Block-scaled GEMM, all layouts.  Takes the role of sm100_fp8_fp4_gemm_1d1d and its grouped, batched and FP4 x FP4
@@ -145,19 +149,26 @@ typedef struct dg_moe_config {
      * min(num_topk, experts per rank); a smaller value saves memory, and a call that receives more rows than fit
      * is abandoned and reported by dg_check_status (code 3). */
     int32_t num_ring_tokens;
-    int32_t reserved;
+    /* Shared experts: applied to every token on the token's own rank, E4M3 weights [2 * S * I, H] and [H, S * I]
+     * (S = num_shared_experts; they act as one expert of intermediate size S * I), no route weight; their row enters
+     * the final sum first (csrc/apis/mega_moe.hpp:82-119,392-415 of the reference).  0 = none. */
+    int32_t num_shared_experts;
 } dg_moe_config;
 
 /* Byte offsets of the views inside one rank's buffer (shapes as in csrc/apis/mega_moe.hpp:137-226 of the
  * reference): x e4m3 [T, H]; x_sf int32 [T, H/128]; topk_idx int64 [T, K]; topk_weights f32 [T, K];
  * l1_acts e4m3 [P, H]; l1_acts_sf int32 [P, H/128] with strides (1, P); l2_acts e4m3 [P, I];
  * l2_acts_sf int32 [P, I/128] with strides (1, P); token_src_metadata int32 [P, 3];
- * combine bf16 [K, T, H].  P = pool_rows.  Inside every 128 pool rows the scale words of l1_acts_sf and
- * l2_acts_sf sit in the order tcgen05.cp consumes: row r of the block is stored at (r % 32) * 4 + r / 32. */
+ * combine bf16 [K (+ 1 with shared experts), T, H].  P = pool_rows.  Inside every 128 pool rows the scale words of
+ * l1_acts_sf and l2_acts_sf sit in the order tcgen05.cp consumes: row r of the block is stored at (r % 32) * 4 + r / 32.
+ * With shared experts (offsets 0 otherwise): shared_l1_acts_sf int32 [T', H/128] with strides (1, T'), T' = T rounded
+ * up to 128 - the scales of x once more, in that same row order, filled by the caller along with x_sf;
+ * shared_l2_acts e4m3 [T', S*I]; shared_l2_acts_sf int32 [T', S*I/128] with strides (1, T'). */
 typedef struct dg_moe_layout {
     int64_t num_bytes, pool_rows;
     int64_t off_x, off_x_sf, off_topk_idx, off_topk_weights;
     int64_t off_l1_acts, off_l1_acts_sf, off_l2_acts, off_l2_acts_sf, off_token_src_metadata, off_combine;
+    int64_t off_shared_l1_acts_sf, off_shared_l2_acts, off_shared_l2_acts_sf;
 } dg_moe_layout;
 
 /* Size and view offsets of the symmetric buffer.  Takes the role of get_symm_buffer_size_for_mega_moe_v3
@@ -204,6 +215,17 @@ typedef struct dg_moe_args {
      * is multiplied by its route weight and rounded to BF16 again where it is written to the combine plane
      * (impls/sm100_fp8_fp4_mega_moe.cuh:1538-1566 of the reference). */
     int32_t post_down;
+    /* 0: expert weights are MXFP4 (two E2M1 codes per byte, [E_local, 2I, H/2] and [E_local, H, I/2]);
+     * 1: E4M3 bytes ([E_local, 2I, H] and [E_local, H, I]), the reference's mma_type "fp8xfp8"
+     * (csrc/apis/mega_moe.hpp:374-377,473).  Scales are packed 1 x 32 UE8M0 in both cases. */
+    int32_t weights_fp8;
+    /* Shared experts' weights as produced by transform_weights_for_mega_moe (E4M3, gate / up rows interleaved, packed
+     * 1 x 32 scales in tcgen05.cp row order); all null when cfg.num_shared_experts == 0. */
+    const void* shared_l1_w;      /* e4m3 [2 * S * I, H] */
+    const int32_t* shared_l1_sf;
+    const void* shared_l2_w;      /* e4m3 [H, S * I] */
+    const int32_t* shared_l2_sf;
+    int64_t shared_l1_sf_ld, shared_l2_sf_ld;
 } dg_moe_args;
 
 /* y[t] = bf16( sum over slots of bf16( Q32( SwiGLU(bf16(x_t W13_e^T)) * w_{t,slot} ) W2_e^T ) ) with the tokens
@@ -303,6 +325,10 @@ int dg_debug_set_tile_override(int32_t cta_group, int32_t block_n, int32_t swap)
  * cost in 1/256 of the first token block of a (group, n block) - the one that streams the weights from HBM.  A later
  * token block of `r` rows costs next_base + r * next_per_256_rows / 256.  first = 0 switches to a round-robin deal. */
 int dg_debug_set_masked_costs(int32_t first, int32_t next_base, int32_t next_per_256_rows);
+
+/* Tuning aid: 1 (default) lets the masked grouped GEMM prefetch its weight stream into L2 in 2 KB runs per row ahead
+ * of the tile loads (the weights are read from HBM once; long runs make those reads page-friendly); 0 switches it off. */
+int dg_debug_set_weight_prefetch(int32_t enable);
 
 /* Measurement aid (no counterpart in the reference): copies `bytes` (a multiple of 16, both addresses 16-byte
  * aligned) with plain 16-byte loads and stores by all SMs, the way the Mega MoE forward pulls token rows.  Given a

@@ -292,6 +292,29 @@ def test_m_grouped_contiguous(use_psum, b_kind, tol, tile):
         assert np.array_equal(dn[~v], np.zeros_like(dn[~v]))     # zero input padding -> zero output padding
 
 
+@pytest.mark.parametrize("tile", [None, T(2, 128, 2)])
+def test_m_grouped_psum_without_zero_padding(tile):
+    """ensure_zero_padding=False (scheduler/gemm.cuh:178-184 of the reference): only a group's valid rows, rounded up
+    to 16, are computed (zero input rows give zero output rows there); rows of d beyond the 32-row store granule keep
+    what they held, the rows in between are unspecified."""
+    case = H.make_m_grouped_contiguous(5, 300, 512, 1024, use_psum=True, seed=22)
+    ga, gmb, gb = case["grans"]
+    d = torch.full((case["m"], 512), 7.0, dtype=torch.bfloat16, device="cuda")
+    with H.force_tile(**(tile or {})):
+        dg.m_grouped_fp8_fp4_gemm_nt_contiguous(case["a"], case["b"], d, case["layout"], recipe_a=(1, ga),
+                                                recipe_b=(gmb, gb), use_psum_layout=True, ensure_zero_padding=False,
+                                                expected_m_for_psum_layout=300)
+    ref, dn, v = H.ref_m_grouped(case), H.to_np(d), case["valid"]
+    assert H.calc_diff(dn[v], ref[v]) < FP8_TOL
+    start = 0
+    for am, al in zip(case["actual"], case["aligned"]):
+        computed = min(al, H.align_up(am, 16))
+        assert np.array_equal(dn[start + am:start + computed], np.zeros_like(dn[start + am:start + computed]))
+        untouched = min(al, H.align_up(am, 32))
+        assert (dn[start + untouched:start + al] == 7.0).all()
+        start += al
+
+
 def test_m_grouped_contiguous_nn_alias():
     case = H.make_m_grouped_contiguous(3, 200, 512, 1024, seed=4)
     ga, gmb, gb = case["grans"]

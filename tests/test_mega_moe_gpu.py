@@ -212,6 +212,101 @@ def _single_rank_case(hidden, inter, experts, topk, tokens, seed=100):
     return forward, ref
 
 
+@pytest.mark.parametrize("fused", [True, False])
+def test_mega_moe_fp8_weights(fused):
+    """Routed experts with E4M3 weights and 1 x 32 UE8M0 scales (the reference's mma_type "fp8xfp8",
+    csrc/apis/mega_moe.hpp:374-377): same forward, the weight operand read as bytes instead of packed nibbles."""
+    hidden, inter, experts, topk, tokens = 2048, 1024, 8, 4, 500
+    g = torch.Generator(device="cpu").manual_seed(99)
+    w1 = (torch.randn((experts, 2 * inter, hidden), generator=g) * (2 / hidden ** 0.5)).to(torch.bfloat16).cuda()
+    w2 = (torch.randn((experts, hidden, inter), generator=g) * (1 / inter ** 0.5)).to(torch.bfloat16).cuda()
+
+    def cast(w):
+        q, sf = zip(*[dg.utils.per_token_cast_to_fp8(w[e], use_ue8m0=True, gran_k=32) for e in range(w.size(0))])
+        q, sf = torch.stack(q), torch.stack(sf)
+        deq = np.stack([OQ.cast_back_from_fp8(H.to_np(q[e]), H.to_np(sf[e]), 32) for e in range(w.size(0))])
+        return q, sf, deq
+
+    (q1, sf1, deq1), (q2, sf2, deq2) = cast(w1), cast(w2)
+    l1 = (q1, dg.transform_sf_into_required_layout(sf1, 2 * inter, hidden, (1, 32), experts))
+    l2 = (q2, dg.transform_sf_into_required_layout(sf2, hidden, inter, (1, 32), experts))
+    l1, l2 = dg.transform_weights_for_mega_moe(l1, l2)
+    x_fp8, x_sf, idx, w, x_deq = make_inputs(tokens, hidden, experts, topk, 55, drop=6)
+    buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter, mma_type="fp8xfp8")
+    dg.mega.set_fused(fused)
+    try:
+        buf.x[:tokens].copy_(x_fp8), buf.x_sf[:tokens].copy_(x_sf)
+        buf.topk_idx[:tokens].copy_(idx), buf.topk_weights[:tokens].copy_(w)
+        y = torch.full((tokens, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+        dg.fp8_fp4_mega_moe(y, l1, l2, buf)
+        torch.cuda.synchronize()
+        dg.check_status()
+        ref = OM.mega_moe_reference(x_deq, idx.cpu().numpy(), w.cpu().numpy(), deq1, deq2)[0]
+        assert not np.isnan(H.to_np(y)).any()
+        assert H.calc_diff(H.to_np(y), ref) < MOE_TOL
+    finally:
+        dg.mega.set_fused(True)
+        buf.destroy()
+
+
+@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("num_shared,routed_fp8", [(1, False), (2, True)])
+def test_mega_moe_shared_experts(fused, num_shared, routed_fp8):
+    """Shared experts (csrc/apis/mega_moe.hpp:392-415 of the reference): E4M3 weights [2 S I, H] / [H, S I] applied to
+    every token on its own rank, no route weight, their BF16 row first in the final sum.  Against the oracle's statement
+    of the reference test's unfused baseline (tests/test_mega_moe.py:280-306); several calls with a changing token count."""
+    hidden, inter, experts, topk, tokens = 2048, 512, 8, 4, 300
+    g = torch.Generator(device="cpu").manual_seed(17)
+
+    def cast_fp8(w):
+        q, sf = dg.utils.per_token_cast_to_fp8(w.cuda(), use_ue8m0=True, gran_k=32)
+        return q, sf, OQ.cast_back_from_fp8(H.to_np(q), H.to_np(sf), 32)
+
+    i_s = inter * num_shared
+    sq1, ssf1, sdeq1 = cast_fp8((torch.randn((2 * i_s, hidden), generator=g) * (2 / hidden ** 0.5)).to(torch.bfloat16))
+    sq2, ssf2, sdeq2 = cast_fp8((torch.randn((hidden, i_s), generator=g) * (1 / i_s ** 0.5)).to(torch.bfloat16))
+    s1 = (sq1, dg.transform_sf_into_required_layout(ssf1, 2 * i_s, hidden, (1, 32)))
+    s2 = (sq2, dg.transform_sf_into_required_layout(ssf2, hidden, i_s, (1, 32)))
+    s1, s2 = dg.transform_weights_for_mega_moe(s1, s2)
+    if routed_fp8:
+        r1 = (torch.randn((experts, 2 * inter, hidden), generator=g) * (2 / hidden ** 0.5)).to(torch.bfloat16)
+        r2 = (torch.randn((experts, hidden, inter), generator=g) * (1 / inter ** 0.5)).to(torch.bfloat16)
+        c1, c2 = [cast_fp8(r1[e]) for e in range(experts)], [cast_fp8(r2[e]) for e in range(experts)]
+        q1, sf1, deq1 = (torch.stack([c[0] for c in c1]), torch.stack([c[1] for c in c1]), np.stack([c[2] for c in c1]))
+        q2, sf2, deq2 = (torch.stack([c[0] for c in c2]), torch.stack([c[1] for c in c2]), np.stack([c[2] for c in c2]))
+    else:
+        (q1, sf1, deq1), (q2, sf2, deq2) = make_weights(experts, hidden, inter)
+    l1 = (q1, dg.transform_sf_into_required_layout(sf1, 2 * inter, hidden, (1, 32), experts))
+    l2 = (q2, dg.transform_sf_into_required_layout(sf2, hidden, inter, (1, 32), experts))
+    l1, l2 = dg.transform_weights_for_mega_moe(l1, l2)
+    buf = dg.get_symm_buffer_for_mega_moe(None, experts, tokens, topk, hidden, inter, num_shared_experts=num_shared,
+                                          mma_type="fp8xfp8" if routed_fp8 else "fp8xfp4")
+    assert buf.combine.size(0) == topk + 1 and buf.shared_l2_acts.size(1) == i_s
+    dg.mega.set_fused(fused)
+    try:
+        for n_tok, seed in ((tokens, 1), (77, 2), (tokens, 3)):
+            x_fp8, x_sf, idx, w, x_deq = make_inputs(n_tok, hidden, experts, topk, seed, drop=5)
+            buf.x[:n_tok].copy_(x_fp8), buf.x_sf[:n_tok].copy_(x_sf)
+            buf.fill_shared_scales(n_tok)
+            buf.topk_idx[:n_tok].copy_(idx), buf.topk_weights[:n_tok].copy_(w)
+            y = torch.full((n_tok, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+            dg.fp8_fp4_mega_moe(y, l1, l2, buf, shared_l1_weights=s1, shared_l2_weights=s2)
+            torch.cuda.synchronize()
+            dg.check_status()
+            ref = OM.mega_moe_reference(x_deq, idx.cpu().numpy(), w.cpu().numpy(), deq1, deq2,
+                                        shared_l1_deq=sdeq1, shared_l2_deq=sdeq2)[0]
+            routed_only = OM.mega_moe_reference(x_deq, idx.cpu().numpy(), w.cpu().numpy(), deq1, deq2)[0]
+            got = H.to_np(y)
+            assert not np.isnan(got).any()
+            assert H.calc_diff(got, ref) < MOE_TOL, (n_tok, seed)
+            assert H.calc_diff(got, routed_only) > 50 * MOE_TOL      # the shared part is not small
+        with pytest.raises(RuntimeError, match="shared expert weights"):
+            dg.fp8_fp4_mega_moe(y, l1, l2, buf)
+    finally:
+        dg.mega.set_fused(True)
+        buf.destroy()
+
+
 def test_mega_moe_with_fewer_sms():
     """The persistent grid follows set_num_sms and DG_MEGA_MOE_SM_HEADROOM between calls on one buffer (its grid barrier
     does not remember earlier grids); a grouped GEMM runs under the same knob.  Results equal the full-grid ones bit

@@ -108,3 +108,6 @@ def test_reference_arm_under_torchrun_prints_one_line():
     rec = json.loads(lines[0])
     assert rec["impl"] == "reference" and rec["n_gpus"] == 2 and rec["value"] > 0
     assert rec["e2e"]["h2d_bytes_per_step"] == 0 and rec["cpu_baseline"]["kind"] == "port"
+    # torchrun gives its children OMP_NUM_THREADS=1; the arm must use all the host cores anyway
+    assert rec["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
+    assert rec["config"]["workload"].startswith("m_grouped_fp8_gemm_nt_contiguous") and rec["config"]["m"] == 67328
