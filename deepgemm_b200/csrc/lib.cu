@@ -1,5 +1,6 @@
 // Host side of libdeepgemm_b200.so: argument checks, tile selection, tensor-map encoding and
 // launches behind the C ABI declared in include/deepgemm_b200.h.
+#include <algorithm>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -63,7 +64,7 @@ struct Knobs {
     // 0 (default): round-robin deal.  Measured on config 3: cost-balanced runs were slower (183 vs 132 us): a unit's run
     // stays inside one group, so the units read 16 groups' token blocks and weights at once instead of sharing one.
     int masked_cost_first = 0, masked_cost_next_base = 80, masked_cost_next_per_256 = 30;
-    int prefetch_weights = 1;   // masked layout: L2 prefetch of the weight stream (dg_debug_set_weight_prefetch)
+    int prefetch_weights = 0;   // masked layout: L2 prefetch of the weight stream (dg_debug_set_weight_prefetch)
 } g_knobs;
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -600,7 +601,8 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
         p.c_small = 1;
     }
     {
-        // Masked layout: the weights stream from HBM once with little reuse; prefetch them into L2 in 2 KB runs per row
+        // Masked layout, on request: the weights stream from HBM once with little reuse; prefetch them into L2 in 2 KB runs
+        // per row (four boxes of 32 rows per 128-row tile)
         std::lock_guard<std::mutex> lk(g_knobs.mu);
         const bool bytes_k_major = !op_r.mn_major && (op_r.dtype == DG_E4M3 || mxf4);
         const int64_t k_bytes = mxf4 ? a.k / 2 : a.k;
@@ -610,7 +612,7 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
             const uint64_t batch_stride = op_r.batch_stride > 0 ? static_cast<uint64_t>(op_r.batch_stride)
                                                                 : static_cast<uint64_t>(op_r.ld) * a.n;
             const uint64_t strides[2] = {static_cast<uint64_t>(op_r.ld), batch_stride};
-            const uint32_t box[3] = {256, 128, 1};
+            const uint32_t box[3] = {static_cast<uint32_t>(std::min<uint64_t>(256, dims[0])), 32, 1};
             rc = encode_tmap(&p.tm_r_prefetch, CU_TENSOR_MAP_DATA_TYPE_INT64, 3, op_r.data, dims, strides, box,
                              CU_TENSOR_MAP_SWIZZLE_NONE, "b (prefetch view)");
             if (rc != DG_OK) return rc;
