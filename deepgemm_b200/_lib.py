@@ -51,7 +51,7 @@ class MoeLayout(C.Structure):
     _fields_ = [(n, C.c_int64) for n in ("num_bytes", "pool_rows", "off_x", "off_x_sf", "off_topk_idx",
                                           "off_topk_weights", "off_l1_acts", "off_l1_acts_sf", "off_l2_acts",
                                           "off_l2_acts_sf", "off_token_src_metadata", "off_combine",
-                                          "off_shared_l1_acts_sf", "off_shared_l2_acts", "off_shared_l2_acts_sf")]
+                                          "off_shared_l1_acts_sf", "off_shared_l2_acts", "off_shared_l2_acts_sf", "sf_rows")]
 
 
 class MoeArgs(C.Structure):

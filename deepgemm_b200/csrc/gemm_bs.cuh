@@ -105,6 +105,7 @@ struct MoeEpilogueParams {
     uint8_t* peer_base[16];    // every rank's buffer base
     uint64_t off_combine;
     uint32_t pool_rows, inter, hidden, t_max;
+    uint32_t sf_ld;            // row pitch of l2_sf
     float clamp;               // activation clamp; +inf = none
     uint32_t fast_math;
     uint32_t activation;       // 0 SwiGLU, 1 GeGLU (tanh form), 2 SiTU
@@ -521,7 +522,8 @@ DG_DEVICE float moe_gate(float g, float beta) {
 
 template <bool kFast, bool kClamp, int kAct>
 DG_DEVICE void moe_l1_chunk_impl(const MoeEpilogueParams& m, const uint8_t* stage, uint32_t pitch, const float* wtab,
-                                 uint32_t q, uint32_t lane, uint32_t ch, uint32_t chunk_rows, uint32_t m0, uint32_t n0) {
+                                 uint32_t q, uint32_t lane, uint32_t ch, uint32_t chunk_rows, uint32_t m0, uint32_t n0,
+                                 uint32_t sf_base) {
     // A warp takes 8 tokens; lane = (token, 32-output group g, half): 16 outputs per
     // thread = 32 interleaved rows laid out as 2 x [8 gate | 8 up] (the weights come
     // interleaved in blocks of 8 rows); the two halves of a group share their amax.
@@ -578,29 +580,33 @@ DG_DEVICE void moe_l1_chunk_impl(const MoeEpilogueParams& m, const uint8_t* stag
                                   half * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         const uint32_t kgroup = inter0 / 32;
         if (half == 0)
-            m.l2_sf[(static_cast<uint64_t>(kgroup / 4) * m.pool_rows + moe_sf_row(row)) * 4 + (kgroup & 3)] =
+            // scale rows in tcgen05.cp order relative to the tile: sf_base is the tile's first scale row
+            m.l2_sf[(static_cast<uint64_t>(kgroup / 4) * m.sf_ld + sf_base + moe_sf_row(ch * 32 + t)) * 4 + (kgroup & 3)] =
                 static_cast<uint8_t>(e);
     }
 }
 
 template <int kAct>
 DG_DEVICE void moe_l1_chunk_act(const MoeEpilogueParams& m, const uint8_t* stage, uint32_t pitch, const float* wtab,
-                                uint32_t q, uint32_t lane, uint32_t ch, uint32_t chunk_rows, uint32_t m0, uint32_t n0) {
+                                uint32_t q, uint32_t lane, uint32_t ch, uint32_t chunk_rows, uint32_t m0, uint32_t n0,
+                                uint32_t sf_base) {
     const bool clamp = m.clamp < 3.0e38f;   // +inf: no clamp
     if (m.fast_math) {
-        if (clamp) moe_l1_chunk_impl<true, true, kAct>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
-        else       moe_l1_chunk_impl<true, false, kAct>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
+        if (clamp) moe_l1_chunk_impl<true, true, kAct>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0, sf_base);
+        else       moe_l1_chunk_impl<true, false, kAct>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0, sf_base);
     } else {
-        if (clamp) moe_l1_chunk_impl<false, true, kAct>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
-        else       moe_l1_chunk_impl<false, false, kAct>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
+        if (clamp) moe_l1_chunk_impl<false, true, kAct>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0, sf_base);
+        else       moe_l1_chunk_impl<false, false, kAct>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0, sf_base);
     }
 }
 
+// sf_base: first scale row of the tile in l2_sf (the tile's first pool row where tiles start on 128-row boundaries)
 DG_DEVICE void moe_l1_chunk(const MoeEpilogueParams& m, const uint8_t* stage, uint32_t pitch, const float* wtab,
-                            uint32_t q, uint32_t lane, uint32_t ch, uint32_t chunk_rows, uint32_t m0, uint32_t n0) {
-    if (m.activation == 0)      moe_l1_chunk_act<0>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
-    else if (m.activation == 1) moe_l1_chunk_act<1>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
-    else                        moe_l1_chunk_act<2>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0);
+                            uint32_t q, uint32_t lane, uint32_t ch, uint32_t chunk_rows, uint32_t m0, uint32_t n0,
+                            uint32_t sf_base) {
+    if (m.activation == 0)      moe_l1_chunk_act<0>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0, sf_base);
+    else if (m.activation == 1) moe_l1_chunk_act<1>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0, sf_base);
+    else                        moe_l1_chunk_act<2>(m, stage, pitch, wtab, q, lane, ch, chunk_rows, m0, n0, sf_base);
 }
 
 // One 32-token chunk of the second expert GEMM's epilogue: 16 lanes move one token's 256 B segment of BF16
@@ -1223,7 +1229,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                                                                                   Cfg::MOE_TABLE_OFF) + acc * 256;
                         if constexpr (Cfg::kEpi == 1)
                             moe_l1_chunk(p.moe, stage_gen, Cfg::MOE_PITCH, reinterpret_cast<const float*>(table), q, lane, ch,
-                                         chunk_rows, m0, n0);
+                                         chunk_rows, m0, n0, /*sf_base=*/m0);   // tiles start on 128-row boundaries here
                         else
                             moe_l2_chunk(stage_gen, Cfg::MOE_PITCH, table, q * 32 + lane, ch, chunk_rows, n0,
                                          p.moe.post_down ? p.moe.pool_w + m0 : nullptr);

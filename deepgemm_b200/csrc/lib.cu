@@ -767,7 +767,7 @@ static void fill_moe_gemm_args(const dg_moe_args& m, const dg::MoeArgs& a, dg::M
     e->pool_w = reinterpret_cast<const float*>(mine + L.off_pool_w);
     e->pool_meta = reinterpret_cast<const int32_t*>(mine + L.off_pool_meta);
     for (uint32_t r = 0; r < L.ranks; ++r) e->peer_base[r] = a.base[r];
-    e->off_combine = L.off_combine, e->pool_rows = L.pool_rows, e->inter = L.inter, e->hidden = L.hidden, e->t_max = L.t_max;
+    e->off_combine = L.off_combine, e->pool_rows = L.pool_rows, e->sf_ld = L.pool_rows, e->inter = L.inter, e->hidden = L.hidden, e->t_max = L.t_max;
     e->clamp = m.activation_clamp, e->fast_math = m.fast_math ? 1 : 0;
     e->activation = static_cast<uint32_t>(m.activation);
     e->post_down = m.post_down ? 1u : 0u;
@@ -830,7 +830,7 @@ static int run_shared_experts(const dg_moe_args& m, const dg::MoeArgs& a) {
     e.l2_acts = mine + L.off_shared_l2_acts, e.l2_sf = mine + L.off_shared_l2_sf;
     e.pool_w = reinterpret_cast<const float*>(mine + L.off_topk_w);   // read into the per-tile table, never applied
     e.pool_meta = reinterpret_cast<const int32_t*>(mine + L.off_shared_meta);
-    e.pool_rows = t_al, e.inter = inter_s;
+    e.pool_rows = t_al, e.sf_ld = t_al, e.inter = inter_s;
     dg_gemm_args g;
     memset(&g, 0, sizeof(g));
     g.gemm_type = DG_GEMM_NORMAL, g.num_groups = 1, g.stream = m.stream, g.alpha = 1.0f, g.d_dtype = DG_BF16;
@@ -857,14 +857,21 @@ static int launch_moe_fused(const dg_moe_args& m, const dg::MoeArgs& a, int num_
     p.a = a;
     dg_gemm_args g[2];
     fill_moe_gemm_args(m, a, &p.e, &g[0], &g[1]);
+    p.e.sf_ld = a.L.sf_rows;
     for (int i = 0; i < 2; ++i) {
-        // weights are the UMMA row operand (128 rows per CTA), tokens the column operand (half of 256 per CTA)
+        // weights are the UMMA row operand (128 rows per CTA), tokens the column operand (half a token tile per CTA)
         OperandPlan w, act;
         int rc = plan_operand(g[i], g[i].b, /*is_a=*/false, 128, 128, false, &w);
         if (rc != DG_OK) return rc;
-        rc = plan_operand(g[i], g[i].a, /*is_a=*/true, 128, 256, false, &act);
+        rc = plan_operand(g[i], g[i].a, /*is_a=*/true, dg::FusedCfg::BN / 2, 256, false, &act);
         if (rc != DG_OK) return rc;
-        p.tm_w[i] = w.tm, p.tm_wsf[i] = w.tm_sf, p.tm_act[i] = act.tm, p.tm_actsf[i] = act.tm_sf;
+        // the tokens' scale words: 256 rows per token tile, tile after tile
+        dg_gemm_args gs = g[i];
+        gs.m = a.L.sf_rows, gs.a.sf_ld = a.L.sf_rows;
+        OperandPlan act_sf;
+        rc = plan_operand(gs, gs.a, /*is_a=*/true, 32, 256, false, &act_sf);
+        if (rc != DG_OK) return rc;
+        p.tm_w[i] = w.tm, p.tm_wsf[i] = w.tm_sf, p.tm_act[i] = act.tm, p.tm_actsf[i] = act_sf.tm_sf;
         for (int j = 0; j < 2; ++j) {
             OperandPlan small;
             rc = plan_operand(g[i], g[i].a, /*is_a=*/true, j == 0 ? 32 : 64, 256, false, &small);
@@ -920,6 +927,7 @@ int dg_mega_moe_buffer_layout(const dg_moe_config* cfg, dg_moe_layout* out) {
     out->off_combine = L.off_combine;
     out->off_shared_l1_acts_sf = L.off_shared_sf, out->off_shared_l2_acts = L.off_shared_l2_acts;
     out->off_shared_l2_acts_sf = L.off_shared_l2_sf;
+    out->sf_rows = static_cast<int64_t>(L.sf_rows);
     return DG_OK;
 }
 

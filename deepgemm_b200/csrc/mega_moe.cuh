@@ -18,6 +18,11 @@ namespace dg {
 
 constexpr uint32_t kMoeMaxRanks = 16;
 constexpr uint32_t kMoePoolAlign = 128;   // rows: every expert's pool segment starts on this boundary
+// Token rows per tile of the single-kernel forward: two accumulators of 240 columns plus the scale columns fit the 512
+// columns of tensor memory without sharing any (with 256 a tile's first UMMA has to wait until the tile before it has
+// been drained from the columns they share); the reference chooses the same tile for the same reason
+// (csrc/jit_kernels/heuristics/mega_moe.hpp:88-141).
+constexpr uint32_t kMoeTileRows = 240;
 
 // The first kMoeCtrlBytes of every buffer hold the control block: words whose meaning and place do not depend on the
 // configuration (num_experts, tokens, hidden ...), so that a buffer may be reused for another configuration between
@@ -41,6 +46,8 @@ struct MoeLayout {
     uint32_t shared;         // shared experts (0: none); they act as one expert of intermediate size shared * inter
     uint32_t planes;         // combine planes: topk, plus one for the shared experts' result
     uint32_t pool_rows;      // capacity of the expert-sorted pool (multiple of 256)
+    uint32_t sf_rows;        // row pitch of l1_sf / l2_sf: pool_rows, or more where the single kernel's tiles need it (each
+                             // tile owns 256 scale rows of its own, in tcgen05.cp order relative to the tile's first row)
     uint64_t off_ctrl;       // control block, always 0
     uint64_t off_recv_count; // u32 [ranks][experts_local]: rows each source rank sends to each local expert
     uint64_t off_src_idx;    // u32 [experts_local][ranks][t_max]: token * topk + slot, written by the source rank
@@ -67,12 +74,14 @@ struct MoeWork {
 
 // Work-area tables used only by the fused kernel (after the tables of MoeWork)
 struct MoeFusedWork {
-    __host__ __device__ static uint32_t max_tiles(const MoeLayout& L) { return L.pool_rows / 256 + L.experts_local; }
+    __host__ __device__ static uint32_t max_tiles(const MoeLayout& L) { return L.pool_rows / kMoeTileRows + L.experts_local + 1; }
     __host__ __device__ static uint32_t tile_table(const MoeLayout& L) { return MoeWork::words(L.experts_local, L.ranks); }
-    // per tile: row0, rows (UMMA N), expert, valid rows in its first 128-row block, valid rows in its second
-    __host__ __device__ static uint32_t pulled(const MoeLayout& L) { return tile_table(L) + max_tiles(L) * 8; }   // [pool_rows / 128]
-    __host__ __device__ static uint32_t l1_done(const MoeLayout& L) { return pulled(L) + L.pool_rows / 128; }      // [max_tiles]
-    __host__ __device__ static uint32_t words(const MoeLayout& L) { return l1_done(L) + max_tiles(L); }
+    // per tile: row0, rows (UMMA N, a multiple of 16), expert, rows that carry a token, first scale row (tile * 256)
+    __host__ __device__ static uint32_t pulled(const MoeLayout& L) { return tile_table(L) + max_tiles(L) * 8; }   // [max_tiles]
+    __host__ __device__ static uint32_t l1_done(const MoeLayout& L) { return pulled(L) + max_tiles(L); }          // [max_tiles]
+    // per expert: first pool row, first tile
+    __host__ __device__ static uint32_t expert_tab(const MoeLayout& L) { return l1_done(L) + max_tiles(L); }      // [2 * experts_local]
+    __host__ __device__ static uint32_t words(const MoeLayout& L) { return expert_tab(L) + 2 * L.experts_local; }
 };
 
 inline uint64_t moe_align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
@@ -89,6 +98,8 @@ inline MoeLayout make_moe_layout(uint32_t ranks, uint32_t experts, uint32_t t_ma
     uint64_t rows = static_cast<uint64_t>(t_max) * ranks * active_topk;
     if (pool_cap != 0 && pool_cap < rows) rows = pool_cap;
     L.pool_rows = static_cast<uint32_t>(moe_align_up(rows + slack, 256));
+    const uint32_t tile_sf_rows = (L.pool_rows / kMoeTileRows + L.experts_local + 1) * 256;
+    L.sf_rows = tile_sf_rows > L.pool_rows ? tile_sf_rows : L.pool_rows;
     uint64_t off = 0;
     auto take = [&](uint64_t bytes) {
         const uint64_t o = off;
@@ -103,11 +114,11 @@ inline MoeLayout make_moe_layout(uint32_t ranks, uint32_t experts, uint32_t t_ma
     L.off_topk_idx = take(static_cast<uint64_t>(t_max) * topk * 8);
     L.off_topk_w = take(static_cast<uint64_t>(t_max) * topk * 4);
     L.off_l1_acts = take(static_cast<uint64_t>(L.pool_rows) * hidden);
-    L.off_l1_sf = take(static_cast<uint64_t>(L.pool_rows) * (hidden / 128) * 4);
+    L.off_l1_sf = take(static_cast<uint64_t>(L.sf_rows) * (hidden / 128) * 4);
     L.off_pool_w = take(static_cast<uint64_t>(L.pool_rows) * 4);
     L.off_pool_meta = take(static_cast<uint64_t>(L.pool_rows) * 12);
     L.off_l2_acts = take(static_cast<uint64_t>(L.pool_rows) * inter);
-    L.off_l2_sf = take(static_cast<uint64_t>(L.pool_rows) * (inter / 128) * 4);
+    L.off_l2_sf = take(static_cast<uint64_t>(L.sf_rows) * (inter / 128) * 4);
     L.off_combine = take(static_cast<uint64_t>(L.planes) * t_max * hidden * 2);
     if (shared != 0) {
         const uint64_t t_al = moe_align_up(t_max, 128), inter_s = static_cast<uint64_t>(shared) * inter;
@@ -185,7 +196,7 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const MoeArgs a) {
 // (`nthreads` of them).  With `fused` != nullptr it also writes the fused kernel's tile table, clears its
 // progress counters and finally publishes `layout_ready`.  Returns false if the barrier timed out.
 struct MoeFusedHooks {
-    uint32_t tile_table, pulled, l1_done;   // word offsets in the work area
+    uint32_t tile_table, pulled, l1_done, expert_tab;   // word offsets in the work area
 };
 // `scratch`: kMoeScanWords words of shared memory for the layout scan (nullptr: scan in global memory).
 constexpr uint32_t kMoeScanCap = 512, kMoeScanWords = 4 * kMoeScanCap + 1;
@@ -255,14 +266,13 @@ DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthrea
                 break;
             }
             if (fused != nullptr) {
-                // 256-token tiles over the expert's aligned extent
+                // tiles of kMoeTileRows tokens over the expert's rows; the last one rounded up to the UMMA's N step
                 const uint32_t total = row - start;
-                const uint32_t aligned = (total + kMoePoolAlign - 1) / kMoePoolAlign * kMoePoolAlign;
-                for (uint32_t off = 0; off < aligned; off += 256, ++tiles) {
+                work[fused->expert_tab + 2 * el] = start, work[fused->expert_tab + 2 * el + 1] = tiles;
+                for (uint32_t off = 0; off < total; off += kMoeTileRows, ++tiles) {
                     uint32_t* t = work + fused->tile_table + tiles * 8;
-                    t[0] = start + off, t[1] = min(256u, aligned - off), t[2] = el;
-                    t[3] = total > off ? min(128u, total - off) : 0;
-                    t[4] = total > off + 128 ? min(128u, total - off - 128) : 0;
+                    const uint32_t valid = min(kMoeTileRows, total - off);
+                    t[0] = start + off, t[1] = (valid + 15u) & ~15u, t[2] = el, t[3] = valid, t[4] = tiles * 256;
                 }
             }
             prev_end = row;
@@ -309,8 +319,7 @@ DG_DEVICE bool moe_exchange_body(const MoeArgs& a, uint32_t tid, uint32_t nthrea
         for (uint32_t r = end + tid; r < stop; r += nthreads) meta[r * 3] = -1;
     }
     if (fused != nullptr) {
-        for (uint32_t i = tid; i < s_rows / 128; i += nthreads) work[fused->pulled + i] = 0;
-        for (uint32_t i = tid; i < s_tiles; i += nthreads) work[fused->l1_done + i] = 0;
+        for (uint32_t i = tid; i < s_tiles; i += nthreads) work[fused->pulled + i] = 0, work[fused->l1_done + i] = 0;
         __threadfence();
         __syncthreads();
         if (tid == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ctrl + MoeCtrl::kLayoutReady), "r"(s_call) : "memory");
@@ -324,9 +333,10 @@ __global__ void __launch_bounds__(256) moe_exchange_kernel(const MoeArgs a) {
 }
 
 // ---- step 3: pull every routed token (row, packed scales, route weight) into the pool.  One warp per row:
-// flat rows first, first + stride, ...; `pulled` (optional) counts finished rows per 128-row pool block.
+// flat rows first, first + stride, ...  The single kernel passes `pulled` (finished rows per tile) and `expert_tab`
+// (first pool row and first tile per expert): its scale rows are laid out per tile.
 DG_DEVICE void moe_pull_rows(const MoeArgs& a, const uint32_t* s_prefix, uint32_t first, uint32_t stride, uint32_t lane,
-                             uint32_t* pulled) {
+                             uint32_t* pulled, const uint32_t* expert_tab = nullptr) {
     const MoeLayout& L = a.L;
     const uint32_t* work = reinterpret_cast<const uint32_t*>(a.base[a.rank] + L.off_work);
     const uint32_t segments = L.experts_local * L.ranks;
@@ -367,9 +377,15 @@ DG_DEVICE void moe_pull_rows(const MoeArgs& a, const uint32_t* s_prefix, uint32_
             }
         }
         const uint32_t* sf_from = reinterpret_cast<const uint32_t*>(peer + L.off_x_sf) + static_cast<uint64_t>(token) * sf_words;
-        // scale words go straight into the per-128-row order tcgen05.cp reads (no transposition in the GEMM)
-        const uint32_t sf_dst = moe_sf_row(dst);
-        for (uint32_t c = lane; c < sf_words; c += 32) l1_sf[static_cast<uint64_t>(c) * L.pool_rows + sf_dst] = sf_from[c];
+        // scale words go straight into the per-128-row order tcgen05.cp reads (no transposition in the GEMM):
+        // relative to the pool (kernel-per-phase path) or to the row's tile (single kernel)
+        uint32_t sf_dst = moe_sf_row(dst), sf_ld = L.pool_rows, tile = 0;
+        if (expert_tab != nullptr) {
+            const uint32_t pos = dst - expert_tab[2 * el];
+            tile = expert_tab[2 * el + 1] + pos / kMoeTileRows;
+            sf_dst = tile * 256 + moe_sf_row(pos % kMoeTileRows), sf_ld = L.sf_rows;
+        }
+        for (uint32_t c = lane; c < sf_words; c += 32) l1_sf[static_cast<uint64_t>(c) * sf_ld + sf_dst] = sf_from[c];
         if (lane == 0) {
             pool_w[dst] = reinterpret_cast<const float*>(peer + L.off_topk_w)[pair];
             meta[dst * 3 + 0] = static_cast<int32_t>(src);
@@ -381,7 +397,7 @@ DG_DEVICE void moe_pull_rows(const MoeArgs& a, const uint32_t* s_prefix, uint32_
             asm volatile("fence.proxy.async;" ::: "memory");
             __threadfence();
             __syncwarp();
-            if (lane == 0) atomicAdd(pulled + dst / 128, 1u);
+            if (lane == 0) atomicAdd(pulled + tile, 1u);
         }
     }
 }

@@ -1,9 +1,9 @@
 // Mega MoE forward as ONE persistent kernel: dispatch (count, index scatter, count exchange, token pull over
-// NVLink peer loads), the two expert GEMMs (tcgen05 block-scaled UMMA, 2-CTA pairs, 256-token tiles) with the
+// NVLink peer loads), the two expert GEMMs (tcgen05 block-scaled UMMA, 2-CTA pairs, 240-token tiles) with the
 // SwiGLU / requantisation and combine-push epilogues, and the top-k reduction.
 //
-// Dataflow inside the launch: pull warps fill the expert-sorted pool in pool order and count rows per 128-row
-// block; the TMA producer starts a first-GEMM tile as soon as its rows are there; second-GEMM tiles of token
+// Dataflow inside the launch: pull warps fill the expert-sorted pool in pool order and count rows per token
+// tile; the TMA producer starts a first-GEMM tile as soon as its rows are there; second-GEMM tiles of token
 // tile j - lag are interleaved after the first-GEMM tiles of tile j and wait (rarely) on a per-tile counter
 // that the first GEMM's epilogue bumps; the combine push therefore spreads over the whole kernel.  Two
 // grid-wide barriers (after the scatter, before the reduction) and two cross-rank barriers per call.
@@ -35,7 +35,8 @@ struct MoeFusedParams {
 };
 
 struct FusedCfg {
-    static constexpr uint32_t BN = 256, R_STAGE = 128 * 128, C_STAGE = 128 * 128, SFR_STAGE = 512, SFC_STAGE = 1024;
+    // Two accumulators of BN columns and the scale columns fit tensor memory without sharing columns
+    static constexpr uint32_t BN = kMoeTileRows, R_STAGE = 128 * 128, C_STAGE = BN / 2 * 128, SFR_STAGE = 512, SFC_STAGE = 1024;
     static constexpr uint32_t STAGE_BYTES = R_STAGE + C_STAGE + SFR_STAGE + SFC_STAGE;
     static constexpr uint32_t PITCH = 272;
     static constexpr uint32_t TABLE_OFF = 2 * 32 * PITCH;
@@ -44,14 +45,15 @@ struct FusedCfg {
     static constexpr uint32_t CD_BYTES = (PREFIX_OFF + 512 * 4 + 1023) / 1024 * 1024;
     static constexpr uint32_t kStages = (232448 - 1024 - CD_BYTES - 1024) / STAGE_BYTES;
     static constexpr uint32_t kSmemBytes = 1024 + kStages * STAGE_BYTES + CD_BYTES + 1024;
-    static constexpr uint32_t kOverlap = 16, kAccStride = BN - kOverlap, kSfrCol = 2 * BN - kOverlap, kSfcCol = kSfrCol + 4;
+    static constexpr uint32_t kAccStride = BN, kSfrCol = 2 * BN, kSfcCol = kSfrCol + 4;
     static constexpr uint32_t kTmemCols = 512;
 };
 static_assert(FusedCfg::kStages >= 4 && FusedCfg::kStages <= 10, "stage count");
+static_assert(FusedCfg::kSfcCol + 8 <= FusedCfg::kTmemCols && FusedCfg::C_STAGE % 1024 == 0 && FusedCfg::BN % 16 == 0, "tile");
 
 struct FusedTile {
     uint32_t kind;   // 0: first GEMM, 1: second GEMM
-    uint32_t tile, row0, rows, group, n_blk, valid0, valid1;
+    uint32_t tile, row0, rows, group, n_blk, valid, sf_base;
 };
 
 // Bounded spin on a device-scope counter; false on timeout / abort.
@@ -92,7 +94,7 @@ DG_DEVICE bool fused_slot_to_tile(const uint32_t* table, uint32_t num_tiles, uin
         t.kind = 1, t.tile = round - lag, t.n_blk = r - n1;
     }
     const uint32_t* e = table + t.tile * 8;
-    t.row0 = e[0], t.rows = e[1], t.group = e[2], t.valid0 = e[3], t.valid1 = e[4];
+    t.row0 = e[0], t.rows = e[1], t.group = e[2], t.valid = e[3], t.sf_base = e[4];
     return true;
 }
 
@@ -131,7 +133,7 @@ DG_DEVICE bool fused_grid_barrier(uint32_t* ctrl, uint32_t num_ctas, volatile ui
 // number of threads.  Thread 0 issues, all threads sum (slot order, FP32) and store BF16.  The kernel's operand
 // stages are free by now (all roles have left their loops and the grid barrier has passed).
 #ifndef DG_REDUCE_PIECE
-#define DG_REDUCE_PIECE 3072
+#define DG_REDUCE_PIECE 2560
 #define DG_REDUCE_STAGES 4
 #endif
 constexpr uint32_t kReducePiece = DG_REDUCE_PIECE, kReduceStages = DG_REDUCE_STAGES, kReduceSlotBytes = kReducePiece * 2;
@@ -293,7 +295,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
         for (uint32_t i = 0; i < 2; ++i) {
             mbar_init(&bars->tmem_full[i], 1);
             mbar_init(&bars->tmem_empty[i], 2 * 4);
-            mbar_init(&bars->overlap[i], 2 * 4);
             mbar_init(&s_epi_bar[i][0], 4), mbar_init(&s_epi_bar[i][1], 4);
         }
         bars->abort = 0;
@@ -320,7 +321,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     if (ok && blockIdx.x == 0) {
         MoeFusedHooks hooks;
         hooks.tile_table = MoeFusedWork::tile_table(L), hooks.pulled = MoeFusedWork::pulled(L);
-        hooks.l1_done = MoeFusedWork::l1_done(L);
+        hooks.l1_done = MoeFusedWork::l1_done(L), hooks.expert_tab = MoeFusedWork::expert_tab(L);
         // the operand stages are idle until the roles start: their first words serve the layout scan
         moe_exchange_body(p.a, threadIdx.x, kFusedThreads, &hooks, reinterpret_cast<uint32_t*>(smem_gen));
     }
@@ -367,8 +368,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             if (!fused_slot_to_tile(table, num_tiles, n1, n2, p.lag, slot, tc)) continue;
             // Data dependencies: pool rows pulled (first GEMM) / activations written (second GEMM)
             if (tc.kind == 0) {
-                DG_FUSED_TIMED(5, ok = fused_wait_counter(pulled + tc.row0 / 128, tc.valid0, abort_flag, p.a, 203, tc.tile));
-                if (ok && tc.rows > 128) DG_FUSED_TIMED(5, ok = fused_wait_counter(pulled + tc.row0 / 128 + 1, tc.valid1, abort_flag, p.a, 203, tc.tile));
+                DG_FUSED_TIMED(5, ok = fused_wait_counter(pulled + tc.tile, tc.valid, abort_flag, p.a, 203, tc.tile));
             } else {
                 DG_FUSED_TIMED(7, ok = fused_wait_counter(l1_done + tc.tile, n1 * 8, abort_flag, p.a, 204, tc.tile));
             }
@@ -379,11 +379,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             const uint32_t r_mn = tc.n_blk * 256 + cta_rank * 128;   // row inside the expert; the expert is the map's third coordinate
             const uint32_t sfr_mn = tc.n_blk * 256 + cta_rank * 128, sfr_k = tc.group * pk;
             const uint32_t c_mn = tc.row0 + cta_rank * (tc.rows / 2);
-            const uint32_t sfc_mn = tc.row0;
+            const uint32_t sfc_mn = tc.sf_base;   // the tile's own 256 scale rows
             const uint32_t num_kb = pk;
             const uint32_t per_cta = tc.rows / 2;
             const CUtensorMap* tm_act = per_cta <= 32 ? &p.tm_act_small[k][0] : per_cta <= 64 ? &p.tm_act_small[k][1] : &p.tm_act[k];
-            const uint32_t tx_bytes = (per_cta <= 32 ? 32u : per_cta <= 64 ? 64u : 128u) * 128u;
+            const uint32_t tx_bytes = (per_cta <= 32 ? 32u : per_cta <= 64 ? 64u : BN / 2) * 128u;
             for (uint32_t kb = 0; kb < num_kb; ++kb, advance()) {
                 DG_FUSED_TIMED(6, ok = wait_barrier(&bars->empty[stage], phase ^ 1, abort_flag, peer_abort, wp, kSiteProducerEmpty, acc_iter, kb, stage));
                 if (!ok) break;
@@ -418,10 +418,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                 if (!fused_slot_to_tile(table, num_tiles, n1, n2, p.lag, slot, tc)) continue;
                 const uint32_t acc = acc_iter & 1, acc_phase = (acc_iter >> 1) & 1;
                 DG_FUSED_TIMED(5, ok = wait_barrier(&bars->tmem_empty[acc], acc_phase ^ 1, abort_flag, peer_abort, wp, kSiteMmaTmemEmpty, acc_iter, 0, acc));
-                if (ok && acc_iter > 0) {
-                    const uint32_t prev = acc_iter - 1;
-                    DG_FUSED_TIMED(7, ok = wait_barrier(&bars->overlap[prev & 1], (prev >> 1) & 1, abort_flag, peer_abort, wp, kSiteMmaOverlap, acc_iter, 0, acc));
-                }
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * Cfg::kAccStride;
@@ -459,7 +455,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
         // buffer read).
         const uint32_t group = warp >= 13 ? 1u : 0u, q = warp % 4;
         const uint32_t tmem_empty_bar = map_to_cta(smem_u32(&bars->tmem_empty[0]), 0);
-        const uint32_t overlap_bar = map_to_cta(smem_u32(&bars->overlap[0]), 0);
         uint64_t* bar_written = &s_epi_bar[group][0];
         uint64_t* bar_read = &s_epi_bar[group][1];
         uint8_t* stage_gen = smem_gen + (smem_cd - smem_base) + group * 32 * Cfg::PITCH;
@@ -474,8 +469,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             // Per-token data of the tile, fetched while its UMMAs run.  The reading threads themselves must have
             // seen the counters that say the pool rows (and, for the second GEMM, the routing metadata) are there.
             if (tc.kind == 0) {
-                DG_FUSED_TIMED(7, ok = fused_wait_counter(pulled + tc.row0 / 128, tc.valid0, abort_flag, p.a, 207, tc.tile));
-                if (ok && tc.rows > 128) DG_FUSED_TIMED(7, ok = fused_wait_counter(pulled + tc.row0 / 128 + 1, tc.valid1, abort_flag, p.a, 207, tc.tile));
+                DG_FUSED_TIMED(7, ok = fused_wait_counter(pulled + tc.tile, tc.valid, abort_flag, p.a, 207, tc.tile));
             } else {
                 DG_FUSED_TIMED(7, ok = fused_wait_counter(l1_done + tc.tile, n1 * 8, abort_flag, p.a, 208, tc.tile));
             }
@@ -509,19 +503,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             const uint32_t t_acc = tmem_base + acc * Cfg::kAccStride + ((q * 32) << 16);
             const uint32_t n0 = tc.n_blk * 256 + cta_rank * 128;
             const uint32_t num_chunks = (tc.rows + 31) / 32;
-            const bool reverse = acc == 0;   // stage 0 shares its last columns, stage 1 its first: drain those first
 #pragma unroll 1
             for (uint32_t i = 0; i < num_chunks && ok; ++i) {
-                const uint32_t ch = reverse ? num_chunks - 1 - i : i;
+                const uint32_t ch = i;
                 uint32_t v[32];
                 DG_EPI_TIMED(1, tmem_ld_32x32b_x32(t_acc + ch * 32, v); tmem_ld_wait(););
-                if (i == 0 || i + 1 == num_chunks) {
+                if (i + 1 == num_chunks) {
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) {
-                        if (i == 0) mbar_arrive_cluster(overlap_bar + acc * 8);
-                        if (i + 1 == num_chunks) mbar_arrive_cluster(tmem_empty_bar + acc * 8);
-                    }
+                    if (lane == 0) mbar_arrive_cluster(tmem_empty_bar + acc * 8);
                 }
                 // the staging buffer's previous chunk has been read by all four warps (the tile's first chunk
                 // already waited above)
@@ -539,7 +529,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                 if (!ok) break;
                 const uint32_t chunk_rows = min(32u, tc.rows - ch * 32);
                 if (tc.kind == 0)
-                    DG_EPI_TIMED(3, moe_l1_chunk(p.e, stage_gen, Cfg::PITCH, reinterpret_cast<const float*>(ttab), q, lane, ch, chunk_rows, tc.row0, n0); __syncwarp(););
+                    DG_EPI_TIMED(3, moe_l1_chunk(p.e, stage_gen, Cfg::PITCH, reinterpret_cast<const float*>(ttab), q, lane, ch, chunk_rows, tc.row0, n0, tc.sf_base); __syncwarp(););
                 else
                     DG_EPI_TIMED(4, moe_l2_chunk(stage_gen, Cfg::PITCH, ttab, q * 32 + lane, ch, chunk_rows, n0, p.e.post_down ? p.e.pool_w + tc.row0 : nullptr); __syncwarp(););
                 __syncwarp();
@@ -560,7 +550,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     } else if (ok) {
         // ============================================================ pull warps (2, 8..11): fill the pool in pool order
         const uint32_t pw = warp == 2 ? 0 : warp - 7;   // 0..4
-        moe_pull_rows(p.a, s_prefix, blockIdx.x * 5 + pw, p.num_ctas * 5, lane, pulled);
+        moe_pull_rows(p.a, s_prefix, blockIdx.x * 5 + pw, p.num_ctas * 5, lane, pulled, work + MoeFusedWork::expert_tab(L));
     }
 
     DG_FUSED_FLUSH();

@@ -100,15 +100,15 @@ class SymmBuffer:
             flat = self.buffer[off:off + n].view(dtype)
             return flat.view(shape) if strides is None else flat.as_strided(shape, strides)
 
-        t, k, h, i, p = num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden, lay.pool_rows
+        t, k, h, i, p, q = num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden, lay.pool_rows, lay.sf_rows
         self.x = view(lay.off_x, torch.float8_e4m3fn, (t, h))
         self.x_sf = view(lay.off_x_sf, torch.int32, (t, h // 128))
         self.topk_idx = view(lay.off_topk_idx, torch.int64, (t, k))
         self.topk_weights = view(lay.off_topk_weights, torch.float32, (t, k))
         self.l1_acts = view(lay.off_l1_acts, torch.float8_e4m3fn, (p, h))
-        self.l1_acts_sf = view(lay.off_l1_acts_sf, torch.int32, (p, h // 128), (1, p))
+        self.l1_acts_sf = view(lay.off_l1_acts_sf, torch.int32, (q, h // 128), (1, q))
         self.l2_acts = view(lay.off_l2_acts, torch.float8_e4m3fn, (p, i))
-        self.l2_acts_sf = view(lay.off_l2_acts_sf, torch.int32, (p, i // 128), (1, p))
+        self.l2_acts_sf = view(lay.off_l2_acts_sf, torch.int32, (q, i // 128), (1, q))
         self.token_src_metadata = view(lay.off_token_src_metadata, torch.int32, (p, 3))
         self.combine = view(lay.off_combine, torch.bfloat16, (k + (1 if num_shared_experts else 0), t, h))
         # Shared experts (deep_gemm/mega/__init__.py:107-123): their first GEMM reads x itself; its scales are needed
@@ -121,7 +121,7 @@ class SymmBuffer:
             self.shared_l2_acts = view(lay.off_shared_l2_acts, torch.float8_e4m3fn, (ta, i_s))
             self.shared_l2_acts_sf = view(lay.off_shared_l2_acts_sf, torch.int32, (ta, i_s // 128), (1, ta))
         self.num_ring_tokens = p
-        self.num_sf_ring_tokens = p
+        self.num_sf_ring_tokens = q
 
     def load_tokens(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor) -> int:
         """Fill the input views from BF16 activations: one fused kernel casts x to E4M3 with per-32 UE8M0 scales

@@ -157,10 +157,12 @@ typedef struct dg_moe_config {
 
 /* Byte offsets of the views inside one rank's buffer (shapes as in csrc/apis/mega_moe.hpp:137-226 of the
  * reference): x e4m3 [T, H]; x_sf int32 [T, H/128]; topk_idx int64 [T, K]; topk_weights f32 [T, K];
- * l1_acts e4m3 [P, H]; l1_acts_sf int32 [P, H/128] with strides (1, P); l2_acts e4m3 [P, I];
- * l2_acts_sf int32 [P, I/128] with strides (1, P); token_src_metadata int32 [P, 3];
- * combine bf16 [K (+ 1 with shared experts), T, H].  P = pool_rows.  Inside every 128 pool rows the scale words of
- * l1_acts_sf and l2_acts_sf sit in the order tcgen05.cp consumes: row r of the block is stored at (r % 32) * 4 + r / 32.
+ * l1_acts e4m3 [P, H]; l1_acts_sf int32 [Q, H/128] with strides (1, Q); l2_acts e4m3 [P, I];
+ * l2_acts_sf int32 [Q, I/128] with strides (1, Q); token_src_metadata int32 [P, 3];
+ * combine bf16 [K (+ 1 with shared experts), T, H].  P = pool_rows, Q = sf_rows >= P.  The scale words of l1_acts_sf
+ * and l2_acts_sf sit in blocks of 128 rows in the order tcgen05.cp consumes (row r of a block at (r % 32) * 4 + r / 32);
+ * the single-kernel forward gives every 240-token tile 256 scale rows of its own (tile j: rows [256 j, 256 j + 256)),
+ * the kernel-per-phase forward uses the first P rows, pool row for pool row.
  * With shared experts (offsets 0 otherwise): shared_l1_acts_sf int32 [T', H/128] with strides (1, T'), T' = T rounded
  * up to 128 - the scales of x once more, in that same row order, filled by the caller along with x_sf;
  * shared_l2_acts e4m3 [T', S*I]; shared_l2_acts_sf int32 [T', S*I/128] with strides (1, T'). */
@@ -169,6 +171,7 @@ typedef struct dg_moe_layout {
     int64_t off_x, off_x_sf, off_topk_idx, off_topk_weights;
     int64_t off_l1_acts, off_l1_acts_sf, off_l2_acts, off_l2_acts_sf, off_token_src_metadata, off_combine;
     int64_t off_shared_l1_acts_sf, off_shared_l2_acts, off_shared_l2_acts_sf;
+    int64_t sf_rows;
 } dg_moe_layout;
 
 /* Size and view offsets of the symmetric buffer.  Takes the role of get_symm_buffer_size_for_mega_moe_v3

@@ -140,6 +140,21 @@ def test_mega_moe_buffer_layout_and_checks():
     assert dg.get_token_alignment_for_mega_moe() == 128
 
 
+def test_mega_moe_scale_rows_cover_every_tile():
+    """The single-kernel forward gives every 240-token tile 256 scale rows: whatever the split of the pool over the
+    local experts, the tiles' scale rows fit `sf_rows`."""
+    lay = _lib.MoeLayout()
+    for ranks, experts, tokens, topk in ((8, 256, 4096, 8), (1, 48, 8192, 6), (2, 8, 128, 4), (8, 64, 128, 8)):
+        cfg = _lib.MoeConfig(ranks, experts, tokens, topk, 1024, 512, 0, 0)
+        assert _lib.lib().dg_mega_moe_buffer_layout(ctypes.byref(cfg), ctypes.byref(lay)) == 0
+        local, rows = experts // ranks, min(ranks * tokens * topk, lay.pool_rows)
+        assert lay.sf_rows >= lay.pool_rows and lay.sf_rows % 256 == 0
+        for split in ([rows // local] * local, [1] * (local - 1) + [rows - (local - 1)],
+                      [241] * min(local, rows // 241) + [0] * (local - min(local, rows // 241))):
+            tiles = sum(-(-r // 240) for r in split)
+            assert tiles * 256 <= lay.sf_rows, (ranks, experts, split[:3])
+
+
 def test_mega_moe_sm_headroom_policy(monkeypatch):
     """The table of the reference's tests/test_mega_moe_headroom.py: the grid is num_sms minus the headroom rounded up to
     even; negative, all-consuming and odd results are refused."""
