@@ -726,8 +726,6 @@ def main():
     ap.add_argument("--tile", default="", help="tuning aid: cta_group,block_n,swap (0 = automatic) pinned for every GEMM")
     ap.add_argument("--masked-costs", default="", help="tuning aid: first,next_base,next_per_256_rows of the masked GEMM's "
                                                      "tile cost estimate (first = 0: round-robin deal)")
-    ap.add_argument("--weight-prefetch", type=int, default=-1, help="tuning aid: 0 / 1 switches the masked GEMM's L2 prefetch "
-                                                                  "of the weight stream")
     ap.add_argument("--masked-rows", type=int, default=0, help="tuning aid: config c3 with this many rows in every group")
     ap.add_argument("--moe-tokens", type=int, default=4096, help="tokens per rank of the Mega MoE run")
     ap.add_argument("--moe-experts", type=int, default=32, help="experts per rank of the Mega MoE run")
@@ -757,8 +755,6 @@ def main():
         _lib.check(_lib.lib().dg_debug_set_tile_override(cta, bn, swap))
     if args.masked_costs:
         _lib.check(_lib.lib().dg_debug_set_masked_costs(*(int(v) for v in args.masked_costs.split(","))))
-    if args.weight_prefetch >= 0:
-        _lib.check(_lib.lib().dg_debug_set_weight_prefetch(args.weight_prefetch))
     global MASKED_ROWS_OVERRIDE
     MASKED_ROWS_OVERRIDE = args.masked_rows
 
@@ -774,7 +770,7 @@ def main():
         out = other_configs(device, max(1, min(args.steps, 10)), args.warmup, which=(args.only,))
         if rank == 0:
             emit({"other_configs": out, "tile": args.tile or "automatic", "masked_costs": args.masked_costs or "default",
-                  "masked_rows": args.masked_rows or "config", "weight_prefetch": args.weight_prefetch})
+                  "masked_rows": args.masked_rows or "config"})
         return
 
     w = make_c2(device, seed=0)

@@ -124,10 +124,6 @@ __host__ __device__ inline uint32_t moe_sf_row(uint32_t row) {
 struct GemmParams {
     CUtensorMap tm_r, tm_c, tm_sfr, tm_sfc, tm_d;
     CUtensorMap tm_d_half;   // swapped tiles: D seen through boxes of 16 token rows, for a tile's last 16 rows
-    // R seen as 8-byte elements through boxes of 32 rows x 2 KB: L2 prefetch of an operand that streams from HBM once
-    // (the weights of the masked layout).  prefetch_r = 0: not used
-    CUtensorMap tm_r_prefetch;
-    uint32_t prefetch_r;
     // Swapped tiles with few token rows: the same C operand seen through boxes of 32 and 64 rows per CTA, so a
     // ragged last tile of an expert does not fetch 128 rows per CTA and K block (c_small != 0 when encoded)
     CUtensorMap tm_c_small[2];
@@ -817,19 +813,6 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                       }
                     } else if (r_role) {
                       if (elect_one()) {
-                        if (p.prefetch_r && (kb & 15u) == 0) {
-                            // 2 KB of K (16 K blocks) per row at a time, one chunk ahead of the tile loads; a tile's
-                            // first two chunks go out together
-                            const uint32_t kbyte = r_k + kb * 128;
-                            for (uint32_t rows = 0; rows < 128; rows += 32) {
-                                if (kb == 0)
-                                    tma_prefetch_l2_3d(&p.tm_r_prefetch, static_cast<int32_t>(kbyte >> 3),
-                                                       static_cast<int32_t>(r_mn + rows), r_batch);
-                                if (kb + 16 < num_kb)
-                                    tma_prefetch_l2_3d(&p.tm_r_prefetch, static_cast<int32_t>((kbyte + 2048) >> 3),
-                                                       static_cast<int32_t>(r_mn + rows), r_batch);
-                            }
-                        }
                         // Operand tiles land on the leader's barrier (both CTAs of a pair feed one UMMA)
                         const uint32_t full_bar = full_bar0 + stage * 8;
                         mbar_arrive_expect_tx_cluster(full_bar, p.r.tx_bytes);

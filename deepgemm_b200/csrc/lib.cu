@@ -64,7 +64,6 @@ struct Knobs {
     // 0 (default): round-robin deal.  Measured on config 3: cost-balanced runs were slower (183 vs 132 us): a unit's run
     // stays inside one group, so the units read 16 groups' token blocks and weights at once instead of sharing one.
     int masked_cost_first = 0, masked_cost_next_base = 80, masked_cost_next_per_256 = 30;
-    int prefetch_weights = 0;   // masked layout: L2 prefetch of the weight stream (dg_debug_set_weight_prefetch)
 } g_knobs;
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -163,8 +162,9 @@ struct OperandPlan {
 // Build the tensor maps and kernel parameters of one GEMM operand in the role of R (128 rows per
 // CTA) or C (`box_rows` rows per CTA).  Data maps are 3-D: (K, row inside the group, group) for a K-major operand,
 // (row, K row, group) for an MN-major one; an operand without a group axis has a third extent of 1.
+// sf_mn: rows of the scale tensor where they differ from the operand's (scales stored in whole 128-row blocks); 0 = same
 int plan_operand(const dg_gemm_args& a, const dg_operand& op, bool is_a, uint32_t box_rows, uint32_t sf_box_rows,
-                 bool mxf4, OperandPlan* out) {
+                 bool mxf4, OperandPlan* out, uint32_t sf_mn = 0) {
     const uint32_t mn = is_a ? a.m : a.n;
     const bool fp4 = op.dtype == DG_E2M1_PACKED;
     const bool k_grouped = a.gemm_type == DG_GEMM_K_GROUPED || a.gemm_type == DG_GEMM_K_GROUPED_PSUM;
@@ -229,7 +229,7 @@ int plan_operand(const dg_gemm_args& a, const dg_operand& op, bool is_a, uint32_
         packed_k = (static_cast<uint64_t>(a.k) + op.gran_k * 4 - 1) / (op.gran_k * 4);
     }
     {
-        const uint64_t dims[2] = {static_cast<uint64_t>(mn), packed_k * groups};
+        const uint64_t dims[2] = {static_cast<uint64_t>(sf_mn > 0 ? sf_mn : mn), packed_k * groups};
         const uint64_t strides[1] = {static_cast<uint64_t>(op.sf_ld) * 4};
         const uint32_t box[2] = {sf_box_rows, mxf4 ? 2u : 1u};   // kind::mxf4: two scale words per row and stage
         rc = encode_tmap(&out->tm_sf, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, op.sf, dims, strides, box,
@@ -392,11 +392,6 @@ int dg_debug_set_masked_costs(int32_t first, int32_t next_base, int32_t next_per
     std::lock_guard<std::mutex> lk(g_knobs.mu);
     g_knobs.masked_cost_first = first, g_knobs.masked_cost_next_base = next_base;
     g_knobs.masked_cost_next_per_256 = next_per_256_rows;
-    return DG_OK;
-}
-int dg_debug_set_weight_prefetch(int32_t enable) {
-    std::lock_guard<std::mutex> lk(g_knobs.mu);
-    g_knobs.prefetch_weights = enable ? 1 : 0;
     return DG_OK;
 }
 int dg_set_wait_timeout_ms(int32_t ms) {
@@ -583,7 +578,10 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
     OperandPlan plan_r, plan_c;
     int rc = plan_operand(a, op_r, /*is_a=*/!t.swap, 128, 128, mxf4, &plan_r);
     if (rc != DG_OK) return rc;
-    rc = plan_operand(a, op_c, /*is_a=*/t.swap, c_rows_per_cta, sfc_rows, mxf4, &plan_c);
+    // The fused Mega MoE epilogues read token scales stored in tcgen05.cp order, 128 rows to a block: a token's word
+    // may lie anywhere inside its block, so the map covers whole blocks
+    const uint32_t sfc_mn = moe_epi != 0 ? (static_cast<uint32_t>(a.m) + 127u) / 128u * 128u : 0u;
+    rc = plan_operand(a, op_c, /*is_a=*/t.swap, c_rows_per_cta, sfc_rows, mxf4, &plan_c, sfc_mn);
     if (rc != DG_OK) return rc;
 
     dg::GemmLaunch launch;
@@ -599,25 +597,6 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
             p.tm_c_small[i] = small.tm;
         }
         p.c_small = 1;
-    }
-    {
-        // Masked layout, on request: the weights stream from HBM once with little reuse; prefetch them into L2 in 2 KB runs
-        // per row (four boxes of 32 rows per 128-row tile)
-        std::lock_guard<std::mutex> lk(g_knobs.mu);
-        const bool bytes_k_major = !op_r.mn_major && (op_r.dtype == DG_E4M3 || mxf4);
-        const int64_t k_bytes = mxf4 ? a.k / 2 : a.k;
-        if (g_knobs.prefetch_weights && a.gemm_type == DG_GEMM_M_MASKED && t.swap && bytes_k_major && k_bytes % 8 == 0) {
-            const uint64_t groups = a.num_groups;
-            const uint64_t dims[3] = {static_cast<uint64_t>(k_bytes / 8), static_cast<uint64_t>(a.n), groups};
-            const uint64_t batch_stride = op_r.batch_stride > 0 ? static_cast<uint64_t>(op_r.batch_stride)
-                                                                : static_cast<uint64_t>(op_r.ld) * a.n;
-            const uint64_t strides[2] = {static_cast<uint64_t>(op_r.ld), batch_stride};
-            const uint32_t box[3] = {static_cast<uint32_t>(std::min<uint64_t>(256, dims[0])), 32, 1};
-            rc = encode_tmap(&p.tm_r_prefetch, CU_TENSOR_MAP_DATA_TYPE_INT64, 3, op_r.data, dims, strides, box,
-                             CU_TENSOR_MAP_SWIZZLE_NONE, "b (prefetch view)");
-            if (rc != DG_OK) return rc;
-            p.prefetch_r = 1;
-        }
     }
     p.r = plan_r.params, p.c = plan_c.params;
     p.sf_groups_r = plan_r.sf_groups, p.sf_groups_c = plan_c.sf_groups;

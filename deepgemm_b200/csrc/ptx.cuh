@@ -155,14 +155,6 @@ DG_DEVICE void tma_load_3d(uint32_t dst_smem, const void* tmap, uint32_t mbar_ad
             : "memory");
     }
 }
-// Bring a tile of global memory into L2 without a destination in shared memory: long contiguous runs per row make
-// the DRAM reads of an operand that is streamed once far more page-friendly than the 128-byte-per-row tile loads.
-DG_DEVICE void tma_prefetch_l2_3d(const void* tmap, int32_t c0, int32_t c1, int32_t c2) {
-    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(
-                     reinterpret_cast<uint64_t>(tmap)),
-                 "r"(c0), "r"(c1), "r"(c2)
-                 : "memory");
-}
 DG_DEVICE void tma_store_2d(const void* tmap, uint32_t src_smem, int32_t c0, int32_t c1) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                      reinterpret_cast<uint64_t>(tmap)),

@@ -329,10 +329,6 @@ int dg_debug_set_tile_override(int32_t cta_group, int32_t block_n, int32_t swap)
  * token block of `r` rows costs next_base + r * next_per_256_rows / 256.  first = 0 switches to a round-robin deal. */
 int dg_debug_set_masked_costs(int32_t first, int32_t next_base, int32_t next_per_256_rows);
 
-/* Tuning aid: 1 (default) lets the masked grouped GEMM prefetch its weight stream into L2 in 2 KB runs per row ahead
- * of the tile loads (the weights are read from HBM once; long runs make those reads page-friendly); 0 switches it off. */
-int dg_debug_set_weight_prefetch(int32_t enable);
-
 /* Measurement aid (no counterpart in the reference): copies `bytes` (a multiple of 16, both addresses 16-byte
  * aligned) with plain 16-byte loads and stores by all SMs, the way the Mega MoE forward pulls token rows.  Given a
  * peer GPU's mapped address as `src` it measures the NVLink bandwidth that path can reach. */
