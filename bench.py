@@ -445,8 +445,54 @@ def nvlink_probe(device, group, rank, world, buf, nbytes=256 << 20):
     return nbytes / float(t.item()) / 1e6
 
 
+def moe_trace_summary(t, num_ctas, ms):
+    """Text summary of the time stamps a -DDG_TRACE build of the single-kernel Mega MoE forward leaves per CTA and warp:
+    [cta][warp or 18 (epilogue cycles) or 19 (clock64 at the stamps)][slot]; slots 0-4 = %globaltimer at kernel start,
+    roles begin, roles end, reduce begin, end; 5-7 = cycles spent in that warp's waits."""
+    import numpy as np
+    t = t.reshape(-1, 20, 8).astype(np.float64)[:num_ctas]
+    t0 = t[:, :, 0][t[:, :, 0] > 0].min()
+    out = ["event-timed step: %.1f us; %d CTAs; times in us after the first CTA's start (min / median / max over CTAs)" % (ms * 1e3, num_ctas)]
+    names = ["kernel start", "roles begin (scatter, exchange, layout done)", "roles end", "reduce begin (barriers passed)", "end"]
+    for w, role in ((0, "weight-copy warp"), (1, "UMMA warp"), (4, "epilogue warp 4"), (2, "pull warp 2")):
+        for s in range(5):
+            v = t[:, w, s]
+            v = v[v > 0]
+            if len(v):
+                out.append("%-17s %-45s %8.1f %8.1f %8.1f" % (role, names[s], (v.min() - t0) / 1e3, (np.median(v) - t0) / 1e3, (v.max() - t0) / 1e3))
+    waits = {0: ("weight-copy warp", ("pulled / l1_done counters", "stage empty", "-")),
+             3: ("scale-copy warp", ("pulled / l1_done counters", "stage empty", "-")),
+             1: ("UMMA warp", ("accumulator empty", "stage full", "-")),
+             4: ("epilogue warp 4", ("accumulator full", "staging buffer", "pulled / l1_done counters")),
+             13: ("epilogue warp 13", ("accumulator full", "staging buffer", "pulled / l1_done counters"))}
+    out.append("cycles spent waiting, thousands (min / median / max over CTAs):")
+    for w, (role, what) in waits.items():
+        for i, s in enumerate((5, 6, 7)):
+            v = t[:, w, s][0::2] if w == 1 else t[:, w, s]      # the leader CTA of a pair issues the UMMAs
+            if what[i] != "-":
+                out.append("%-17s %-28s %9.1f %9.1f %9.1f" % (role, what[i], v.min() / 1e3, np.median(v) / 1e3, v.max() / 1e3))
+    out.append("epilogue warp 4, cycles per part, thousands (median): per-token table %.1f, tcgen05.ld %.1f, staging %.1f, "
+               "layer-1 chunks %.1f, layer-2 chunks %.1f, layer-1 fence + counter %.1f"
+               % tuple(np.median(t[:, 18, s]) / 1e3 for s in range(6)))
+    fine = ("scatter done", "grid barrier 1 passed", "exchange done (CTA 0: counts out, cross-rank barrier 1, layout, tile table)",
+            "layout seen", "grid barrier 2 passed", "cross-rank barrier 2 passed (CTA 0)")
+    out.append("thread 0 of every CTA, us after the first CTA's start (min / median / max):")
+    for s, name in enumerate(fine):
+        v = t[:, 17, s]
+        v = v[v > 0]
+        if len(v):
+            out.append("  %-88s %8.1f %8.1f %8.1f" % (name, (v.min() - t0) / 1e3, (np.median(v) - t0) / 1e3, (v.max() - t0) / 1e3))
+    cyc, ns = t[:, 19, :5], t[:, 0, :5]
+    for a, b, name in ((0, 1, "prologue"), (1, 2, "roles"), (3, 4, "reduce")):
+        d = ns[:, b] - ns[:, a]
+        f = (cyc[:, b] - cyc[:, a]) / np.maximum(d, 1.0)
+        out.append("%-8s median %7.1f us, SM clock %.3f GHz (clock64 / %%globaltimer), %.0f k cycles"
+                   % (name, np.median(d) / 1e3, np.median(f), np.median(cyc[:, b] - cyc[:, a]) / 1e3))
+    return "\n".join(out) + "\n"
+
+
 def mega_moe_bench(device, group, rank, world, steps, warmup, tokens=4096, experts_per_rank=32, topk=8, hidden=7168,
-                   inter=2048, check_tokens=2048):
+                   inter=2048, check_tokens=2048, trace_path=None):
     """Mega MoE forward of BASELINE config 5 under weak scaling: 32 experts and 4096 tokens per GPU, top-8,
     hidden 7168, intermediate 2048; activations E4M3 with per-32 UE8M0 scales, expert weights MXFP4."""
     import torch
@@ -521,6 +567,28 @@ def mega_moe_bench(device, group, rank, world, steps, warmup, tokens=4096, exper
     ms_phase, _, _ = timed(False)            # one launch per phase (7 kernels)
     y_phase = y.clone()
     ms, rows, stats_fused = timed(True)      # the library's default: one persistent kernel
+    if trace_path:
+        # one more step of the single kernel with its time stamps switched on (needs the -DDG_TRACE build:
+        # python -m deepgemm_b200.build --trace, DEEPGEMM_B200_LIB=deepgemm_b200/lib/libdeepgemm_b200_trace.so)
+        import ctypes
+        from deepgemm_b200 import _lib
+        if not hasattr(_lib.lib(), "dg_debug_set_trace"):
+            raise RuntimeError("--trace needs the library built with -DDG_TRACE (python -m deepgemm_b200.build --trace)")
+        set_trace = _lib.lib().dg_debug_set_trace
+        set_trace.argtypes, set_trace.restype = [ctypes.c_void_p], None
+        trace = torch.zeros(256 * 20 * 8, dtype=torch.int64, device=device)
+        barrier()
+        set_trace(trace.data_ptr())
+        torch.cuda._sleep(1_000_000)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        step()
+        e.record()
+        e.synchronize()
+        set_trace(None)
+        barrier()
+        with open("%s.ep%d.rank%d.txt" % (trace_path, world, rank), "w") as f:
+            f.write(moe_trace_summary(trace.cpu().numpy(), _lib.lib().dg_get_mega_moe_num_sms() // 2 * 2, s.elapsed_time(e)))
     # full-size property: the two paths sum in the same order, so their outputs agree bit for bit on every rank
     agree = reduce(1.0 if torch.equal(y, y_phase) and bool(torch.isfinite(y.float()).all()) else 0.0, dist.ReduceOp.MIN)
     del y_phase
@@ -726,6 +794,8 @@ def main():
     ap.add_argument("--tile", default="", help="tuning aid: cta_group,block_n,swap (0 = automatic) pinned for every GEMM")
     ap.add_argument("--masked-costs", default="", help="tuning aid: first,next_base,next_per_256_rows of the masked GEMM's "
                                                      "tile cost estimate (first = 0: round-robin deal)")
+    ap.add_argument("--trace", default="", help="with --only mega_moe and a -DDG_TRACE build of the library: write the single "
+                                                "kernel's per-CTA time stamps, summarised, to <this>.ep<N>.rank<r>.txt")
     ap.add_argument("--masked-rows", type=int, default=0, help="tuning aid: config c3 with this many rows in every group")
     ap.add_argument("--moe-tokens", type=int, default=4096, help="tokens per rank of the Mega MoE run")
     ap.add_argument("--moe-experts", type=int, default=32, help="experts per rank of the Mega MoE run")
@@ -760,7 +830,8 @@ def main():
 
     if args.only == "mega_moe":
         moe = mega_moe_bench(device, dist.group.WORLD if world > 1 else None, rank, world, max(1, min(args.steps, 10)),
-                             args.warmup, tokens=args.moe_tokens, experts_per_rank=args.moe_experts)
+                             args.warmup, tokens=args.moe_tokens, experts_per_rank=args.moe_experts,
+                             trace_path=args.trace or None)
         if rank == 0:
             emit({"mega_moe": moe})
         if world > 1:

@@ -38,19 +38,24 @@ def needs_build() -> bool:
     return any(os.path.exists(d) and os.path.getmtime(d) > t for d in dependencies())
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
     """Compile every CUDA source for sm_100a (one nvcc per source, in parallel) and link one shared library; returns
-    its path."""
-    if not force and not needs_build():
+    its path.  trace=True builds a second library, lib/libdeepgemm_b200_trace.so, with -DDG_TRACE: the Mega MoE kernel
+    then records per-CTA time stamps and wait cycles into a buffer given through dg_debug_set_trace (select it with the
+    DEEPGEMM_B200_LIB environment variable; `bench.py --only mega_moe --trace <file>` summarises the stamps)."""
+    lib_path = os.path.join(LIB_DIR, "libdeepgemm_b200_trace.so") if trace else LIB_PATH
+    if not force and not trace and not needs_build():
         return LIB_PATH
     from concurrent.futures import ThreadPoolExecutor
     os.makedirs(LIB_DIR, exist_ok=True)
-    obj_dir = os.path.join(LIB_DIR, "obj")
+    obj_dir = os.path.join(LIB_DIR, "obj_trace" if trace else "obj")
     os.makedirs(obj_dir, exist_ok=True)
     nvcc = nvcc_path()
     flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
     if verbose:
         flags += ["-Xptxas", "-v"]
+    if trace:
+        flags += ["-DDG_TRACE"]
 
     def compile_one(src):
         obj = os.path.join(obj_dir, os.path.splitext(src)[0] + ".o")
@@ -64,12 +69,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
             raise RuntimeError(f"nvcc failed on {src}:\n" + res.stdout + res.stderr)
         if verbose:
             sys.stderr.write(res.stderr)
-    res = subprocess.run([nvcc, "-shared", "-o", LIB_PATH] + [obj for _, obj, _ in results],
+    res = subprocess.run([nvcc, "-shared", "-o", lib_path] + [obj for _, obj, _ in results],
                          capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("linking failed:\n" + res.stdout + res.stderr)
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv))

@@ -884,6 +884,7 @@ int dg_set_mega_moe_fused(int32_t enable) {
 }
 
 int dg_get_token_alignment_for_mega_moe(void) { return 128; }
+int dg_get_block_m_for_mega_moe(void) { return static_cast<int>(dg::kMoeTileRows); }
 
 int dg_get_mega_moe_num_sms(void) {
     int n = 0;

@@ -1,5 +1,5 @@
 // Mega MoE forward as ONE persistent kernel: dispatch (count, index scatter, count exchange, token pull over
-// NVLink peer loads), the two expert GEMMs (tcgen05 block-scaled UMMA, 2-CTA pairs, 240-token tiles) with the
+// NVLink peer loads), the two expert GEMMs (tcgen05 block-scaled UMMA, 2-CTA pairs, 256-token tiles) with the
 // SwiGLU / requantisation and combine-push epilogues, and the top-k reduction.
 //
 // Dataflow inside the launch: pull warps fill the expert-sorted pool in pool order and count rows per token
@@ -35,7 +35,6 @@ struct MoeFusedParams {
 };
 
 struct FusedCfg {
-    // Two accumulators of BN columns and the scale columns fit tensor memory without sharing columns
     static constexpr uint32_t BN = kMoeTileRows, R_STAGE = 128 * 128, C_STAGE = BN / 2 * 128, SFR_STAGE = 512, SFC_STAGE = 1024;
     static constexpr uint32_t STAGE_BYTES = R_STAGE + C_STAGE + SFR_STAGE + SFC_STAGE;
     static constexpr uint32_t PITCH = 272;
@@ -45,7 +44,10 @@ struct FusedCfg {
     static constexpr uint32_t CD_BYTES = (PREFIX_OFF + 512 * 4 + 1023) / 1024 * 1024;
     static constexpr uint32_t kStages = (232448 - 1024 - CD_BYTES - 1024) / STAGE_BYTES;
     static constexpr uint32_t kSmemBytes = 1024 + kStages * STAGE_BYTES + CD_BYTES + 1024;
-    static constexpr uint32_t kAccStride = BN, kSfrCol = 2 * BN, kSfcCol = kSfrCol + 4;
+    // Two accumulators of BN columns, then 4 + 8 scale columns; where that exceeds tensor memory the accumulators share
+    // kOverlap columns (stage 0's last, stage 1's first)
+    static constexpr uint32_t kOverlap = 2 * BN + 12 > 512 ? 16 : 0;
+    static constexpr uint32_t kAccStride = BN - kOverlap, kSfrCol = 2 * BN - kOverlap, kSfcCol = kSfrCol + 4;
     static constexpr uint32_t kTmemCols = 512;
 };
 static_assert(FusedCfg::kStages >= 4 && FusedCfg::kStages <= 10, "stage count");
@@ -133,7 +135,7 @@ DG_DEVICE bool fused_grid_barrier(uint32_t* ctrl, uint32_t num_ctas, volatile ui
 // number of threads.  Thread 0 issues, all threads sum (slot order, FP32) and store BF16.  The kernel's operand
 // stages are free by now (all roles have left their loops and the grid barrier has passed).
 #ifndef DG_REDUCE_PIECE
-#define DG_REDUCE_PIECE 2560
+#define DG_REDUCE_PIECE (FusedCfg::BN == 256 ? 3072 : 2560)
 #define DG_REDUCE_STAGES 4
 #endif
 constexpr uint32_t kReducePiece = DG_REDUCE_PIECE, kReduceStages = DG_REDUCE_STAGES, kReduceSlotBytes = kReducePiece * 2;
@@ -248,7 +250,11 @@ DG_DEVICE void fused_reduce_bulk(const MoeFusedParams& p, uint8_t* smem_gen, uin
     if (warp == 4) for (int i_ = 0; i_ < 8; ++i_) p.trace[(blockIdx.x * 20 + 18) * 8 + i_] = epi_cycles[i_]; } } while (0)
 #define DG_EPI_TIMED(slot_, stmt_) do { const long long t0_ = clock64(); stmt_; epi_cycles[slot_] += clock64() - t0_; } while (0)
 #define DG_FUSED_STAMP(slot_) do { if (p.trace != nullptr && lane == 0) { p.trace[(blockIdx.x * 20 + warp) * 8 + (slot_)] = global_timer_ns(); if (warp == 0) p.trace[(blockIdx.x * 20 + 19) * 8 + (slot_)] = clock64(); } } while (0)
+// Finer stamps of thread 0 of every CTA (row 17): 0 scatter done, 1 grid barrier 1 passed, 2 exchange done (CTA 0),
+// 3 layout seen, 4 grid barrier 2 passed, 5 cross-rank barrier 2 passed (CTA 0)
+#define DG_FUSED_STAMP0(slot_) do { if (p.trace != nullptr && threadIdx.x == 0) p.trace[(blockIdx.x * 20 + 17) * 8 + (slot_)] = global_timer_ns(); } while (0)
 #else
+#define DG_FUSED_STAMP0(slot_) do { } while (0)
 #define DG_FUSED_STAMP(slot_) do { } while (0)
 #define DG_FUSED_TIMED(slot_, stmt_) do { stmt_; } while (0)
 #define DG_FUSED_FLUSH() do { } while (0)
@@ -295,6 +301,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
         for (uint32_t i = 0; i < 2; ++i) {
             mbar_init(&bars->tmem_full[i], 1);
             mbar_init(&bars->tmem_empty[i], 2 * 4);
+            mbar_init(&bars->overlap[i], 2 * 4);
             mbar_init(&s_epi_bar[i][0], 4), mbar_init(&s_epi_bar[i][1], 4);
         }
         bars->abort = 0;
@@ -316,7 +323,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     const uint32_t call_new = call_old + 1;
     for (uint32_t i = blockIdx.x * kFusedThreads + threadIdx.x; i < p.a.num_tokens * L.topk; i += p.num_ctas * kFusedThreads)
         moe_scatter_pair(p.a, i);
+    DG_FUSED_STAMP0(0);
     bool ok = fused_grid_barrier(ctrl, p.num_ctas, abort_flag, p.a, 201);
+    DG_FUSED_STAMP0(1);
     // step 2 (CTA 0): publish counts, cross-rank barrier, pool layout, tile table, counters, layout_ready
     if (ok && blockIdx.x == 0) {
         MoeFusedHooks hooks;
@@ -324,6 +333,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
         hooks.l1_done = MoeFusedWork::l1_done(L), hooks.expert_tab = MoeFusedWork::expert_tab(L);
         // the operand stages are idle until the roles start: their first words serve the layout scan
         moe_exchange_body(p.a, threadIdx.x, kFusedThreads, &hooks, reinterpret_cast<uint32_t*>(smem_gen));
+        DG_FUSED_STAMP0(2);
     }
     if (ok) {
         if (threadIdx.x == 0)
@@ -333,6 +343,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
         if (threadIdx.x == 0) s_layout_ok = ok ? 1u : 0u;
         __syncthreads();
         ok = s_layout_ok != 0;
+        DG_FUSED_STAMP0(3);
     }
     const uint32_t num_tiles = ok ? ctrl[MoeCtrl::kNumTiles] : 0;
     const uint32_t* table = work + MoeFusedWork::tile_table(L);
@@ -418,6 +429,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
                 if (!fused_slot_to_tile(table, num_tiles, n1, n2, p.lag, slot, tc)) continue;
                 const uint32_t acc = acc_iter & 1, acc_phase = (acc_iter >> 1) & 1;
                 DG_FUSED_TIMED(5, ok = wait_barrier(&bars->tmem_empty[acc], acc_phase ^ 1, abort_flag, peer_abort, wp, kSiteMmaTmemEmpty, acc_iter, 0, acc));
+                if (Cfg::kOverlap > 0 && ok && acc_iter > 0) {
+                    // the tile before this one has been read out of the columns the two accumulators share
+                    const uint32_t prev = acc_iter - 1;
+                    DG_FUSED_TIMED(7, ok = wait_barrier(&bars->overlap[prev & 1], (prev >> 1) & 1, abort_flag, peer_abort, wp, kSiteMmaOverlap, acc_iter, 0, acc));
+                }
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * Cfg::kAccStride;
@@ -455,6 +471,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
         // buffer read).
         const uint32_t group = warp >= 13 ? 1u : 0u, q = warp % 4;
         const uint32_t tmem_empty_bar = map_to_cta(smem_u32(&bars->tmem_empty[0]), 0);
+        const uint32_t overlap_bar = map_to_cta(smem_u32(&bars->overlap[0]), 0);
         uint64_t* bar_written = &s_epi_bar[group][0];
         uint64_t* bar_read = &s_epi_bar[group][1];
         uint8_t* stage_gen = smem_gen + (smem_cd - smem_base) + group * 32 * Cfg::PITCH;
@@ -503,15 +520,19 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
             const uint32_t t_acc = tmem_base + acc * Cfg::kAccStride + ((q * 32) << 16);
             const uint32_t n0 = tc.n_blk * 256 + cta_rank * 128;
             const uint32_t num_chunks = (tc.rows + 31) / 32;
+            const bool reverse = Cfg::kOverlap > 0 && acc == 0;   // stage 0 shares its last columns, stage 1 its first: drain those first
 #pragma unroll 1
             for (uint32_t i = 0; i < num_chunks && ok; ++i) {
-                const uint32_t ch = i;
+                const uint32_t ch = reverse ? num_chunks - 1 - i : i;
                 uint32_t v[32];
                 DG_EPI_TIMED(1, tmem_ld_32x32b_x32(t_acc + ch * 32, v); tmem_ld_wait(););
-                if (i + 1 == num_chunks) {
+                if (i == 0 || i + 1 == num_chunks) {
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(tmem_empty_bar + acc * 8);
+                    if (lane == 0) {
+                        if (Cfg::kOverlap > 0 && i == 0) mbar_arrive_cluster(overlap_bar + acc * 8);
+                        if (i + 1 == num_chunks) mbar_arrive_cluster(tmem_empty_bar + acc * 8);
+                    }
                 }
                 // the staging buffer's previous chunk has been read by all four warps (the tile's first chunk
                 // already waited above)
@@ -557,6 +578,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     DG_FUSED_STAMP(2);
     // ---------------------------------------------------------------- combine: everyone has pushed, then reduce
     bool ok2 = fused_grid_barrier(ctrl, p.num_ctas, abort_flag, p.a, 205);
+    DG_FUSED_STAMP0(4);
     if (ok2 && blockIdx.x == 0) {
         __shared__ uint32_t s_bar_ok;
         if (threadIdx.x == 0) s_bar_ok = 1;
@@ -564,6 +586,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
         if (threadIdx.x < L.ranks)
             if (!moe_cross_rank_barrier(p.a, 1, 2 * call_new, threadIdx.x)) s_bar_ok = 0;
         __syncthreads();
+        DG_FUSED_STAMP0(5);
         if (threadIdx.x == 0 && s_bar_ok)
             asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ctrl + MoeCtrl::kCombineReady), "r"(call_new) : "memory");
     }

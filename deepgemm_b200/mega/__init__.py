@@ -33,7 +33,7 @@ def get_token_alignment_for_mega_moe() -> int:
 def get_block_m_for_mega_moe(num_ranks: int, num_experts: int, num_max_tokens_per_rank: int, num_tokens: int,
                              num_topk: int, mma_type: str = "fp8xfp4") -> int:
     """Token rows per expert tile; tiles shrink at run time for short experts (csrc/apis/mega_moe.hpp:38-47)."""
-    return 256
+    return int(_lib.lib().dg_get_block_m_for_mega_moe())
 
 
 _ACTIVATIONS = {"swiglu": 0, "geglu": 1, "situ": 2}

@@ -161,7 +161,7 @@ typedef struct dg_moe_config {
  * l2_acts_sf int32 [Q, I/128] with strides (1, Q); token_src_metadata int32 [P, 3];
  * combine bf16 [K (+ 1 with shared experts), T, H].  P = pool_rows, Q = sf_rows >= P.  The scale words of l1_acts_sf
  * and l2_acts_sf sit in blocks of 128 rows in the order tcgen05.cp consumes (row r of a block at (r % 32) * 4 + r / 32);
- * the single-kernel forward gives every 240-token tile 256 scale rows of its own (tile j: rows [256 j, 256 j + 256)),
+ * the single-kernel forward gives every token tile (dg_get_block_m_for_mega_moe rows) 256 scale rows of its own (tile j: rows [256 j, 256 j + 256)),
  * the kernel-per-phase forward uses the first P rows, pool row for pool row.
  * With shared experts (offsets 0 otherwise): shared_l1_acts_sf int32 [T', H/128] with strides (1, T'), T' = T rounded
  * up to 128 - the scales of x once more, in that same row order, filled by the caller along with x_sf;
@@ -180,6 +180,10 @@ int dg_mega_moe_buffer_layout(const dg_moe_config* cfg, dg_moe_layout* out);
 
 /* Row granularity of num_max_tokens_per_rank (csrc/apis/mega_moe.hpp:34-36). */
 int dg_get_token_alignment_for_mega_moe(void);
+
+/* Token rows per expert tile of the single-kernel forward; an expert's last tile shrinks to its rows rounded up to 16
+ * (get_block_m_for_mega_moe, csrc/apis/mega_moe.hpp:38-47, which chooses per configuration; here it is one constant). */
+int dg_get_block_m_for_mega_moe(void);
 
 /* SMs the Mega MoE grid takes: dg_get_num_sms() (capped at the device's count) minus the environment variable
  * DG_MEGA_MOE_SM_HEADROOM rounded up to an even number; -1 with dg_last_error() set when the headroom is negative,

@@ -141,17 +141,19 @@ def test_mega_moe_buffer_layout_and_checks():
 
 
 def test_mega_moe_scale_rows_cover_every_tile():
-    """The single-kernel forward gives every 240-token tile 256 scale rows: whatever the split of the pool over the
-    local experts, the tiles' scale rows fit `sf_rows`."""
+    """The single-kernel forward gives every token tile 256 scale rows: whatever the split of the pool over the local
+    experts, the tiles' scale rows fit `sf_rows`."""
     lay = _lib.MoeLayout()
+    bm = dg.get_block_m_for_mega_moe(8, 256, 4096, 4096, 8)
+    assert bm % 16 == 0 and 16 <= bm <= 256
     for ranks, experts, tokens, topk in ((8, 256, 4096, 8), (1, 48, 8192, 6), (2, 8, 128, 4), (8, 64, 128, 8)):
         cfg = _lib.MoeConfig(ranks, experts, tokens, topk, 1024, 512, 0, 0)
         assert _lib.lib().dg_mega_moe_buffer_layout(ctypes.byref(cfg), ctypes.byref(lay)) == 0
         local, rows = experts // ranks, min(ranks * tokens * topk, lay.pool_rows)
         assert lay.sf_rows >= lay.pool_rows and lay.sf_rows % 256 == 0
         for split in ([rows // local] * local, [1] * (local - 1) + [rows - (local - 1)],
-                      [241] * min(local, rows // 241) + [0] * (local - min(local, rows // 241))):
-            tiles = sum(-(-r // 240) for r in split)
+                      [bm + 1] * min(local, rows // (bm + 1)) + [0] * (local - min(local, rows // (bm + 1)))):
+            tiles = sum(-(-r // bm) for r in split)
             assert tiles * 256 <= lay.sf_rows, (ranks, experts, split[:3])
 
 
