@@ -451,7 +451,8 @@ def moe_trace_summary(t, num_ctas, ms):
     roles begin, roles end, reduce begin, end; 5-7 = cycles spent in that warp's waits."""
     import numpy as np
     t = t.reshape(-1, 20, 8).astype(np.float64)[:num_ctas]
-    t0 = t[:, :, 0][t[:, :, 0] > 0].min()
+    starts = t[:, :17, 0]          # rows 17-19 hold other things than the warps' stamps
+    t0 = starts[starts > 0].min()
     out = ["event-timed step: %.1f us; %d CTAs; times in us after the first CTA's start (min / median / max over CTAs)" % (ms * 1e3, num_ctas)]
     names = ["kernel start", "roles begin (scatter, exchange, layout done)", "roles end", "reduce begin (barriers passed)", "end"]
     for w, role in ((0, "weight-copy warp"), (1, "UMMA warp"), (4, "epilogue warp 4"), (2, "pull warp 2")):
