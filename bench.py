@@ -380,15 +380,39 @@ def config_fp4(device, steps, warmup, flush):
                 calc_diff=float(calc_diff(np_of(d[:rows]), ref)), tolerance=5e-3, parity_sample=f"rows 0..{rows - 1}")
 
 
+def config_bf16(device, steps, warmup, flush):
+    """BF16 x BF16 (kind::f16, no scale factors) 4096 x 4096 x 7168 and the grouped form 8 x 8192 x 4096 x 7168's first
+    expert shape 8192 x 4096 x 7168; parity: 1024 rows against a float64 matmul of the same BF16 values.  The fraction is
+    against the measured cuBLAS BF16 figure itself."""
+    import torch
+    import deepgemm_b200 as dg
+    from oracle.quant import calc_diff
+    torch.manual_seed(6)
+    peak = measured_peaks()["bf16"]
+    out = {}
+    for m, n, k in ((4096, 4096, 7168), (8192, 4096, 7168)):
+        a = torch.randn((m, k), device=device, dtype=torch.bfloat16)
+        b = torch.randn((n, k), device=device, dtype=torch.bfloat16)
+        d = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+        ms = median(time_steps(lambda: dg.bf16_gemm_nt(a, b, d), steps, warmup, flush))
+        rows = 1024
+        ref = np_of(a[:rows]).astype("float64") @ np_of(b).astype("float64").T
+        tf = 2.0 * m * n * k / ms / 1e9
+        out[f"{m}x{n}x{k}"] = dict(ms=ms, tflops=tf, frac_of_measured_bf16=tf / peak, frac_of_nominal_2250=tf / 2250.0,
+                                   calc_diff=float(calc_diff(np_of(d[:rows]), ref)), tolerance=1e-5,
+                                   parity_sample=f"rows 0..{rows - 1}")
+    return out
+
+
 MASKED_ROWS_OVERRIDE = 0
 
 CONFIGS = {"c1": ("c1_dense_fp8_4096x4096x7168", config_c1), "c4": ("c4_fp8xfp4_8192x7168x2048", config_c4),
            "c3": ("c3_masked_16x(256 of 1024)x4096x7168", config_c3),
            "kg": ("k_grouped_tn_4x4096x7168x8192_fp32_accumulate", config_k_grouped),
-           "fp4": ("fp4xfp4_mxf4_8192x7168x4096", config_fp4)}
+           "fp4": ("fp4xfp4_mxf4_8192x7168x4096", config_fp4), "bf16": ("bf16_dense", config_bf16)}
 
 
-def other_configs(device, steps, warmup, which=("c1", "c4", "c3", "kg", "fp4", "cast")):
+def other_configs(device, steps, warmup, which=("c1", "c4", "c3", "kg", "fp4", "bf16", "cast")):
     """Kernel-only figures of the other single-GPU configurations, each with its parity sample."""
     import gc
     import torch
@@ -402,7 +426,7 @@ def other_configs(device, steps, warmup, which=("c1", "c4", "c3", "kg", "fp4", "
                 continue
             name, fn = CONFIGS[key]
             rec = fn(device, steps, warmup, flush)
-            if "tflops" in rec and key != "fp4":
+            if "tflops" in rec and key not in ("fp4", "bf16"):
                 rec["frac_of_2x_measured_bf16"] = rec["tflops"] / peak
                 rec["frac_of_nominal_4500"] = rec["tflops"] / NOMINAL_FP8_TFLOPS
             out[name] = rec

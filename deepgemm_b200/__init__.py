@@ -24,6 +24,10 @@ from .ops import (  # noqa: F401
     m_grouped_fp8_fp4_gemm_nt_masked, k_grouped_fp8_gemm_tn_contiguous, k_grouped_fp4_gemm_nt_contiguous,
 )
 from .einsum import fp8_einsum  # noqa: F401
+from .bf16 import (  # noqa: F401
+    bf16_gemm_nt, bf16_gemm_nn, bf16_gemm_tn, bf16_gemm_tt, m_grouped_bf16_gemm_nt_contiguous,
+    m_grouped_bf16_gemm_nn_contiguous, m_grouped_bf16_gemm_nt_masked, k_grouped_bf16_gemm_tn_contiguous,
+)
 
 from . import mega  # noqa: F401,E402
 from . import cast  # noqa: F401,E402

@@ -14,7 +14,8 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_DIR = os.path.join(PKG_DIR, "lib")
 LIB_PATH = os.environ.get("DEEPGEMM_B200_LIB") or os.path.join(LIB_DIR, "libdeepgemm_b200.so")
-SOURCES = ["lib.cu", "gemm_inst_plain.cu", "gemm_inst_moe.cu", "gemm_inst_mxf4.cu", "gemm_inst_epi.cu"]
+SOURCES = ["lib.cu", "gemm_inst_plain.cu", "gemm_inst_moe.cu", "gemm_inst_mxf4.cu", "gemm_inst_epi.cu",
+           "gemm_inst_bf16.cu"]
 PUBLIC_HEADER = os.path.join(PKG_DIR, "..", "include", "deepgemm_b200.h")
 
 

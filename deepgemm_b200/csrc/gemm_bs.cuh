@@ -321,14 +321,18 @@ struct TileWalker {
     }
 };
 
-template <int kCtas_, int BN_, bool kSwap_, bool kCdF32_, int kEpi_ = 0, bool kMxf4_ = false>
+// kKind_: which tcgen05.mma kind the operands take
+enum : int { kKindMxf8f6f4 = 0, kKindMxf4 = 1, kKindBf16 = 2 };
+template <int kCtas_, int BN_, bool kSwap_, bool kCdF32_, int kEpi_ = 0, int kKind_ = kKindMxf8f6f4>
 struct GemmConfig {
     static constexpr int kEpi = kEpi_;   // EpilogueKind
     static constexpr bool kMoeEpi = kEpi_ == kEpiMoeL1 || kEpi_ == kEpiMoeL2;
     static_assert(!kMoeEpi || kSwap_, "the fused Mega MoE epilogues work on D^T tiles");
     static_assert(!(kEpi_ == kEpiStochastic || kEpi_ == kEpiFp8Cast) || (!kSwap_ && !kCdF32_),
                   "the value epilogues work on D tiles with 16-bit or 8-bit output");
-    static constexpr bool kMxf4 = kMxf4_;   // both operands packed E2M1: kind::mxf4, 256 K elements per stage
+    static constexpr bool kMxf4 = kKind_ == kKindMxf4;   // both operands packed E2M1: kind::mxf4, 256 K elements per stage
+    static constexpr bool kBf16 = kKind_ == kKindBf16;   // BF16 operands without scale factors: kind::f16, 64 K elements per stage
+    static_assert(!(kBf16 && (kEpi_ == kEpiMoeL1 || kEpi_ == kEpiMoeL2 || kEpi_ == kEpiFp8Cast)), "BF16 operands: store and stochastic epilogues");
     static constexpr int kCtas = kCtas_;
     static constexpr int BN = BN_;
     static constexpr bool kSwap = kSwap_;
@@ -338,8 +342,8 @@ struct GemmConfig {
 
     static constexpr uint32_t kThreads = 288;   // warps 0-3: R copies, UMMA, scale transposer, scale copies; 4-7: epilogue; 8: C copies
     static constexpr uint32_t BLOCK_K = 128;          // bytes of K per row and stage
-    static constexpr uint32_t BLOCK_K_ELEMS = kMxf4 ? 256 : 128;
-    static constexpr uint32_t SF_WORDS = kMxf4 ? 2 : 1;   // packed scale words (128 K elements each) per row and stage
+    static constexpr uint32_t BLOCK_K_ELEMS = kMxf4 ? 256 : kBf16 ? 64 : 128;
+    static constexpr uint32_t SF_WORDS = kMxf4 ? 2 : kBf16 ? 0 : 1;   // packed scale words (128 K elements each) per row and stage
     static constexpr uint32_t R_ROWS = 128;
     static constexpr uint32_t C_ROWS_PER_CTA = BN / kCtas;
     static constexpr uint32_t R_STAGE = R_ROWS * BLOCK_K;
@@ -670,7 +674,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
         prefetch_tmap(&p.tm_sfc);
         prefetch_tmap(&p.tm_d);
         for (uint32_t i = 0; i < kStages; ++i) {
-            mbar_init(&bars->full[i], kCtas * 3);   // per CTA: R producer, C producer, transposer
+            mbar_init(&bars->full[i], kCtas * (Cfg::kBf16 ? 2 : 3));   // per CTA: R producer, C producer, scale transposer
             mbar_init(&bars->empty[i], 1);          // UMMA commit
             mbar_init(&bars->sf_full[i], 1);        // producer (SF copies land here)
         }
@@ -743,6 +747,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
         // whole warp runs the loop (uniform control flow keeps addresses and coordinates in uniform registers); one
         // elected lane issues the copies.
         const bool sf_role = warp == 3, r_role = warp == 0;
+        if (Cfg::kBf16 && sf_role) ok = false;   // no scale factors: this warp has nothing to fetch
         const uint32_t full_bar0 = leader_addr(&bars->full[0]);
         const uint32_t stage_tx_bytes = p.r.tx_bytes + p.c.tx_bytes;
         const uint32_t r_boxes = p.r.num_boxes, r_box_bytes = p.r.box_bytes, r_box_mn = p.r.box_mn;
@@ -762,14 +767,17 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                 // Data: (K, row inside the group, group) through 3-D tensor maps; the K coordinate counts the map's
                 // elements (bytes for E4M3 and for packed E2M1 under kind::mxf4)
                 const uint32_t a_mn = tc.row0, b_mn = tc.n_blk * Cfg::UNIT_N;
+                // (BF16 operands go through byte maps: the contiguous axis counts two bytes per element)
                 const uint32_t k0 = Cfg::kMxf4 ? tc.k_start >> 1 : tc.k_start;
+                const uint32_t r_esz = (Cfg::kBf16 && r_mn_major) ? 2u : 1u, c_esz = (Cfg::kBf16 && c_mn_major) ? 2u : 1u;
+                const uint32_t r_kstep = (Cfg::kBf16 && r_mn_major) ? 64u : 128u, c_kstep = (Cfg::kBf16 && c_mn_major) ? 64u : 128u;
                 const int32_t r_batch = r_batched ? static_cast<int32_t>(tc.group) : 0;
                 const int32_t c_batch = c_batched ? static_cast<int32_t>(tc.group) : 0;
                 const uint32_t sfa_k = tc.sfk_base + tc.group * sfg_a, sfb_k = tc.sfk_base + tc.group * sfg_b;
                 // SF rows are addressed inside the group (the group offset is on the packed-K axis)
                 const uint32_t sfa_mn = tc.row0, sfb_mn = tc.n_blk * Cfg::UNIT_N;
                 uint32_t r_mn = kSwap ? b_mn : a_mn, c_mn = kSwap ? a_mn : b_mn;
-                const uint32_t r_k = k0, c_k = k0;
+                const uint32_t r_k = (Cfg::kBf16 && !r_mn_major) ? k0 * 2 : k0, c_k = (Cfg::kBf16 && !c_mn_major) ? k0 * 2 : k0;
                 uint32_t sfr_mn = kSwap ? sfb_mn : sfa_mn;
                 const uint32_t sfc_mn = kSwap ? sfa_mn : sfb_mn;
                 const uint32_t sfr_k = kSwap ? sfb_k : sfa_k, sfc_k = kSwap ? sfa_k : sfb_k;
@@ -816,10 +824,10 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                         // Operand tiles land on the leader's barrier (both CTAs of a pair feed one UMMA)
                         const uint32_t full_bar = full_bar0 + stage * 8;
                         mbar_arrive_expect_tx_cluster(full_bar, p.r.tx_bytes);
-                        const uint32_t kr = r_k + kb * 128;
+                        const uint32_t kr = r_k + kb * r_kstep;
                         for (uint32_t b = 0; b < r_boxes; ++b) {
                             const uint32_t dst = smem_r + stage * Cfg::R_STAGE + b * r_box_bytes;
-                            const uint32_t mn = r_mn + b * r_box_mn;
+                            const uint32_t mn = (r_mn + b * r_box_mn) * r_esz;
                             if (r_mn_major) tma_load_3d<kPair>(dst, &p.tm_r, full_bar, mn, kr, r_batch);
                             else            tma_load_3d<kPair>(dst, &p.tm_r, full_bar, kr, mn, r_batch);
                         }
@@ -827,10 +835,10 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                     } else if (elect_one()) {
                         const uint32_t full_bar = full_bar0 + stage * 8;
                         mbar_arrive_expect_tx_cluster(full_bar, tile_tx_bytes - p.r.tx_bytes);
-                        const uint32_t kc = c_k + kb * 128;
+                        const uint32_t kc = c_k + kb * c_kstep;
                         for (uint32_t b = 0; b < c_boxes; ++b) {
                             const uint32_t dst = smem_c + stage * Cfg::C_STAGE + b * c_box_bytes;
-                            const uint32_t mn = c_mn + b * c_box_mn;
+                            const uint32_t mn = (c_mn + b * c_box_mn) * c_esz;
                             if (c_mn_major) tma_load_3d<kPair>(dst, &p.tm_c, full_bar, mn, kc, c_batch);
                             else            tma_load_3d<kPair>(dst, tm_c_tile, full_bar, kc, mn, c_batch);
                         }
@@ -846,6 +854,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
         if (is_leader) {
             const uint32_t idesc_base = Cfg::kMxf4
                 ? make_idesc_mxf4(128 * kCtas, BN)
+                : Cfg::kBf16 ? make_idesc_bf16(p.r.mn_major != 0, p.c.mn_major != 0, 128 * kCtas, BN)
                 : make_idesc_mxf8f6f4(p.r.fmt, p.c.fmt, p.r.mn_major != 0, p.c.mn_major != 0, 128 * kCtas, BN);
             const uint64_t sf_desc_hi = make_smem_desc(0, 0, 128, kSwizzleNone);
             // Operand descriptors: constant high word; the low word carries (address >> 4) and the LBO field
@@ -891,6 +900,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                             // Fresh scale factors: shared memory (already in 32x4 order) -> TMEM
                             // (kind::mxf4: two scale words per row; word w of 128 rows i sits at
                             // (w * rows + i * 128) * 4 in the stage and goes to columns w * rows / 32 + i * 4)
+                            if constexpr (!Cfg::kBf16) {
                             if ((kb & sf_mask_r) == 0) {
 #pragma unroll
                                 for (uint32_t w = 0; w < Cfg::SF_WORDS; ++w) {
@@ -909,6 +919,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                                     }
                                 }
                             }
+                            }
                             const uint32_t r_lo = r_lo0 + stage * (Cfg::R_STAGE >> 4);
                             const uint32_t c_lo = c_lo0 + stage * (Cfg::C_STAGE >> 4);
                             const uint32_t id128 = kb & 3;
@@ -919,7 +930,9 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                             for (uint32_t ks = 0; ks < 4; ++ks) {
                                 const uint64_t r_desc = (static_cast<uint64_t>(r_hi) << 32) | (r_lo + ks * r_kstep);
                                 const uint64_t c_desc = (static_cast<uint64_t>(c_hi) << 32) | (c_lo + ks * c_kstep);
-                                if constexpr (Cfg::kMxf4) {
+                                if constexpr (Cfg::kBf16) {
+                                    umma_bf16<kCtas>(d_tmem, r_desc, c_desc, idesc_tile, (kb | ks) != 0);
+                                } else if constexpr (Cfg::kMxf4) {
                                     // UMMA K = 64: scale bytes (ks % 2) * 2 and + 1 of word ks / 2, on both sides
                                     const uint32_t id = (ks & 1u) * 2u;
                                     umma_mxf4<kCtas>(d_tmem, r_desc, c_desc, idesc_tile | (id << 4) | (id << 29),
@@ -943,6 +956,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
         // ============================================================ scale-factor transposer
         // tcgen05.cp 32x128b.warpx4 wants, per 128 rows, row i's word at position (i % 32) * 4 + i / 32.
         const uint32_t full_bar = leader_addr(&bars->full[0]);
+        if constexpr (!Cfg::kBf16) {   // BF16 operands carry no scale factors
         for (uint32_t iter = 0; ok; ++iter) {
             const uint32_t slot = slot_first + iter * slot_stride;
             if (slot >= slot_end) break;
@@ -977,6 +991,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                     if (lane == 0) mbar_arrive_cluster(full_bar + stage * 8);
                 }
             }
+        }
         }
     } else if (warp >= 4) {
         // ============================================================ epilogue

@@ -5,14 +5,14 @@
 namespace dg {
 
 int dispatch_gemm_epi(const GemmLaunch& l) {
-    DG_GEMM_CASE(1, 128, false, false, kEpiStochastic, false)
-    DG_GEMM_CASE(1, 256, false, false, kEpiStochastic, false)
-    DG_GEMM_CASE(2, 128, false, false, kEpiStochastic, false)
-    DG_GEMM_CASE(2, 256, false, false, kEpiStochastic, false)
-    DG_GEMM_CASE(1, 128, false, false, kEpiFp8Cast, false)
-    DG_GEMM_CASE(1, 256, false, false, kEpiFp8Cast, false)
-    DG_GEMM_CASE(2, 128, false, false, kEpiFp8Cast, false)
-    DG_GEMM_CASE(2, 256, false, false, kEpiFp8Cast, false)
+    DG_GEMM_CASE(1, 128, false, false, kEpiStochastic, kKindMxf8f6f4)
+    DG_GEMM_CASE(1, 256, false, false, kEpiStochastic, kKindMxf8f6f4)
+    DG_GEMM_CASE(2, 128, false, false, kEpiStochastic, kKindMxf8f6f4)
+    DG_GEMM_CASE(2, 256, false, false, kEpiStochastic, kKindMxf8f6f4)
+    DG_GEMM_CASE(1, 128, false, false, kEpiFp8Cast, kKindMxf8f6f4)
+    DG_GEMM_CASE(1, 256, false, false, kEpiFp8Cast, kKindMxf8f6f4)
+    DG_GEMM_CASE(2, 128, false, false, kEpiFp8Cast, kKindMxf8f6f4)
+    DG_GEMM_CASE(2, 256, false, false, kEpiFp8Cast, kKindMxf8f6f4)
     return kLaunchNoKernel;
 }
 

@@ -4,14 +4,14 @@
 namespace dg {
 
 int dispatch_gemm_moe(const GemmLaunch& l) {
-    DG_GEMM_CASE(2, 256, true, false, 1, false)
-    DG_GEMM_CASE(2, 128, true, false, 1, false)
-    DG_GEMM_CASE(1, 256, true, false, 1, false)
-    DG_GEMM_CASE(1, 128, true, false, 1, false)
-    DG_GEMM_CASE(2, 256, true, false, 2, false)
-    DG_GEMM_CASE(2, 128, true, false, 2, false)
-    DG_GEMM_CASE(1, 256, true, false, 2, false)
-    DG_GEMM_CASE(1, 128, true, false, 2, false)
+    DG_GEMM_CASE(2, 256, true, false, 1, kKindMxf8f6f4)
+    DG_GEMM_CASE(2, 128, true, false, 1, kKindMxf8f6f4)
+    DG_GEMM_CASE(1, 256, true, false, 1, kKindMxf8f6f4)
+    DG_GEMM_CASE(1, 128, true, false, 1, kKindMxf8f6f4)
+    DG_GEMM_CASE(2, 256, true, false, 2, kKindMxf8f6f4)
+    DG_GEMM_CASE(2, 128, true, false, 2, kKindMxf8f6f4)
+    DG_GEMM_CASE(1, 256, true, false, 2, kKindMxf8f6f4)
+    DG_GEMM_CASE(1, 128, true, false, 2, kKindMxf8f6f4)
     return kLaunchNoKernel;
 }
 

@@ -4,20 +4,20 @@
 namespace dg {
 
 int dispatch_gemm_mxf4(const GemmLaunch& l) {
-    DG_GEMM_CASE(1, 128, false, false, 0, true)
-    DG_GEMM_CASE(1, 256, false, false, 0, true)
-    DG_GEMM_CASE(2, 128, false, false, 0, true)
-    DG_GEMM_CASE(2, 256, false, false, 0, true)
-    DG_GEMM_CASE(1, 128, false, true, 0, true)
-    DG_GEMM_CASE(1, 256, false, true, 0, true)
-    DG_GEMM_CASE(2, 128, false, true, 0, true)
-    DG_GEMM_CASE(2, 256, false, true, 0, true)
-    DG_GEMM_CASE(1, 64, true, false, 0, true)
-    DG_GEMM_CASE(1, 128, true, false, 0, true)
-    DG_GEMM_CASE(2, 64, true, false, 0, true)
-    DG_GEMM_CASE(2, 128, true, false, 0, true)
-    DG_GEMM_CASE(2, 256, true, false, 0, true)
-    DG_GEMM_CASE(1, 256, true, false, 0, true)
+    DG_GEMM_CASE(1, 128, false, false, 0, kKindMxf4)
+    DG_GEMM_CASE(1, 256, false, false, 0, kKindMxf4)
+    DG_GEMM_CASE(2, 128, false, false, 0, kKindMxf4)
+    DG_GEMM_CASE(2, 256, false, false, 0, kKindMxf4)
+    DG_GEMM_CASE(1, 128, false, true, 0, kKindMxf4)
+    DG_GEMM_CASE(1, 256, false, true, 0, kKindMxf4)
+    DG_GEMM_CASE(2, 128, false, true, 0, kKindMxf4)
+    DG_GEMM_CASE(2, 256, false, true, 0, kKindMxf4)
+    DG_GEMM_CASE(1, 64, true, false, 0, kKindMxf4)
+    DG_GEMM_CASE(1, 128, true, false, 0, kKindMxf4)
+    DG_GEMM_CASE(2, 64, true, false, 0, kKindMxf4)
+    DG_GEMM_CASE(2, 128, true, false, 0, kKindMxf4)
+    DG_GEMM_CASE(2, 256, true, false, 0, kKindMxf4)
+    DG_GEMM_CASE(1, 256, true, false, 0, kKindMxf4)
     return kLaunchNoKernel;
 }
 

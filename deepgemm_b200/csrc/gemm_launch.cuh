@@ -3,6 +3,7 @@
 //   gemm_inst_plain.cu  kind::mxf8f6f4, store / accumulate epilogue
 //   gemm_inst_moe.cu    kind::mxf8f6f4, the two fused Mega MoE epilogues
 //   gemm_inst_mxf4.cu   kind::mxf4 (both operands packed E2M1)
+//   gemm_inst_bf16.cu   kind::f16 (BF16 operands without scale factors)
 //   gemm_inst_epi.cu    the value epilogues (stochastic rounding, FP8 cast with clamp)
 #pragma once
 
@@ -19,7 +20,8 @@ struct GemmLaunch {
     int pdl;          // launch with programmatic stream serialisation
     // which instantiation
     int ctas, bn, epi;
-    bool swap, f32, mxf4;
+    bool swap, f32;
+    int kind;         // kKindMxf8f6f4, kKindMxf4, kKindBf16
 };
 
 enum : int { kLaunchNoKernel = -1 };
@@ -28,6 +30,7 @@ enum : int { kLaunchNoKernel = -1 };
 int dispatch_gemm_plain(const GemmLaunch& l);
 int dispatch_gemm_moe(const GemmLaunch& l);
 int dispatch_gemm_mxf4(const GemmLaunch& l);
+int dispatch_gemm_bf16(const GemmLaunch& l);
 int dispatch_gemm_epi(const GemmLaunch& l);
 
 template <class Cfg>
@@ -57,8 +60,8 @@ int launch_gemm(const GemmLaunch& l) {
     return static_cast<int>(cudaLaunchKernelEx(&cfg, gemm_bs_kernel<Cfg>, l.p));
 }
 
-#define DG_GEMM_CASE(CT, BNV, SW, F32, EPI, MX)                                                                \
-    if (l.ctas == CT && l.bn == BNV && l.swap == SW && l.f32 == F32 && l.epi == EPI && l.mxf4 == MX)           \
-        return launch_gemm<GemmConfig<CT, BNV, SW, F32, EPI, MX>>(l);
+#define DG_GEMM_CASE(CT, BNV, SW, F32, EPI, KIND)                                                              \
+    if (l.ctas == CT && l.bn == BNV && l.swap == SW && l.f32 == F32 && l.epi == EPI && l.kind == int(KIND))    \
+        return launch_gemm<GemmConfig<CT, BNV, SW, F32, EPI, int(KIND)>>(l);
 
 }  // namespace dg

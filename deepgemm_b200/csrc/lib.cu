@@ -167,6 +167,7 @@ int plan_operand(const dg_gemm_args& a, const dg_operand& op, bool is_a, uint32_
                  bool mxf4, OperandPlan* out, uint32_t sf_mn = 0) {
     const uint32_t mn = is_a ? a.m : a.n;
     const bool fp4 = op.dtype == DG_E2M1_PACKED;
+    const bool bf16 = op.dtype == DG_BF16;   // moved as bytes: two per element on the contiguous axis
     const bool k_grouped = a.gemm_type == DG_GEMM_K_GROUPED || a.gemm_type == DG_GEMM_K_GROUPED_PSUM;
     // Which operands carry a group axis
     uint32_t groups = 1;
@@ -185,7 +186,7 @@ int plan_operand(const dg_gemm_args& a, const dg_operand& op, bool is_a, uint32_
         // K contiguous.  Packed E2M1 is seen as bytes under kind::mxf4 (two codes per byte in shared memory too) and as
         // 4-bit elements that TMA spreads to one per byte otherwise (kind::mxf8f6f4 reads 8-bit containers).
         const bool unpack = fp4 && !mxf4;
-        const uint64_t k_extent = mxf4 ? static_cast<uint64_t>(a.k) / 2 : static_cast<uint64_t>(a.k);
+        const uint64_t k_extent = mxf4 ? static_cast<uint64_t>(a.k) / 2 : bf16 ? static_cast<uint64_t>(a.k) * 2 : static_cast<uint64_t>(a.k);
         const uint64_t batch_stride = op.batch_stride > 0 ? static_cast<uint64_t>(op.batch_stride)
                                                           : static_cast<uint64_t>(op.ld) * mn;
         const uint64_t dims[3] = {k_extent, static_cast<uint64_t>(mn), groups};
@@ -200,24 +201,28 @@ int plan_operand(const dg_gemm_args& a, const dg_operand& op, bool is_a, uint32_
         q.tx_bytes = box_rows * 128 / (unpack ? 2 : 1);
         q.desc_lbo = 0, q.desc_sbo = 1024, q.desc_kstep = 32;
     } else {
-        // MN contiguous (E4M3 only): rows of the map are K rows; K-grouped layouts stack all groups' K rows on that axis
+        // MN contiguous (E4M3, BF16): rows of the map are K rows; K-grouped layouts stack all groups' K rows on that axis.
+        // A stage holds 128 B of K per row: 128 K rows of E4M3, 64 of BF16; one box is one 128-byte-wide column of
+        // swizzle atoms (128 MN elements of E4M3, 64 of BF16)
         if (fp4) return fail(DG_ERR_INVALID, "Assertion failed: packed FP4 operands are K-major (%s)", name);
         if (box_rows % 128 != 0)
             return fail(DG_ERR_INVALID, "Assertion failed: MN-major %s needs a tile of whole 128-row atoms", name);
+        const uint32_t esz = bf16 ? 2 : 1, k_rows = 128 / esz, box_mn = 128 / esz;
         const uint64_t batch_stride = op.batch_stride > 0 ? static_cast<uint64_t>(op.batch_stride)
                                                           : static_cast<uint64_t>(op.ld) * a.k;
-        const uint64_t dims[3] = {static_cast<uint64_t>(mn), static_cast<uint64_t>(a.k), groups};
+        const uint64_t dims[3] = {static_cast<uint64_t>(mn) * esz, static_cast<uint64_t>(a.k), groups};
         const uint64_t strides[2] = {static_cast<uint64_t>(op.ld), batch_stride};
-        const uint32_t box[3] = {128, 128, 1};
+        const uint32_t box[3] = {128, k_rows, 1};
         rc = encode_tmap(&out->tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, op.data, dims, strides, box,
                          CU_TENSOR_MAP_SWIZZLE_128B, name);
         if (rc != DG_OK) return rc;
-        q.num_boxes = box_rows / 128;
-        q.box_bytes = 128 * 128;
-        q.box_mn = 128;
+        q.num_boxes = box_rows / box_mn;
+        q.box_bytes = 128 * k_rows;
+        q.box_mn = box_mn;
         q.tx_bytes = box_rows * 128;
-        q.desc_lbo = 128 * 128, q.desc_sbo = 1024, q.desc_kstep = 32 * 128;
+        q.desc_lbo = 128 * k_rows, q.desc_sbo = 1024, q.desc_kstep = (32 / esz) * 128;
     }
+    if (bf16) return DG_OK;   // no scale factors
     // Scale factors: int32 [groups * packed_k, mn] seen with MN innermost
     uint64_t packed_k;
     if (k_grouped) {
@@ -498,14 +503,22 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
     DG_REQUIRE(a.m >= 0 && a.n >= 0 && a.k >= 0, "shape");
     if (a.m == 0 || a.n == 0) return DG_OK;
     DG_REQUIRE(a.k > 0, "k == 0 is handled by the caller");
-    DG_REQUIRE(a.a.data && a.b.data && a.a.sf && a.b.sf && (a.d || moe_epi != 0), "null tensor");
-    DG_REQUIRE(a.a.dtype == DG_E4M3 || a.a.dtype == DG_E2M1_PACKED, "a dtype");
-    DG_REQUIRE(a.b.dtype == DG_E4M3 || a.b.dtype == DG_E2M1_PACKED, "b dtype");
+    // BF16 operands (both, without scale factors) run the same kernel on kind::f16
+    const bool bf16 = a.a.dtype == DG_BF16 || a.b.dtype == DG_BF16;
+    DG_REQUIRE(!bf16 || (a.a.dtype == DG_BF16 && a.b.dtype == DG_BF16), "a and b are both BF16");
+    DG_REQUIRE(a.a.data && a.b.data && (bf16 || (a.a.sf && a.b.sf)) && (a.d || moe_epi != 0), "null tensor");
+    DG_REQUIRE(bf16 || a.a.dtype == DG_E4M3 || a.a.dtype == DG_E2M1_PACKED, "a dtype");
+    DG_REQUIRE(bf16 || a.b.dtype == DG_E4M3 || a.b.dtype == DG_E2M1_PACKED, "b dtype");
     DG_REQUIRE(a.epilogue >= DG_EPILOGUE_STORE && a.epilogue <= DG_EPILOGUE_FP8_CAST, "epilogue");
     const bool fp8_out = a.epilogue == DG_EPILOGUE_FP8_CAST;
     DG_REQUIRE(fp8_out ? a.d_dtype == DG_E4M3 : (a.d_dtype == DG_BF16 || a.d_dtype == DG_F32), "d dtype");
-    DG_REQUIRE(a.a.gran_k == 32 || a.a.gran_k == 128, "gran_k of a");
-    DG_REQUIRE(a.b.gran_k == 32 || a.b.gran_k == 128, "gran_k of b");
+    DG_REQUIRE(bf16 || a.a.gran_k == 32 || a.a.gran_k == 128, "gran_k of a");
+    DG_REQUIRE(bf16 || a.b.gran_k == 32 || a.b.gran_k == 128, "gran_k of b");
+    if (bf16) {
+        DG_REQUIRE(moe_epi == 0 && a.epilogue != DG_EPILOGUE_FP8_CAST, "BF16 operands take the store and stochastic-rounding epilogues");
+        DG_REQUIRE(a.gemm_type != DG_GEMM_BATCHED, "batched GEMMs take FP8 operands");
+        DG_REQUIRE(a.a.ld % 16 == 0 && a.b.ld % 16 == 0, "leading dimensions are multiples of 16 bytes");
+    }
     // Both operands packed E2M1: the dedicated kind::mxf4 path (K-major, one scale per 32 elements)
     const bool mxf4 = a.a.dtype == DG_E2M1_PACKED && a.b.dtype == DG_E2M1_PACKED;
     if (mxf4) {
@@ -524,8 +537,8 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
     DG_REQUIRE(!k_grouped || mxf4 || (a.a.mn_major && a.b.mn_major), "k-grouped FP8 operands are MN-major");
     DG_REQUIRE(!m_grouped || !a.a.mn_major, "m-grouped A is K-major");
     DG_REQUIRE(!m_grouped || a.d_dtype == DG_BF16, "m-grouped D is BF16");
-    DG_REQUIRE(a.a.dtype == DG_E4M3 || a.k % 128 == 0, "FP4 K is a multiple of 128");
-    DG_REQUIRE(a.b.dtype == DG_E4M3 || a.k % 128 == 0, "FP4 K is a multiple of 128");
+    DG_REQUIRE(a.a.dtype != DG_E2M1_PACKED || a.k % 128 == 0, "FP4 K is a multiple of 128");
+    DG_REQUIRE(a.b.dtype != DG_E2M1_PACKED || a.k % 128 == 0, "FP4 K is a multiple of 128");
     if (a.epilogue != DG_EPILOGUE_STORE) {
         DG_REQUIRE(a.gemm_type == DG_GEMM_NORMAL || batched, "value epilogues belong to the dense and batched GEMMs");
         DG_REQUIRE(!a.accumulate && a.alpha == 1.0f, "value epilogues write D directly");
@@ -588,7 +601,7 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
     memset(&launch, 0, sizeof(launch));
     dg::GemmParams& p = launch.p;
     p.tm_r = plan_r.tm, p.tm_c = plan_c.tm, p.tm_sfr = plan_r.tm_sf, p.tm_sfc = plan_c.tm_sf;
-    if (t.swap && !op_c.mn_major && (op_c.dtype == DG_E4M3 || mxf4) && c_rows_per_cta == 128) {
+    if (t.swap && !op_c.mn_major && (op_c.dtype == DG_E4M3 || mxf4 || bf16) && c_rows_per_cta == 128) {
         // narrower views of the token operand for ragged tiles
         for (int i = 0; i < 2; ++i) {
             OperandPlan small;
@@ -702,14 +715,15 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
     launch.epi = moe_epi != 0 ? moe_epi : a.epilogue == DG_EPILOGUE_STOCHASTIC_BF16 ? dg::kEpiStochastic
                  : fp8_out                                                          ? dg::kEpiFp8Cast
                                                                                     : dg::kEpiStore;
-    launch.mxf4 = mxf4;
+    launch.kind = mxf4 ? dg::kKindMxf4 : bf16 ? dg::kKindBf16 : dg::kKindMxf8f6f4;
     int lrc = mxf4 ? dg::dispatch_gemm_mxf4(launch)
+              : bf16 ? dg::dispatch_gemm_bf16(launch)
               : moe_epi != 0 ? dg::dispatch_gemm_moe(launch)
               : launch.epi != dg::kEpiStore ? dg::dispatch_gemm_epi(launch)
                                             : dg::dispatch_gemm_plain(launch);
     if (lrc == dg::kLaunchNoKernel)
-        return fail(DG_ERR_INVALID, "no kernel built for cta_group %d, block_n %d, swap %d, f32 %d, epilogue %d, mxf4 %d",
-                    t.ctas, t.bn, static_cast<int>(t.swap), static_cast<int>(launch.f32), launch.epi, static_cast<int>(mxf4));
+        return fail(DG_ERR_INVALID, "no kernel built for cta_group %d, block_n %d, swap %d, f32 %d, epilogue %d, kind %d",
+                    t.ctas, t.bn, static_cast<int>(t.swap), static_cast<int>(launch.f32), launch.epi, launch.kind);
     if (lrc != 0)
         return fail(DG_ERR_CUDA, "CUDA error: %s launching the GEMM kernel", cudaGetErrorString(static_cast<cudaError_t>(lrc)));
     return DG_OK;

@@ -245,6 +245,25 @@ DG_DEVICE void umma_mxf8f6f4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, 
             : "memory");
 }
 
+// D[tmem] (+)= A[smem] * B[smem] for BF16 operands without scale factors (kind::f16, UMMA K = 16, FP32 accumulation).
+template <int kCtas>
+DG_DEVICE void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (kCtas == 1)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+}
+
 // The same with both operands packed E2M1 (two values per byte in shared memory), UMMA K = 64 and one UE8M0 scale
 // per 32 K elements: two scale bytes per row and instruction (scale_vec::2X), byte ids 0 or 2 of the TMEM word.
 template <int kCtas>
@@ -348,6 +367,19 @@ __host__ __device__ inline uint32_t make_idesc_mxf4(uint32_t umma_m, uint32_t um
     d |= 1u << 10;
     d |= ((umma_n >> 3) & 0x3F) << 17;
     d |= 1u << 23;
+    d |= ((umma_m >> 4) & 0x1F) << 24;
+    return d;
+}
+// kind::f16 with BF16 operands and an FP32 accumulator: no scale fields; [4,6) accumulator format (1 = F32),
+// [7,10) / [10,13) operand formats (1 = BF16), [15] / [16] MN-major flags, [17,23) N >> 3, [24,29) M >> 4.
+__host__ __device__ inline uint32_t make_idesc_bf16(bool a_mn_major, bool b_mn_major, uint32_t umma_m, uint32_t umma_n) {
+    uint32_t d = 0;
+    d |= 1u << 4;
+    d |= 1u << 7;
+    d |= 1u << 10;
+    d |= (a_mn_major ? 1u : 0u) << 15;
+    d |= (b_mn_major ? 1u : 0u) << 16;
+    d |= ((umma_n >> 3) & 0x3F) << 17;
     d |= ((umma_m >> 4) & 0x1F) << 24;
     return d;
 }

@@ -89,9 +89,13 @@ def _logical_mn_k(t: torch.Tensor, major: int) -> Tuple[int, int]:
     return mn, k
 
 
-def _operand(data: torch.Tensor, sf: torch.Tensor, major: int, gran_k: int, batched: bool = False) -> _lib.Operand:
+def _operand(data: torch.Tensor, sf: Optional[torch.Tensor], major: int, gran_k: int, batched: bool = False) -> _lib.Operand:
     op = _lib.Operand()
     op.data = data.data_ptr()
+    if sf is None:                      # BF16 operand: no scale factors
+        op.ld = (data.stride(-2) if major == _K else data.stride(-1)) * data.element_size()
+        op.dtype, op.mn_major = _lib.DG_BF16, int(major == _MN)
+        return op
     op.sf = sf.data_ptr()
     op.ld = (data.stride(-2) if major == _K else data.stride(-1)) * data.element_size()
     op.batch_stride = data.stride(0) * data.element_size() if batched else 0

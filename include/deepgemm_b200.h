@@ -44,8 +44,9 @@ enum dg_epilogue {
 
 enum dg_dtype { DG_E4M3 = 0, DG_E2M1_PACKED = 1, DG_BF16 = 2, DG_F32 = 3 };   /* d_dtype: BF16, F32, or E4M3 (FP8_CAST) */
 
-/* One quantised operand: data plus packed UE8M0 scale factors.
- *   data : E4M3 bytes, or E2M1 codes two per byte (low nibble first).
+/* One operand: quantised data plus packed UE8M0 scale factors, or BF16 data without scales (sf = NULL, gran_k 0;
+ * bf16_gemm_* and their grouped forms, csrc/apis/gemm.hpp:492-726 of the reference).
+ *   data : E4M3 bytes, E2M1 codes two per byte (low nibble first), or BF16.
  *   ld   : distance in bytes between consecutive rows of the non-contiguous axis
  *          (K-major: between MN rows; MN-major: between K rows).
  *   sf   : int32, four UE8M0 exponents per word in K order, MN-major:
@@ -57,8 +58,8 @@ typedef struct dg_operand {
     const int32_t* sf;
     int64_t ld;
     int64_t sf_ld;
-    int32_t dtype;      /* DG_E4M3 or DG_E2M1_PACKED */
-    int32_t mn_major;   /* 0: K contiguous, 1: MN contiguous (E4M3 only) */
+    int32_t dtype;      /* DG_E4M3, DG_E2M1_PACKED or DG_BF16 (then both operands) */
+    int32_t mn_major;   /* 0: K contiguous, 1: MN contiguous (E4M3 and BF16) */
     int32_t gran_k;     /* K elements per scale: 32 or 128 */
     int32_t reserved;
     int64_t batch_stride; /* bytes between the groups / batches of `data`; 0 = stacked without gaps
@@ -76,6 +77,8 @@ typedef struct dg_operand {
  *   BATCHED       : a [G,m,k], b [G,n,k], d [G,m,n], every tensor with its own batch stride
  * Both operands DG_E2M1_PACKED selects the FP4 x FP4 path (tcgen05 kind::mxf4, twice the FP8 rate): K-major
  * operands, gran_k 32 on both sides, k % 128 == 0.
+ * Both operands DG_BF16 selects the unscaled path (tcgen05 kind::f16, FP32 accumulation): every layout but BATCHED,
+ * the STORE and STOCHASTIC_BF16 epilogues, ld a multiple of 16 bytes.
  */
 typedef struct dg_gemm_args {
     int32_t gemm_type;
