@@ -108,9 +108,12 @@ DG_DEVICE bool fused_slot_to_tile(const uint32_t* table, uint32_t num_tiles, uin
 DG_DEVICE bool fused_grid_barrier(uint32_t* ctrl, uint32_t num_ctas, volatile uint32_t* abort_flag, const MoeArgs& a,
                                   uint32_t site) {
     __shared__ uint32_t s_ok;
-    __threadfence_system();   // also covers this CTA's stores to peer buffers
+    // The CTA's threads meet first; then ONE system-scope fence by the arriving thread orders everything the CTA wrote
+    // (its stores to peer buffers too) before the arrival: a fence by each of the 544 threads cost several
+    // microseconds per barrier.
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence_system();
         uint32_t* count = ctrl + MoeCtrl::kGridCount;
         uint32_t* gen = ctrl + MoeCtrl::kGridGen;
         uint32_t my_gen;   // read before arriving: the generation cannot move until this CTA has arrived
