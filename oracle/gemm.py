@@ -8,6 +8,9 @@ kernels take (quantised data + scales) and accumulate in float32 / float64 on th
 host, so that any difference from the kernel output is kernel error, not
 quantisation error.
 
+The BF16 family (tests/test_bf16.py:23-196 of the reference: torch matmuls of the same BF16 tensors) uses the same
+contractions on the operands' float values; there is nothing to dequantise.
+
 Data conventions: FP8 operands are uint8 arrays of E4M3 bit patterns, FP4 operands
 are uint8 arrays with two E2M1 codes per byte (low nibble first); scales are either
 float32 power-of-two arrays or packed int32 (four UE8M0 bytes per word, K order).
