@@ -83,17 +83,25 @@ DG_DEVICE bool fused_wait_counter(const uint32_t* counter, uint32_t target, vola
 }
 
 
-// Schedule slot -> tile.  Slots come in rounds of (n1 + n2): round j holds the first GEMM's n1 tiles of token
-// tile j and the second GEMM's n2 tiles of token tile j - lag.  Returns false for an empty slot.
+// Schedule slot -> tile.  The order is that of rounds of (n1 + n2) slots, round j holding the first GEMM's n1 tiles of
+// token tile j and the second GEMM's n2 tiles of token tile j - lag, with the slots that have no tile left out: the
+// first `lag` rounds hold first-GEMM tiles only, the last `lag` second-GEMM tiles only.  (With the empty slots left
+// in, the units' shares of the last rounds differed by several tiles and the first CTA finished 40-70 us before the
+// last.)  num_tiles * (n1 + n2) slots in all; a second-GEMM tile always comes after the first-GEMM tiles it reads.
 DG_DEVICE bool fused_slot_to_tile(const uint32_t* table, uint32_t num_tiles, uint32_t n1, uint32_t n2, uint32_t lag,
                                   uint32_t slot, FusedTile& t) {
-    const uint32_t round = slot / (n1 + n2), r = slot % (n1 + n2);
-    if (r < n1) {
-        if (round >= num_tiles) return false;
-        t.kind = 0, t.tile = round, t.n_blk = r;
+    const uint32_t head = min(lag, num_tiles);          // token tiles whose two GEMMs are not interleaved with others'
+    const uint32_t head_slots = head * n1, mid_slots = (num_tiles - head) * (n1 + n2);
+    if (slot < head_slots) {
+        t.kind = 0, t.tile = slot / n1, t.n_blk = slot % n1;
+    } else if (slot - head_slots < mid_slots) {
+        const uint32_t s = slot - head_slots, round = head + s / (n1 + n2), r = s % (n1 + n2);
+        if (r < n1) t.kind = 0, t.tile = round, t.n_blk = r;
+        else        t.kind = 1, t.tile = round - lag, t.n_blk = r - n1;
     } else {
-        if (round < lag || round - lag >= num_tiles) return false;
-        t.kind = 1, t.tile = round - lag, t.n_blk = r - n1;
+        const uint32_t s = slot - head_slots - mid_slots;
+        if (s >= head * n2) return false;
+        t.kind = 1, t.tile = num_tiles - head + s / n2, t.n_blk = s % n2;
     }
     const uint32_t* e = table + t.tile * 8;
     t.row0 = e[0], t.rows = e[1], t.group = e[2], t.valid = e[3], t.sf_base = e[4];
@@ -353,7 +361,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) mega_moe_fused_kernel(const 
     uint32_t* pulled = work + MoeFusedWork::pulled(L);
     uint32_t* l1_done = work + MoeFusedWork::l1_done(L);
     const uint32_t n1 = 2 * L.inter / 256, n2 = L.hidden / 256;
-    const uint32_t num_slots = ok ? (num_tiles + p.lag) * (n1 + n2) : 0;
+    const uint32_t num_slots = ok ? num_tiles * (n1 + n2) : 0;
     const uint32_t segments = L.experts_local * L.ranks;
     if (ok) {
         for (uint32_t i = threadIdx.x; i <= segments; i += kFusedThreads)
