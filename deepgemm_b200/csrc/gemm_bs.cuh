@@ -829,6 +829,9 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                             const uint32_t dst = smem_r + stage * Cfg::R_STAGE + b * r_box_bytes;
                             const uint32_t mn = (r_mn + b * r_box_mn) * r_esz;
                             if (r_mn_major) tma_load_3d<kPair>(dst, &p.tm_r, full_bar, mn, kr, r_batch);
+#ifdef DG_EXP_LOAD_HINT
+                            else if (kSwap) tma_load_3d_hint<kPair>(dst, &p.tm_r, full_bar, kr, mn, r_batch, l2_policy_evict_last());
+#endif
                             else            tma_load_3d<kPair>(dst, &p.tm_r, full_bar, kr, mn, r_batch);
                         }
                       }
@@ -1203,7 +1206,11 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                         // the rows after them belong to another tile
                         const CUtensorMap* tm_out = (kSwap && tc.rows - ch * 32 == 16) ? &p.tm_d_half : &p.tm_d;
                         if (p.accumulate) tma_reduce_add_3d(tm_out, slab, cn, cm, cg);
+#ifdef DG_EXP_STORE_HINT
+                        else              tma_store_3d_hint(tm_out, slab, cn, cm, cg, l2_policy_evict_first());
+#else
                         else              tma_store_3d(tm_out, slab, cn, cm, cg);
+#endif
                         tma_store_commit();
                     }
                     buf = buf + 1 == Cfg::kStoreBufs ? 0 : buf + 1;

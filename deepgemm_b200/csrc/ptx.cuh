@@ -167,6 +167,41 @@ DG_DEVICE void tma_store_3d(const void* tmap, uint32_t src_smem, int32_t c0, int
                  "r"(src_smem), "r"(c0), "r"(c1), "r"(c2)
                  : "memory");
 }
+template <bool kCtaGroup2>
+DG_DEVICE void tma_load_3d_hint(uint32_t dst_smem, const void* tmap, uint32_t mbar_addr, int32_t c0, int32_t c1,
+                                int32_t c2, uint64_t policy) {
+    if constexpr (kCtaGroup2) {
+        asm volatile(
+            "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+            " [%0], [%1, {%3, %4, %5}], [%2], %6;" ::"r"(dst_smem),
+            "l"(reinterpret_cast<uint64_t>(tmap)), "r"(mbar_addr), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
+            : "memory");
+    } else {
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+            " [%0], [%1, {%3, %4, %5}], [%2], %6;" ::"r"(dst_smem),
+            "l"(reinterpret_cast<uint64_t>(tmap)), "r"(mbar_addr), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
+            : "memory");
+    }
+}
+// L2 eviction priorities for bulk copies (createpolicy): lines fetched or written with evict_first leave L2 before
+// others, evict_last ones stay longest.
+DG_DEVICE uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+DG_DEVICE uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+DG_DEVICE void tma_store_3d_hint(const void* tmap, uint32_t src_smem, int32_t c0, int32_t c1, int32_t c2, uint64_t policy) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3, %4}], [%1], %5;" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(src_smem), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
+                 : "memory");
+}
 DG_DEVICE void tma_reduce_add_2d(const void* tmap, uint32_t src_smem, int32_t c0, int32_t c1) {
     asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                      reinterpret_cast<uint64_t>(tmap)),
