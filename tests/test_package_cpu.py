@@ -96,6 +96,28 @@ def test_gemm_argument_checks_raise_runtime_error():
     assert lib.dg_gemm_bs(ctypes.byref(args)) == 0          # empty problem: nothing to do
 
 
+def test_bf16_family_surface_and_checks():
+    """The BF16 operators exist under the reference's names (csrc/apis/gemm.hpp:938-985) and refuse wrong dtypes, shapes
+    and mixed operand kinds before anything is launched."""
+    for name in ("bf16_gemm_nt", "bf16_gemm_nn", "bf16_gemm_tn", "bf16_gemm_tt", "m_grouped_bf16_gemm_nt_contiguous",
+                 "m_grouped_bf16_gemm_nn_contiguous", "m_grouped_bf16_gemm_nt_masked", "k_grouped_bf16_gemm_tn_contiguous"):
+        assert callable(getattr(dg, name))
+    a, b = torch.zeros((128, 64), dtype=torch.bfloat16), torch.zeros((128, 64), dtype=torch.bfloat16)
+    d = torch.zeros((128, 128), dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="kBFloat16"):
+        dg.bf16_gemm_nt(a.float(), b, d)
+    with pytest.raises(RuntimeError, match="m == m_ and n == n_ and k == k_"):
+        dg.bf16_gemm_nt(a, b[:, :32], d)
+    with pytest.raises(RuntimeError, match="major_a == cute::UMMA::Major::K"):
+        dg.m_grouped_bf16_gemm_nt_contiguous(a.t().contiguous().t(), b.unsqueeze(0), d, torch.zeros(128, dtype=torch.int32))
+    lib = _lib.lib()
+    args = _lib.GemmArgs()
+    args.gemm_type, args.m, args.n, args.k = 0, 128, 128, 128
+    args.a.data = args.b.data = args.d = 16                  # never dereferenced: the checks come first
+    args.a.dtype, args.b.dtype = _lib.DG_BF16, _lib.DG_E4M3
+    assert lib.dg_gemm_bs(ctypes.byref(args)) != 0 and b"both BF16" in lib.dg_last_error()
+
+
 def test_sf_layout_validation_messages():
     sf = torch.zeros((64, 3), dtype=torch.int32)
     with pytest.raises(RuntimeError, match=r"sf\.size\(-1\)"):
