@@ -700,6 +700,11 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
     DG_REQUIRE(units > 0, "empty grid");
     p.num_units = units;
     p.raster = choose_raster(p.num_m_blocks, unit_m, unit_n, units);
+    // M-grouped layouts whose weights of one group fit L2 comfortably walk the n blocks of a token block first: all of
+    // the group's weight blocks stay hot and each token block is read from DRAM exactly once.  Measured on the grouped
+    // headline shape (8 x ~8192 x 4096 x 7168, 29 MB of weights per group): DRAM reads 0.96 GB against 1.44 GB with
+    // super-rows of eight token blocks, 3 % faster.  (K-grouped shapes measured 5 % slower that way; dense ones equal.)
+    if (m_grouped && static_cast<uint64_t>(a.n) * static_cast<uint64_t>(a.k) <= (40ull << 20)) p.raster = 1;
     if (a.gemm_type == DG_GEMM_M_MASKED && a.num_groups <= static_cast<int>(dg::kMaxBalancedGroups) && a.m <= 65535) {
         std::lock_guard<std::mutex> lk(g_knobs.mu);
         if (g_knobs.masked_cost_first > 0) {
