@@ -817,8 +817,6 @@ def main():
                     help="profiling aid: `gemm` runs the headline GEMM alone (no other configs, no Mega MoE, no CPU "
                          "baseline); `mega_moe` the Mega MoE forward alone; c1 / c3 / c4 / kg / fp4 one other config alone")
     ap.add_argument("--tile", default="", help="tuning aid: cta_group,block_n,swap (0 = automatic) pinned for every GEMM")
-    ap.add_argument("--masked-costs", default="", help="tuning aid: first,next_base,next_per_256_rows of the masked GEMM's "
-                                                     "tile cost estimate (first = 0: round-robin deal)")
     ap.add_argument("--trace", default="", help="with --only mega_moe and a -DDG_TRACE build of the library: write the single "
                                                 "kernel's per-CTA time stamps, summarised, to <this>.ep<N>.rank<r>.txt")
     ap.add_argument("--masked-rows", type=int, default=0, help="tuning aid: config c3 with this many rows in every group")
@@ -848,8 +846,6 @@ def main():
     if args.tile:
         cta, bn, swap = (int(v) for v in args.tile.split(","))
         _lib.check(_lib.lib().dg_debug_set_tile_override(cta, bn, swap))
-    if args.masked_costs:
-        _lib.check(_lib.lib().dg_debug_set_masked_costs(*(int(v) for v in args.masked_costs.split(","))))
     global MASKED_ROWS_OVERRIDE
     MASKED_ROWS_OVERRIDE = args.masked_rows
 
@@ -865,8 +861,7 @@ def main():
     if args.only in CONFIGS:
         out = other_configs(device, max(1, min(args.steps, 10)), args.warmup, which=(args.only,))
         if rank == 0:
-            emit({"other_configs": out, "tile": args.tile or "automatic", "masked_costs": args.masked_costs or "default",
-                  "masked_rows": args.masked_rows or "config"})
+            emit({"other_configs": out, "tile": args.tile or "automatic", "masked_rows": args.masked_rows or "config"})
         return
 
     w = make_c2(device, seed=0)

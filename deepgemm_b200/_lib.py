@@ -20,7 +20,7 @@ EXPORTS = (
     "dg_get_mk_alignment_for_contiguous_layout", "dg_get_theoretical_mk_alignment_for_contiguous_layout",
     "dg_set_wait_timeout_ms", "dg_check_status", "dg_last_error", "dg_version",
     "dg_mega_moe_buffer_layout", "dg_get_token_alignment_for_mega_moe", "dg_mega_moe_forward", "dg_set_mega_moe_fused", "dg_gemm_fp8_fp32sf_noalloc", "dg_noalloc_scratch_bytes",
-    "dg_per_token_cast_to_fp8", "dg_debug_set_tile_override", "dg_get_mega_moe_num_sms", "dg_debug_copy", "dg_set_pdl", "dg_get_pdl", "dg_debug_set_masked_costs", "dg_get_block_m_for_mega_moe",
+    "dg_per_token_cast_to_fp8", "dg_debug_set_tile_override", "dg_get_mega_moe_num_sms", "dg_debug_copy", "dg_set_pdl", "dg_get_pdl", "dg_get_block_m_for_mega_moe",
 )
 
 
@@ -111,7 +111,6 @@ def lib() -> C.CDLL:
                      "dg_set_mega_moe_fused"):
             getattr(l, name).argtypes = [C.c_int32]
         l.dg_debug_set_tile_override.argtypes = [C.c_int32, C.c_int32, C.c_int32]
-        l.dg_debug_set_masked_costs.argtypes = [C.c_int32, C.c_int32, C.c_int32]
         l.dg_debug_copy.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
         _lib = l
     return _lib

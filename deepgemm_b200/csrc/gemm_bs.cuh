@@ -68,7 +68,6 @@ enum WaitSite : uint32_t {
 };
 
 // One UMMA operand as the kernel sees it (all values computed on the host).
-constexpr uint32_t kMaxBalancedGroups = 256;   // masked layouts with more groups keep the round-robin deal
 
 struct OperandParams {
     uint32_t mn_major;    // 0: K is the contiguous axis in global memory
@@ -150,8 +149,6 @@ struct GemmParams {
     uint32_t c_sf_pretransposed;  // same for C (Mega MoE activations: the pool is written in that order)
     MoeEpilogueParams moe;      // fused Mega MoE epilogues (GemmConfig::kEpi == 1, 2)
     CastEpilogueParams cast;    // kEpiFp8Cast
-    uint32_t balance_masked;    // masked layout: cost-balanced runs of slots per unit instead of a round-robin deal
-    uint32_t cost_first, cost_next_base, cost_next_per_256_rows;   // tile cost estimates, see masked_balanced_run
     uint32_t timeout_ms;
     uint32_t* status;           // 16 words: [0] code, [1] site, [2] block, [3] tile iter, [4] k block, [5] stage
     unsigned long long* trace;  // optional clock samples of block 0's first tile (builds with DG_TRACE only)
@@ -406,62 +403,8 @@ struct alignas(8) GemmBarriers {
     uint64_t epi_sync[2];   // fused epilogues: the four epilogue warps meet here once per chunk
     uint32_t tmem_base;
     uint32_t abort;
-    uint32_t sched_first, sched_end;   // masked layout: this unit's run of consecutive schedule slots
-    uint16_t group_rows[kMaxBalancedGroups];   // masked layout: the groups' row counts, staged for the cost scan
 };
 static_assert(sizeof(GemmBarriers) <= 1024, "barrier block");
-
-// Masked layout: schedule slots are not dealt round robin but cut into one run of consecutive slots per unit, the runs
-// balanced by an estimate of each tile's cost.  A group's weight tile (one n block) streams from HBM for the first
-// token block that uses it and comes from L2 for the following ones, which sit right behind it in the same unit's
-// run: tiles differ a lot in cost (first token block: the HBM-bound stream; others: a re-run over cached weights with
-// few tokens), and a round-robin deal leaves some units with only expensive tiles.  Costs are in 1/256 of a first tile.
-// All units evaluate the same integer arithmetic on the same masked_m values, so the runs partition the slots.
-// Called by one thread; rows[] holds the groups' row counts.
-struct MaskedCosts {
-    uint32_t first, next_base, next_per_256_rows;
-};
-DG_DEVICE void masked_balanced_run(const uint16_t* rows, uint32_t num_groups, uint32_t bm, uint32_t num_n,
-                                   const MaskedCosts& mc, uint32_t unit, uint32_t num_units, uint32_t& first_slot,
-                                   uint32_t& end_slot) {
-    auto column_cost = [&](uint32_t r, uint32_t mb) -> uint32_t {   // all token blocks of one n block of a group
-        if (mb == 0) return 0;
-        uint32_t c = mc.first;
-        for (uint32_t j = 1; j < mb; ++j) c += mc.next_base + min(bm, r - j * bm) * mc.next_per_256_rows / 256u;
-        return c;
-    };
-    uint64_t total = 0;
-    for (uint32_t g = 0; g < num_groups; ++g) {
-        const uint32_t r = rows[g], mb = (r + bm - 1) / bm;
-        total += static_cast<uint64_t>(column_cost(r, mb)) * num_n;
-    }
-    // first slot whose middle lies at or beyond `target` on the cost axis
-    auto slot_at = [&](uint64_t target) -> uint32_t {
-        uint64_t prefix = 0;
-        uint32_t slots = 0;
-        for (uint32_t g = 0; g < num_groups; ++g) {
-            const uint32_t r = rows[g], mb = (r + bm - 1) / bm;
-            const uint32_t cc = column_cost(r, mb);
-            const uint64_t gc = static_cast<uint64_t>(cc) * num_n;
-            if (cc != 0 && prefix + gc > target) {
-                const uint64_t into = target > prefix ? target - prefix : 0;
-                const uint32_t col = static_cast<uint32_t>(into / cc);
-                uint32_t rem = static_cast<uint32_t>(into - static_cast<uint64_t>(col) * cc), j = 0, start = 0;
-                // first tile of the column whose middle is >= rem (a tile goes to the unit that holds its middle)
-                while (j < mb) {
-                    const uint32_t c = j == 0 ? mc.first : mc.next_base + min(bm, r - j * bm) * mc.next_per_256_rows / 256u;
-                    if (start + c / 2 >= rem) break;
-                    start += c, ++j;
-                }
-                return slots + col * mb + j;   // j == mb: the next column's first tile
-            }
-            prefix += gc, slots += mb * num_n;
-        }
-        return slots;
-    };
-    first_slot = slot_at((total * unit + num_units - 1) / num_units);
-    end_slot = unit + 1 == num_units ? slot_at(total) : slot_at((total * (unit + 1) + num_units - 1) / num_units);
-}
 
 static __device__ __noinline__ void report_timeout(const GemmParams& p, uint32_t site, uint32_t iter, uint32_t kb,
                                             uint32_t stage) {
@@ -691,19 +634,6 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
     if (warp == 1) {
         tmem_alloc<kCtas>(&bars->tmem_base, Cfg::kTmemCols);
         tmem_relinquish<kCtas>();
-    } else if (warp == 2 && p.balance_masked) {
-        // this unit's run of schedule slots (masked_m is read here: wait for the kernel that may have written it)
-        grid_dependency_wait();
-        for (uint32_t g = lane; g < p.num_groups; g += 32)
-            bars->group_rows[g] = static_cast<uint16_t>(min(static_cast<uint32_t>(max(__ldg(p.grouped_layout + g), 0)), p.m));
-        __syncwarp();
-        if (lane == 0) {
-            MaskedCosts mc{p.cost_first, p.cost_next_base, p.cost_next_per_256_rows};
-            uint32_t first_slot, end_slot;
-            masked_balanced_run(bars->group_rows, p.num_groups, Cfg::UNIT_M, p.num_n_blocks, mc,
-                                kPair ? blockIdx.x / 2 : blockIdx.x, p.num_units, first_slot, end_slot);
-            bars->sched_first = first_slot, bars->sched_end = end_slot;
-        }
     }
     tc_fence_before();
     if (kPair) cluster_sync(); else __syncthreads();
@@ -733,10 +663,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
     };
     TileWalker walker(p, Cfg::UNIT_M, Cfg::UNIT_N, kSwap);
     TileCoord tiles[2];
-    // Schedule slots of this unit: unit, unit + num_units, ... or (balanced masked layout) one run of consecutive slots
-    const uint32_t slot_first = p.balance_masked ? bars->sched_first : unit;
-    const uint32_t slot_stride = p.balance_masked ? 1u : p.num_units;
-    const uint32_t slot_end = p.balance_masked ? bars->sched_end : 0xFFFFFFFFu;
+    // Schedule slots of this unit: unit, unit + num_units, ... (the walker says when they are used up)
     bool ok = true;
     uint32_t acc_iter = 0;   // accumulator tiles handled so far by this role
 
@@ -757,8 +684,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
         const uint32_t sfg_b = kSwap ? p.sf_groups_r : p.sf_groups_c;
         const bool r_batched = p.r.batched != 0, c_batched = p.c.batched != 0;
         for (uint32_t iter = 0; ok; ++iter) {
-            const uint32_t slot = slot_first + iter * slot_stride;
-            if (slot >= slot_end) break;
+            const uint32_t slot = unit + iter * p.num_units;
             const uint32_t num_sub = walker.next(slot, tiles);
             if (num_sub == 0) break;
             for (uint32_t sub = 0; sub < num_sub && ok; ++sub, ++acc_iter) {
@@ -870,8 +796,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
             const uint32_t r_per32 = p.r.gran_k == 32 ? 1u : 0u, c_per32 = p.c.gran_k == 32 ? 1u : 0u;
             const uint32_t sfr_tmem = tmem_base + Cfg::kSfrCol, sfc_tmem = tmem_base + Cfg::kSfcCol;
             for (uint32_t iter = 0; ok; ++iter) {
-                const uint32_t slot = slot_first + iter * slot_stride;
-                if (slot >= slot_end) break;
+                const uint32_t slot = unit + iter * p.num_units;
                 const uint32_t num_sub = walker.next(slot, tiles);
                 if (num_sub == 0) break;
                 for (uint32_t sub = 0; sub < num_sub && ok; ++sub, ++acc_iter) {
@@ -961,8 +886,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
         const uint32_t full_bar = leader_addr(&bars->full[0]);
         if constexpr (!Cfg::kBf16) {   // BF16 operands carry no scale factors
         for (uint32_t iter = 0; ok; ++iter) {
-            const uint32_t slot = slot_first + iter * slot_stride;
-            if (slot >= slot_end) break;
+            const uint32_t slot = unit + iter * p.num_units;
             const uint32_t num_sub = walker.next(slot, tiles);
             if (num_sub == 0) break;
             for (uint32_t sub = 0; sub < num_sub && ok; ++sub, ++acc_iter) {
@@ -1006,8 +930,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
         uint32_t buf = 0, moe_buf = 0, moe_chunks = 0, clamp_count = 0;
         (void)buf, (void)moe_buf, (void)moe_chunks, (void)clamp_count;
         for (uint32_t iter = 0; ok; ++iter) {
-            const uint32_t slot = slot_first + iter * slot_stride;
-            if (slot >= slot_end) break;
+            const uint32_t slot = unit + iter * p.num_units;
             const uint32_t num_sub = walker.next(slot, tiles);
             if (num_sub == 0) break;
             for (uint32_t sub = 0; sub < num_sub && ok; ++sub, ++acc_iter) {

@@ -60,10 +60,6 @@ struct Knobs {
     int moe_fused = 1;     // Mega MoE: one persistent kernel (1) or the kernel-per-phase path (0)
     int pdl = 0;           // launch with programmatic stream serialisation
     int force_cta_group = 0, force_block_n = 0, force_swap = 0;   // dg_debug_set_tile_override
-    // masked layout: tile cost estimates in 1/256 of a group's first token block (dg_debug_set_masked_costs)
-    // 0 (default): round-robin deal.  Measured on config 3: cost-balanced runs were slower (183 vs 132 us): a unit's run
-    // stays inside one group, so the units read 16 groups' token blocks and weights at once instead of sharing one.
-    int masked_cost_first = 0, masked_cost_next_base = 80, masked_cost_next_per_256 = 30;
 } g_knobs;
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -391,14 +387,6 @@ int dg_debug_copy(void* dst, const void* src, int64_t bytes, void* stream) {
     return DG_OK;
 }
 
-int dg_debug_set_masked_costs(int32_t first, int32_t next_base, int32_t next_per_256_rows) {
-    DG_REQUIRE(first >= 0 && next_base >= 0 && next_per_256_rows >= 0 && first <= 65536 && next_base <= 65536 &&
-               next_per_256_rows <= 65536, "costs");
-    std::lock_guard<std::mutex> lk(g_knobs.mu);
-    g_knobs.masked_cost_first = first, g_knobs.masked_cost_next_base = next_base;
-    g_knobs.masked_cost_next_per_256 = next_per_256_rows;
-    return DG_OK;
-}
 int dg_set_wait_timeout_ms(int32_t ms) {
     DG_REQUIRE(ms > 0, "timeout");
     std::lock_guard<std::mutex> lk(g_knobs.mu);
@@ -705,16 +693,6 @@ static int run_gemm(const dg_gemm_args& a, int moe_epi, const dg::MoeEpiloguePar
     // headline shape (8 x ~8192 x 4096 x 7168, 29 MB of weights per group): DRAM reads 0.96 GB against 1.44 GB with
     // super-rows of eight token blocks, 3 % faster.  (K-grouped shapes measured 5 % slower that way; dense ones equal.)
     if (m_grouped && static_cast<uint64_t>(a.n) * static_cast<uint64_t>(a.k) <= (40ull << 20)) p.raster = 1;
-    if (a.gemm_type == DG_GEMM_M_MASKED && a.num_groups <= static_cast<int>(dg::kMaxBalancedGroups) && a.m <= 65535) {
-        std::lock_guard<std::mutex> lk(g_knobs.mu);
-        if (g_knobs.masked_cost_first > 0) {
-            p.balance_masked = 1;
-            p.cost_first = g_knobs.masked_cost_first, p.cost_next_base = g_knobs.masked_cost_next_base;
-            p.cost_next_per_256_rows = g_knobs.masked_cost_next_per_256;
-            p.raster = p.num_m_blocks;   // a group's token blocks of one n block are consecutive slots
-        }
-    }
-
     launch.stream = stream, launch.units = units;
     launch.ctas = t.ctas, launch.bn = t.bn, launch.swap = t.swap, launch.f32 = a.d_dtype == DG_F32;
     launch.epi = moe_epi != 0 ? moe_epi : a.epilogue == DG_EPILOGUE_STOCHASTIC_BF16 ? dg::kEpiStochastic

@@ -331,11 +331,6 @@ int dg_set_wait_timeout_ms(int32_t ms);  /* budget of every device-side wait; de
  * 2 = weights on the UMMA M axis; 0 in any field = choose automatically. */
 int dg_debug_set_tile_override(int32_t cta_group, int32_t block_n, int32_t swap);
 
-/* Tuning aid for the masked grouped GEMM's schedule: its tiles are cut into one run per CTA pair, balanced by estimated
- * cost in 1/256 of the first token block of a (group, n block) - the one that streams the weights from HBM.  A later
- * token block of `r` rows costs next_base + r * next_per_256_rows / 256.  first = 0 switches to a round-robin deal. */
-int dg_debug_set_masked_costs(int32_t first, int32_t next_base, int32_t next_per_256_rows);
-
 /* Measurement aid (no counterpart in the reference): copies `bytes` (a multiple of 16, both addresses 16-byte
  * aligned) with plain 16-byte loads and stores by all SMs, the way the Mega MoE forward pulls token rows.  Given a
  * peer GPU's mapped address as `src` it measures the NVLink bandwidth that path can reach. */
