@@ -16,9 +16,9 @@
 //
 // Warp roles (288 threads):  0 TMA producer of the R tiles | 1 UMMA issuer (+TMEM owner) | 2 scale-factor
 // transposer | 3 TMA producer of the scale factors | 4..7 epilogue (warp % 4 == TMEM lane quadrant) |
-// 8 TMA producer of the C tiles.
+// 8 TMA producer of the C tiles | 9 second scale-factor transposer (kind::mxf4 only: 320 threads).
 //
-// Two UMMA kinds: kind::mxf8f6f4 (E4M3 and unpacked E2M1 operands, 128 K elements per stage, UMMA K = 32) and, when
+// Three UMMA kinds: kind::f16 for BF16 operands without scale factors (64 K elements per stage, UMMA K = 16), kind::mxf8f6f4 (E4M3 and unpacked E2M1 operands, 128 K elements per stage, UMMA K = 32) and, when
 // both operands are packed E2M1, kind::mxf4 (256 K elements per stage in the same 128 bytes per row, UMMA K = 64,
 // two scale words per row and stage: the 9 PFLOP/s path; sm100_fp8_fp4_gemm_1d1d.cuh:51-54 of the reference).
 //
@@ -337,7 +337,10 @@ struct GemmConfig {
     static_assert(!(kSwap && kCdF32), "the transposed epilogue writes BF16 only");
     static_assert(BN % 16 == 0 && BN >= 32 && BN <= 256, "UMMA N");
 
-    static constexpr uint32_t kThreads = 288;   // warps 0-3: R copies, UMMA, scale transposer, scale copies; 4-7: epilogue; 8: C copies
+    // warps 0-3: R copies, UMMA, scale transposer, scale copies; 4-7: epilogue; 8: C copies; 9 (kind::mxf4 only): a second
+    // scale transposer - with one scale per 32 K elements on both sides every K block brings six 128-row scale blocks
+    static constexpr uint32_t kTransposers = kMxf4 ? 2 : 1;
+    static constexpr uint32_t kThreads = 288 + 32 * (kTransposers - 1);
     static constexpr uint32_t BLOCK_K = 128;          // bytes of K per row and stage
     static constexpr uint32_t BLOCK_K_ELEMS = kMxf4 ? 256 : kBf16 ? 64 : 128;
     static constexpr uint32_t SF_WORDS = kMxf4 ? 2 : kBf16 ? 0 : 1;   // packed scale words (128 K elements each) per row and stage
@@ -580,7 +583,7 @@ DG_DEVICE void moe_l2_chunk(const uint8_t* stage, uint32_t pitch, const uint64_t
 }
 
 template <class Cfg>
-__global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__ GemmParams p) {
+__global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_bs_kernel(const __grid_constant__ GemmParams p) {
     constexpr int kCtas = Cfg::kCtas;
     constexpr uint32_t BN = Cfg::BN;
     constexpr uint32_t kStages = Cfg::kStages;
@@ -617,7 +620,7 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
         prefetch_tmap(&p.tm_sfc);
         prefetch_tmap(&p.tm_d);
         for (uint32_t i = 0; i < kStages; ++i) {
-            mbar_init(&bars->full[i], kCtas * (Cfg::kBf16 ? 2 : 3));   // per CTA: R producer, C producer, scale transposer
+            mbar_init(&bars->full[i], kCtas * (Cfg::kBf16 ? 2 : 2 + Cfg::kTransposers));   // per CTA: R producer, C producer, scale transposer(s)
             mbar_init(&bars->empty[i], 1);          // UMMA commit
             mbar_init(&bars->sf_full[i], 1);        // producer (SF copies land here)
         }
@@ -880,10 +883,12 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                 }
             }
         }
-    } else if (warp == 2) {
-        // ============================================================ scale-factor transposer
-        // tcgen05.cp 32x128b.warpx4 wants, per 128 rows, row i's word at position (i % 32) * 4 + i / 32.
+    } else if (warp == 2 || warp == 9) {
+        // ============================================================ scale-factor transposer(s)
+        // tcgen05.cp 32x128b.warpx4 wants, per 128 rows, row i's word at position (i % 32) * 4 + i / 32.  The 128-row
+        // blocks of a K block (R's, then C's) are dealt to the transposer warps in turn.
         const uint32_t full_bar = leader_addr(&bars->full[0]);
+        const uint32_t tr = warp == 2 ? 0u : 1u;
         if constexpr (!Cfg::kBf16) {   // BF16 operands carry no scale factors
         for (uint32_t iter = 0; ok; ++iter) {
             const uint32_t slot = unit + iter * p.num_units;
@@ -902,14 +907,17 @@ __global__ void __launch_bounds__(288, 1) gemm_bs_kernel(const __grid_constant__
                         reinterpret_cast<uint4*>(w)[lane] = make_uint4(v0, v1, v2, v3);
                     };
                     const bool new_r = (kb & sf_mask_r) == 0, new_c = (kb & sf_mask_c) == 0;
+                    constexpr uint32_t kRBlocks = Cfg::SF_WORDS, kCBlocks = Cfg::SF_WORDS * Cfg::SFC_ROWS / 128;
                     if (new_r && !p.r_sf_pretransposed) {
 #pragma unroll
-                        for (uint32_t i = 0; i < Cfg::SF_WORDS; ++i) transpose_128(sf_words_r + stage * (Cfg::SFR_STAGE / 4) + i * 128);
+                        for (uint32_t i = 0; i < kRBlocks; ++i)
+                            if (i % Cfg::kTransposers == tr) transpose_128(sf_words_r + stage * (Cfg::SFR_STAGE / 4) + i * 128);
                     }
                     if (new_c && !p.c_sf_pretransposed) {
 #pragma unroll
-                        for (uint32_t i = 0; i < Cfg::SF_WORDS * Cfg::SFC_ROWS / 128; ++i)
-                            transpose_128(sf_words_c + stage * (Cfg::SFC_STAGE / 4) + i * 128);
+                        for (uint32_t i = 0; i < kCBlocks; ++i)
+                            if ((kRBlocks + i) % Cfg::kTransposers == tr)
+                                transpose_128(sf_words_c + stage * (Cfg::SFC_STAGE / 4) + i * 128);
                     }
                     if ((new_r && !p.r_sf_pretransposed) || (new_c && !p.c_sf_pretransposed)) {
                         fence_proxy_async_smem();   // generic-proxy writes -> visible to tcgen05.cp
